@@ -1,0 +1,63 @@
+"""ctypes binding of libsx8b200.so (the C ABI declared in include/sx8_b200.h).
+
+There is no fallback: if the shared library is missing the import of any kernel
+wrapper raises, and every non-zero status from the library becomes an exception."""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libsx8b200.so")
+
+_vp, _i, _l, _sz, _u = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_size_t, ctypes.c_uint
+
+# name -> (restype, argtypes); mirrors include/sx8_b200.h one to one
+SIGNATURES = {
+    "sx8_version": (_i, []),
+    "sx8_last_error": (ctypes.c_char_p, []),
+    "sx8_gemv_workspace_bytes": (_sz, [_i, _i]),
+    "sx8_gemv": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _sz, _u, _vp]),
+    "sx8_gemm_workspace_bytes": (_sz, [_i, _i, _i]),
+    "sx8_gemm": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp, _sz, _vp]),
+    "sx8_embed": (_i, [_vp, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "sx8_dequant_planes": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _l, _l, _i, _i, _vp, _vp]),
+    "sx8_dequant_v44": (_i, [_vp, _vp, _vp, _vp, _l, _l, _i, _i, _i, _vp, _vp]),
+    "sx8_quantize_blocks": (_i, [_vp, _i, _l, _l, _l, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "sx8_repack_v44": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _l, _i, _i, _vp, _vp, _vp]),
+    "sx8_device_error_flag": (_i, [ctypes.POINTER(ctypes.c_uint)]),
+}
+
+SX8_F_PDL = 1
+
+
+class SX8Error(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise SX8Error("libsx8b200.so is not built (run `python -m sx8_quantization_b200.build`); "
+                           "there is no CPU or PyTorch fallback for the S-X8 kernels")
+        l = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(l, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = l
+    return _lib
+
+
+def check(rc, what):
+    if rc != 0:
+        msg = lib().sx8_last_error().decode(errors="replace")
+        raise SX8Error("%s failed (%d): %s" % (what, rc, msg))
+
+
+def device_error_flag():
+    v = ctypes.c_uint(0)
+    check(lib().sx8_device_error_flag(ctypes.byref(v)), "sx8_device_error_flag")
+    return v.value

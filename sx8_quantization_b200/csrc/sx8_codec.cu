@@ -1,0 +1,380 @@
+// sx8_codec.cu -- bit-exact S-X8 v4.3 codec kernels for sm_100a: full-tensor decode,
+// embedding-row decode, quantizer search + packing, file-plane -> device-layout repack.
+// All four are HBM-bound byte/float work: one thread owns one 8-weight sub-block, so a
+// warp touches 8 consecutive blocks with 4-, 8- and 16-byte accesses.
+#include "sx8_common.cuh"
+
+namespace sx8 {
+
+// Store up to 8 halfs at dst (row-major output), vectorised when the row allows it.
+__device__ __forceinline__ void store8(__half* dst, const __half (&v)[8], int n_valid, bool vec_ok) {
+    if (n_valid >= 8 && vec_ok) {
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(v);
+    } else {
+        for (int i = 0; i < 8; i++)
+            if (i < n_valid) dst[i] = v[i];
+    }
+}
+
+// ------------------------------------------------------------------ dequant (float64)
+// LAYOUT 0: n-major file planes (bid = n*n_cb + kb); LAYOUT 1: kb-major hdr/levels.
+struct DequantArgs {
+    const uint16_t* dmin;
+    const uint16_t* dmax;
+    const uint8_t* config;
+    const uint8_t* coeff;
+    const uint8_t* hi;
+    const uint8_t* lo;
+    const uint8_t* hdr;
+    const uint8_t* levels;
+    const float* bases;
+    const float* scales;
+    long out_f, in_f;
+    int n_cb, hdr_bytes, use_pca;
+    __half* out;
+};
+
+template <int LAYOUT>
+__global__ void __launch_bounds__(256) dequant_d64_kernel(DequantArgs a) {
+    long gid = (long)blockIdx.x * 256 + threadIdx.x;
+    long blk = gid >> 2;  // output-order block index: n*n_cb + kb
+    int sb = (int)(gid & 3);
+    long n_blk = a.out_f * a.n_cb;
+    if (blk >= n_blk) return;
+    long n = blk / a.n_cb;
+    int kb = (int)(blk - n * a.n_cb);
+
+    uint32_t hi4, lo2, cfg, co;
+    float lo_f, hi_f;
+    if (LAYOUT == 0) {
+        hi4 = *reinterpret_cast<const uint32_t*>(a.hi + blk * 16 + sb * 4);
+        lo2 = *reinterpret_cast<const uint16_t*>(a.lo + blk * 8 + sb * 2);
+        lo_f = h2f_bits(a.dmin[blk]);
+        hi_f = h2f_bits(a.dmax[blk]);
+        cfg = a.config[blk];
+        co = a.coeff[blk];
+    } else {
+        long bid = (long)kb * a.out_f + n;
+        const uint8_t* lv = a.levels + bid * 24;
+        hi4 = *reinterpret_cast<const uint32_t*>(lv + sb * 4);
+        lo2 = *reinterpret_cast<const uint16_t*>(lv + 16 + sb * 2);
+        const uint16_t* h = reinterpret_cast<const uint16_t*>(a.hdr + bid * a.hdr_bytes);
+        lo_f = h2f_bits(h[0]);
+        hi_f = h2f_bits(h[1]);
+        uint32_t cc = h[2];
+        cfg = cc & 0xFF;
+        co = cc >> 8;
+    }
+    RangeD64 r = range_d64(lo_f, hi_f, (cfg >> (sb * 2)) & 3);
+    double p0 = 0.0, p1 = 0.0;
+    if (a.use_pca) {
+        p0 = __dmul_rn((double)s4(co & 0xF), (double)a.scales[kb * 2 + 0]);
+        p1 = __dmul_rn((double)s4((co >> 4) & 0xF), (double)a.scales[kb * 2 + 1]);
+    }
+    __align__(16) __half v[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        int lv = level_of(hi4, lo2, i);
+        double w = __fma_rn(r.step, (double)lv, r.rlo);
+        if (a.use_pca) {
+            int t = sb * 8 + i;
+            w = __fma_rn(p0, (double)a.bases[kb * 64 + t], w);
+            w = __fma_rn(p1, (double)a.bases[kb * 64 + 32 + t], w);
+        }
+        v[i] = __float2half_rn(__double2float_rn(w));
+    }
+    long k0 = (long)kb * 32 + sb * 8;
+    long nv = a.in_f - k0;
+    if (nv <= 0) return;
+    bool vec_ok = (a.in_f % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.out) & 15) == 0);
+    store8(a.out + n * a.in_f + k0, v, (int)(nv > 8 ? 8 : nv), vec_ok);
+}
+
+// ------------------------------------------------------------------ embedding (float32)
+// grid (T, ceil(n_cb/64)), block 256: thread = (kb_local = tid>>2, sb = tid&3).
+template <int HDR>
+__global__ void __launch_bounds__(256)
+embed_d32_kernel(const int64_t* __restrict__ ids, const uint8_t* __restrict__ hdr,
+                 const uint8_t* __restrict__ levels, const float* __restrict__ bases,
+                 const float* __restrict__ scales, __half* __restrict__ out, int K, int N, int n_cb) {
+    long t = blockIdx.x;
+    int kb = blockIdx.y * 64 + (threadIdx.x >> 2);
+    int sb = threadIdx.x & 3;
+    if (kb >= n_cb) return;
+    long k0 = (long)kb * 32 + sb * 8;
+    long nv = (long)K - k0;
+    if (nv <= 0) return;
+    bool vec_ok = (K % 8 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+    __half* dst = out + t * (long)K + k0;
+    __align__(16) __half v[8];
+    long row = ids[t];
+    if (row < 0 || row >= N) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = __float2half_rn(0.0f);
+        store8(dst, v, (int)(nv > 8 ? 8 : nv), vec_ok);
+        return;
+    }
+    long bid = (long)kb * N + row;
+    const uint8_t* lv = levels + bid * 24;
+    uint32_t hi4 = *reinterpret_cast<const uint32_t*>(lv + sb * 4);
+    uint32_t lo2 = *reinterpret_cast<const uint16_t*>(lv + 16 + sb * 2);
+    const uint16_t* h = reinterpret_cast<const uint16_t*>(hdr + bid * HDR);
+    float lo_f = h2f_bits(h[0]), hi_f = h2f_bits(h[1]);
+    uint32_t cc = h[2];
+    uint32_t cfg = cc & 0xFF, co = cc >> 8;
+    float rlo, step;
+    range_d32(lo_f, hi_f, (cfg >> (sb * 2)) & 3, rlo, step);
+    // ((float)c0 * scales) first, then one fused multiply-add per term, in the order
+    // of the reference expression (ref cuda/sx8_embed_v44.cu:72-74).
+    float p0 = __fmul_rn((float)s4(co & 0xF), scales[kb * 2]);
+    float p1 = __fmul_rn((float)s4((co >> 4) & 0xF), scales[kb * 2 + 1]);
+    const float4* b0 = reinterpret_cast<const float4*>(bases + kb * 64 + sb * 8);
+    const float4* b1 = reinterpret_cast<const float4*>(bases + kb * 64 + 32 + sb * 8);
+    float4 b0a = b0[0], b0b = b0[1], b1a = b1[0], b1b = b1[1];
+    float bb0[8] = {b0a.x, b0a.y, b0a.z, b0a.w, b0b.x, b0b.y, b0b.z, b0b.w};
+    float bb1[8] = {b1a.x, b1a.y, b1a.z, b1a.w, b1b.x, b1b.y, b1b.z, b1b.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        float w = __fmaf_rn(step, (float)level_of(hi4, lo2, i), rlo);
+        w = __fmaf_rn(p0, bb0[i], w);
+        w = __fmaf_rn(p1, bb1[i], w);
+        v[i] = __float2half_rn(w);
+    }
+    store8(dst, v, (int)(nv > 8 ? 8 : nv), vec_ok);
+}
+
+// ------------------------------------------------------------------ quantizer search
+// ref scripts/quantize_qwen35_4b_sx8_v43_gpu.py:22-47, torch eager float32 semantics:
+// IEEE division, separately rounded multiply and add, round-half-even, strict '<'
+// with the lowest strategy winning ties, mean over 8 as a left-to-right sum / 8.
+template <bool F16IN>
+__global__ void __launch_bounds__(256)
+quantize_kernel(const void* __restrict__ w_, long out_f, long in_f, long ldw, int n_cb,
+                __half* __restrict__ dmin_o, __half* __restrict__ dmax_o,
+                uint8_t* __restrict__ config_o, uint8_t* __restrict__ hi_o,
+                uint8_t* __restrict__ lo_o, uint8_t* __restrict__ lv_o) {
+    long gid = (long)blockIdx.x * 256 + threadIdx.x;
+    long blk = gid >> 2;
+    int sb = (int)(gid & 3);
+    long n_blk = out_f * n_cb;
+    bool valid = blk < n_blk;
+    float x[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) x[i] = 0.0f;
+    if (valid) {
+        long n = blk / n_cb;
+        long k0 = (blk - n * n_cb) * 32 + sb * 8;
+        long nv = in_f - k0;
+        if (F16IN) {
+            const __half* src = reinterpret_cast<const __half*>(w_) + n * ldw + k0;
+            if (nv >= 8 && ((reinterpret_cast<uintptr_t>(src) & 15) == 0)) {
+                uint4 raw = *reinterpret_cast<const uint4*>(src);
+                const __half* hh = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+                for (int i = 0; i < 8; i++) x[i] = __half2float(hh[i]);
+            } else {
+                for (int i = 0; i < 8; i++)
+                    if (i < nv) x[i] = __half2float(src[i]);
+            }
+        } else {
+            const float* src = reinterpret_cast<const float*>(w_) + n * ldw + k0;
+            if (nv >= 8 && ((reinterpret_cast<uintptr_t>(src) & 15) == 0)) {
+                float4 a = reinterpret_cast<const float4*>(src)[0];
+                float4 b = reinterpret_cast<const float4*>(src)[1];
+                x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+                x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+            } else {
+                for (int i = 0; i < 8; i++)
+                    if (i < nv) x[i] = src[i];
+            }
+        }
+    }
+    float mn = x[0], mx = x[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) {
+        mn = fminf(mn, x[i]);
+        mx = fmaxf(mx, x[i]);
+    }
+    mn = fminf(mn, __shfl_xor_sync(0xFFFFFFFFu, mn, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+    mn = fminf(mn, __shfl_xor_sync(0xFFFFFFFFu, mn, 2));
+    mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+
+    float d = fmaxf(__fsub_rn(mx, mn), 1e-10f);
+    float q = __fdiv_rn(d, 4.0f);
+    float best = __int_as_float(0x7F800000);
+    int best_r = 0;
+    uint32_t best_hi = 0, best_lo = 0;
+#pragma unroll
+    for (int r = 0; r < 4; r++) {
+        float lo = (r == 2) ? __fsub_rn(mx, q) : ((r == 3) ? __fadd_rn(mn, q) : mn);
+        float hi = (r == 1) ? __fadd_rn(mn, q) : ((r == 3) ? __fsub_rn(mx, q) : mx);
+        float step = fmaxf(__fdiv_rn(__fsub_rn(hi, lo), 63.0f), 1e-10f);
+        float sum = 0.0f;
+        uint32_t phi = 0, plo = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            float c = rintf(__fdiv_rn(__fsub_rn(x[i], lo), step));
+            c = fminf(fmaxf(c, 0.0f), 63.0f);
+            int ci = (int)c;
+            float rec = __fadd_rn(lo, __fmul_rn(step, (float)ci));
+            float e = __fsub_rn(x[i], rec);
+            sum = __fadd_rn(sum, __fmul_rn(e, e));
+            phi |= (uint32_t)(ci >> 2) << (4 * i);
+            plo |= (uint32_t)(ci & 3) << ((i >> 2) * 8 + (3 - (i & 3)) * 2);
+        }
+        float mse = __fdiv_rn(sum, 8.0f);
+        if (mse < best) {
+            best = mse;
+            best_r = r;
+            best_hi = phi;
+            best_lo = plo;
+        }
+    }
+    uint32_t cfg = (uint32_t)best_r << (2 * sb);
+    cfg |= __shfl_xor_sync(0xFFFFFFFFu, cfg, 1);
+    cfg |= __shfl_xor_sync(0xFFFFFFFFu, cfg, 2);
+    if (!valid) return;
+    *reinterpret_cast<uint32_t*>(hi_o + blk * 16 + sb * 4) = best_hi;
+    *reinterpret_cast<uint16_t*>(lo_o + blk * 8 + sb * 2) = (uint16_t)best_lo;
+    if (lv_o) {
+        uint32_t a = 0, b = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            a |= (uint32_t)level_of(best_hi, best_lo, i) << (8 * i);
+            b |= (uint32_t)level_of(best_hi, best_lo, i + 4) << (8 * i);
+        }
+        *reinterpret_cast<uint2*>(lv_o + blk * 32 + sb * 8) = make_uint2(a, b);
+    }
+    if (sb == 0) {
+        dmin_o[blk] = __float2half_rn(mn);
+        dmax_o[blk] = __float2half_rn(mx);
+        config_o[blk] = (uint8_t)cfg;
+    }
+}
+
+// ------------------------------------------------------------------ repack to v4.4
+// ref scripts/prepare_v44.py:35-79.  One thread per destination block (kb, n), n
+// fastest, so the kb-major writes are contiguous across the warp.
+template <int HDR>
+__global__ void __launch_bounds__(256)
+repack_v44_kernel(const uint16_t* __restrict__ dmin, const uint16_t* __restrict__ dmax,
+                  const uint8_t* __restrict__ config, const uint8_t* __restrict__ coeff,
+                  const uint8_t* __restrict__ hi, const uint8_t* __restrict__ lo, long out_f,
+                  int n_cb, uint8_t* __restrict__ hdr_o, uint8_t* __restrict__ lev_o) {
+    long dst = (long)blockIdx.x * 256 + threadIdx.x;
+    if (dst >= out_f * n_cb) return;
+    long kb = dst / out_f, n = dst - kb * out_f;
+    long src = n * n_cb + kb;
+    uint4 h = *reinterpret_cast<const uint4*>(hi + src * 16);
+    uint2 l = *reinterpret_cast<const uint2*>(lo + src * 8);
+    uint2* lv = reinterpret_cast<uint2*>(lev_o + dst * 24);
+    lv[0] = make_uint2(h.x, h.y);
+    lv[1] = make_uint2(h.z, h.w);
+    lv[2] = l;
+    uint16_t cc = (uint16_t)(config[src] | (coeff[src] << 8));
+    uint16_t* ho = reinterpret_cast<uint16_t*>(hdr_o + dst * HDR);
+    ho[0] = dmin[src];
+    ho[1] = dmax[src];
+    ho[2] = cc;
+    if (HDR == 8) ho[3] = 0;
+}
+
+}  // namespace sx8
+
+// =================================================================== C ABI
+using namespace sx8;
+
+static inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+extern "C" int sx8_dequant_planes(const void* dmin, const void* dmax, const uint8_t* config,
+                                  const uint8_t* coeff, const uint8_t* hi, const uint8_t* lo,
+                                  const float* bases, const float* scales, long out_f, long in_f,
+                                  int n_cb, int use_pca, void* out, void* stream) {
+    SX8_REQUIRE(dmin && dmax && config && coeff && hi && lo && out, "sx8_dequant_planes: null pointer");
+    SX8_REQUIRE(!use_pca || (bases && scales), "sx8_dequant_planes: use_pca needs bases and scales");
+    SX8_REQUIRE(out_f > 0 && in_f > 0 && n_cb == (in_f + 31) / 32,
+                "sx8_dequant_planes: need out_f>0, in_f>0, n_cb == ceil(in_f/32) (got %ld, %ld, %d)", out_f, in_f, n_cb);
+    SX8_REQUIRE(aligned(hi, 4) && aligned(lo, 2) && aligned(dmin, 2) && aligned(dmax, 2) && aligned(out, 2),
+                "sx8_dequant_planes: misaligned plane pointer");
+    DequantArgs a{(const uint16_t*)dmin, (const uint16_t*)dmax, config, coeff, hi, lo, nullptr, nullptr,
+                  bases, scales, out_f, in_f, n_cb, 6, use_pca, (__half*)out};
+    long threads = out_f * n_cb * 4;
+    dequant_d64_kernel<0><<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(a);
+    SX8_LAUNCH_CHECK("dequant_d64_kernel<planes>");
+    return SX8_OK;
+}
+
+extern "C" int sx8_dequant_v44(const void* hdr, const void* levels, const float* bases,
+                               const float* scales, long out_f, long in_f, int n_cb, int hdr_bytes,
+                               int use_pca, void* out, void* stream) {
+    SX8_REQUIRE(hdr && levels && out, "sx8_dequant_v44: null pointer");
+    SX8_REQUIRE(!use_pca || (bases && scales), "sx8_dequant_v44: use_pca needs bases and scales");
+    SX8_REQUIRE(hdr_bytes == 6 || hdr_bytes == 8, "sx8_dequant_v44: hdr_bytes must be 6 or 8 (got %d)", hdr_bytes);
+    SX8_REQUIRE(out_f > 0 && in_f > 0 && n_cb == (in_f + 31) / 32,
+                "sx8_dequant_v44: need out_f>0, in_f>0, n_cb == ceil(in_f/32) (got %ld, %ld, %d)", out_f, in_f, n_cb);
+    SX8_REQUIRE(aligned(hdr, 2) && aligned(levels, 4) && aligned(out, 2), "sx8_dequant_v44: misaligned pointer");
+    DequantArgs a{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, (const uint8_t*)hdr,
+                  (const uint8_t*)levels, bases, scales, out_f, in_f, n_cb, hdr_bytes, use_pca, (__half*)out};
+    long threads = out_f * n_cb * 4;
+    dequant_d64_kernel<1><<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(a);
+    SX8_LAUNCH_CHECK("dequant_d64_kernel<v44>");
+    return SX8_OK;
+}
+
+extern "C" int sx8_embed(const int64_t* ids, long T, const void* hdr, const void* levels,
+                         const float* bases, const float* scales, int K, int N, int n_cb,
+                         int hdr_bytes, void* out, void* stream) {
+    if (T == 0) return SX8_OK;
+    SX8_REQUIRE(ids && hdr && levels && bases && scales && out, "sx8_embed: null pointer");
+    SX8_REQUIRE(T > 0 && T <= 0x7FFFFFFF, "sx8_embed: T out of range (%ld)", T);
+    SX8_REQUIRE(hdr_bytes == 6 || hdr_bytes == 8, "sx8_embed: hdr_bytes must be 6 or 8 (got %d)", hdr_bytes);
+    SX8_REQUIRE(K > 0 && N > 0 && n_cb == (K + 31) / 32, "sx8_embed: need K>0, N>0, n_cb == ceil(K/32) (got %d, %d, %d)", K, N, n_cb);
+    SX8_REQUIRE(aligned(hdr, 2) && aligned(levels, 4) && aligned(bases, 16) && aligned(out, 2) && aligned(ids, 8),
+                "sx8_embed: misaligned pointer");
+    dim3 grid((unsigned)T, (unsigned)((n_cb + 63) / 64));
+    if (hdr_bytes == 6)
+        embed_d32_kernel<6><<<grid, 256, 0, (cudaStream_t)stream>>>(ids, (const uint8_t*)hdr, (const uint8_t*)levels, bases, scales, (__half*)out, K, N, n_cb);
+    else
+        embed_d32_kernel<8><<<grid, 256, 0, (cudaStream_t)stream>>>(ids, (const uint8_t*)hdr, (const uint8_t*)levels, bases, scales, (__half*)out, K, N, n_cb);
+    SX8_LAUNCH_CHECK("embed_d32_kernel");
+    return SX8_OK;
+}
+
+extern "C" int sx8_quantize_blocks(const void* w, int w_is_f16, long out_f, long in_f, long ldw,
+                                   void* dmin, void* dmax, uint8_t* config, uint8_t* hi, uint8_t* lo,
+                                   uint8_t* levels_u8, void* stream) {
+    SX8_REQUIRE(w && dmin && dmax && config && hi && lo, "sx8_quantize_blocks: null pointer");
+    SX8_REQUIRE(out_f > 0 && in_f > 0 && ldw >= in_f, "sx8_quantize_blocks: need out_f>0, in_f>0, ldw>=in_f (got %ld, %ld, %ld)", out_f, in_f, ldw);
+    SX8_REQUIRE(aligned(w, w_is_f16 ? 2 : 4) && aligned(hi, 4) && aligned(lo, 2) && aligned(dmin, 2) && aligned(dmax, 2) &&
+                    (!levels_u8 || aligned(levels_u8, 8)),
+                "sx8_quantize_blocks: misaligned pointer");
+    int n_cb = (int)((in_f + 31) / 32);
+    long threads = out_f * n_cb * 4;
+    SX8_REQUIRE((threads + 255) / 256 <= 0x7FFFFFFFL, "sx8_quantize_blocks: tensor too large for one launch");
+    unsigned grid = (unsigned)((threads + 255) / 256);
+    if (w_is_f16)
+        quantize_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(w, out_f, in_f, ldw, n_cb, (__half*)dmin, (__half*)dmax, config, hi, lo, levels_u8);
+    else
+        quantize_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(w, out_f, in_f, ldw, n_cb, (__half*)dmin, (__half*)dmax, config, hi, lo, levels_u8);
+    SX8_LAUNCH_CHECK("quantize_kernel");
+    return SX8_OK;
+}
+
+extern "C" int sx8_repack_v44(const void* dmin, const void* dmax, const uint8_t* config,
+                              const uint8_t* coeff, const uint8_t* hi, const uint8_t* lo, long out_f,
+                              int n_cb, int hdr_bytes, void* hdr_out, void* levels_out, void* stream) {
+    SX8_REQUIRE(dmin && dmax && config && coeff && hi && lo && hdr_out && levels_out, "sx8_repack_v44: null pointer");
+    SX8_REQUIRE(hdr_bytes == 6 || hdr_bytes == 8, "sx8_repack_v44: hdr_bytes must be 6 or 8 (got %d)", hdr_bytes);
+    SX8_REQUIRE(out_f > 0 && n_cb > 0, "sx8_repack_v44: need out_f>0, n_cb>0");
+    SX8_REQUIRE(aligned(hi, 16) && aligned(lo, 8) && aligned(dmin, 2) && aligned(dmax, 2) && aligned(hdr_out, 2) && aligned(levels_out, 8),
+                "sx8_repack_v44: misaligned pointer");
+    long n_blk = out_f * n_cb;
+    unsigned grid = (unsigned)((n_blk + 255) / 256);
+    if (hdr_bytes == 6)
+        repack_v44_kernel<6><<<grid, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)dmin, (const uint16_t*)dmax, config, coeff, hi, lo, out_f, n_cb, (uint8_t*)hdr_out, (uint8_t*)levels_out);
+    else
+        repack_v44_kernel<8><<<grid, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)dmin, (const uint16_t*)dmax, config, coeff, hi, lo, out_f, n_cb, (uint8_t*)hdr_out, (uint8_t*)levels_out);
+    SX8_LAUNCH_CHECK("repack_v44_kernel");
+    return SX8_OK;
+}

@@ -1,0 +1,76 @@
+// sx8_gemm.cu -- S-X8 v4.3 prefill GEMM entry point (Y = X * W^T, W decoded on the fly).
+//
+// Small and ragged M run as 8-row passes of the decode-GEMV kernel (weights stay in
+// L2 between passes); large M runs on the tcgen05 kernel in sx8_gemm_tc.cu.
+#include "sx8_common.cuh"
+
+namespace sx8 {
+int gemv_launch(const void* x, int M, int K, long ldx, const void* hdr, const void* levels,
+                const float* bases, const float* scales, int N, int n_cb, int hdr_bytes, float* y,
+                void* workspace, unsigned flags, cudaStream_t stream);
+int gemv_check(const char* who, const void* x, int M, int Mmax, int K, long ldx, const void* hdr,
+               const void* levels, const float* bases, const float* scales, int N, int n_cb, int hdr_bytes,
+               const void* y);
+size_t gemm_tc_workspace_bytes(int M, int N, int n_cb);
+bool gemm_tc_supported(int M, int N, int K, int n_cb, int hdr_bytes);
+int gemm_tc_launch(const void* x, int M, int K, long ldx, const void* hdr, const void* levels,
+                   const float* bases, const float* scales, int N, int n_cb, int hdr_bytes, void* y,
+                   int out_f16, void* workspace, cudaStream_t stream);
+
+__global__ void __launch_bounds__(256) f32_to_f16_kernel(const float* __restrict__ in, __half* __restrict__ out, long n) {
+    long i = ((long)blockIdx.x * 256 + threadIdx.x) * 4;
+    if (i + 3 < n) {
+        float4 v = *reinterpret_cast<const float4*>(in + i);
+        __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+        uint2 o = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+        *reinterpret_cast<uint2*>(out + i) = o;
+    } else {
+        for (; i < n; i++) out[i] = __float2half_rn(in[i]);
+    }
+}
+}  // namespace sx8
+
+using namespace sx8;
+
+static size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+extern "C" size_t sx8_gemm_workspace_bytes(int M, int N, int n_cb) {
+    if (M <= 0 || N <= 0 || n_cb <= 0) return 0;
+    size_t table = round256(sx8_gemv_workspace_bytes(n_cb, 8));
+    size_t y32 = round256((size_t)M * (size_t)N * 4);
+    size_t tc = gemm_tc_workspace_bytes(M, N, n_cb);
+    size_t a = table + y32;
+    return a > tc ? a : tc;
+}
+
+extern "C" int sx8_gemm(const void* x, int M, int K, long ldx, const void* hdr, const void* levels,
+                        const float* bases, const float* scales, int N, int n_cb, int hdr_bytes, void* y,
+                        int out_f16, void* workspace, size_t workspace_bytes, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    int rc = gemv_check("sx8_gemm", x, M, 0x7FFFFFFF, K, ldx, hdr, levels, bases, scales, N, n_cb, hdr_bytes, y);
+    if (rc != SX8_OK) return rc;
+    SX8_REQUIRE((long)M * (long)N < (1L << 40), "sx8_gemm: output too large");
+    if (!workspace || workspace_bytes < sx8_gemm_workspace_bytes(M, N, n_cb) ||
+        (reinterpret_cast<uintptr_t>(workspace) % 256) != 0) {
+        set_error("sx8_gemm: workspace must be 256-byte aligned and hold %zu bytes (got %zu)",
+                  sx8_gemm_workspace_bytes(M, N, n_cb), workspace_bytes);
+        return SX8_E_WORKSPACE;
+    }
+    if (gemm_tc_supported(M, N, K, n_cb, hdr_bytes))
+        return gemm_tc_launch(x, M, K, ldx, hdr, levels, bases, scales, N, n_cb, hdr_bytes, y, out_f16, workspace,
+                              stream);
+    uint8_t* table = (uint8_t*)workspace;
+    float* y32 = out_f16 ? (float*)((uint8_t*)workspace + round256(sx8_gemv_workspace_bytes(n_cb, 8))) : (float*)y;
+    for (int m0 = 0; m0 < M; m0 += 8) {
+        int mc = (M - m0 < 8) ? (M - m0) : 8;
+        rc = gemv_launch((const __half*)x + (long)m0 * ldx, mc, K, ldx, hdr, levels, bases, scales, N, n_cb,
+                         hdr_bytes, y32 + (long)m0 * N, table, 0u, stream);
+        if (rc != SX8_OK) return rc;
+    }
+    if (out_f16) {
+        long n = (long)M * N;
+        f32_to_f16_kernel<<<(unsigned)((n / 4 + 255) / 256 + 1), 256, 0, stream>>>(y32, (__half*)y, n);
+        SX8_LAUNCH_CHECK("f32_to_f16_kernel");
+    }
+    return SX8_OK;
+}

@@ -1,0 +1,169 @@
+"""Tensor-level entry points over the C ABI: PyTorch supplies device memory and the
+current CUDA stream, the library does the work.  Every function validates devices and
+dtypes, and raises SX8Error on any failure; none has a fallback path."""
+import torch
+
+from . import _lib
+from ._lib import SX8Error, SX8_F_PDL  # noqa: F401
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _need(t, dtype, name):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise SX8Error("%s must be a CUDA tensor" % name)
+    if t.dtype != dtype:
+        raise SX8Error("%s must be %s (got %s)" % (name, dtype, t.dtype))
+    if not t.is_contiguous():
+        raise SX8Error("%s must be contiguous" % name)
+    return t
+
+
+class Workspace:
+    """Grow-only device scratch buffers, one per (device, tag); the analogue of the
+    reference's pooled Z/Y buffers (ref scripts/sx8_decode1_v3.py:80-88)."""
+    _bufs = {}
+
+    @classmethod
+    def get(cls, device, nbytes, tag="gemv"):
+        key = (device.index if device.index is not None else torch.cuda.current_device(), tag)
+        b = cls._bufs.get(key)
+        if b is None or b.numel() < nbytes:
+            b = torch.empty(max(int(nbytes), 1 << 16), dtype=torch.uint8, device=device)
+            cls._bufs[key] = b
+        return b
+
+
+def gemv(x, hdr, levels, bases, scales, N, K, n_cb, hdr_bytes=6, out=None, flags=0, workspace=None):
+    """y (M,N) f32 = x (M,K) f16 times the packed matrix; M in 1..8."""
+    if x.dim() == 1:
+        x = x.unsqueeze(0)
+    if not x.is_cuda or x.dtype != torch.float16:
+        raise SX8Error("x must be a CUDA float16 tensor")
+    if x.stride(1) != 1 or x.stride(0) < x.shape[1]:
+        x = x.contiguous()
+    M = x.shape[0]
+    _need(hdr, torch.uint8, "hdr"); _need(levels, torch.uint8, "levels")
+    _need(bases, torch.float32, "bases"); _need(scales, torch.float32, "scales")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    else:
+        _need(out, torch.float32, "out")
+        if out.numel() != M * N:
+            raise SX8Error("out has %d elements, need %d" % (out.numel(), M * N))
+    L = _lib.lib()
+    need = L.sx8_gemv_workspace_bytes(n_cb, M)
+    ws = workspace if workspace is not None else Workspace.get(x.device, need)
+    with torch.cuda.device(x.device):
+        rc = L.sx8_gemv(x.data_ptr(), M, K, x.stride(0), hdr.data_ptr(), levels.data_ptr(), bases.data_ptr(),
+                        scales.data_ptr(), N, n_cb, hdr_bytes, out.data_ptr(), ws.data_ptr(), ws.numel(),
+                        flags, _stream(x))
+    _lib.check(rc, "sx8_gemv")
+    return out
+
+
+def gemm(x, hdr, levels, bases, scales, N, K, n_cb, hdr_bytes=6, out_dtype=torch.float32, out=None):
+    """Y (M,N) = X (M,K) f16 times the packed matrix, any M >= 1; fp32 accumulate."""
+    x = _need(x.contiguous(), torch.float16, "x")
+    M = x.shape[0]
+    _need(hdr, torch.uint8, "hdr"); _need(levels, torch.uint8, "levels")
+    _need(bases, torch.float32, "bases"); _need(scales, torch.float32, "scales")
+    if out_dtype not in (torch.float32, torch.float16):
+        raise SX8Error("out_dtype must be float32 or float16")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    else:
+        _need(out, out_dtype, "out")
+    if M == 0:
+        return out
+    L = _lib.lib()
+    need = L.sx8_gemm_workspace_bytes(M, N, n_cb)
+    ws = Workspace.get(x.device, need, "gemm")
+    with torch.cuda.device(x.device):
+        rc = L.sx8_gemm(x.data_ptr(), M, K, x.stride(0), hdr.data_ptr(), levels.data_ptr(), bases.data_ptr(),
+                        scales.data_ptr(), N, n_cb, hdr_bytes, out.data_ptr(), int(out_dtype == torch.float16),
+                        ws.data_ptr(), ws.numel(), _stream(x))
+    _lib.check(rc, "sx8_gemm")
+    return out
+
+
+def embed(ids, hdr, levels, bases, scales, K, N, n_cb, hdr_bytes=6, out=None):
+    """out (T,K) f16 = decoded rows ids[t] (float32 reference arithmetic)."""
+    ids = _need(ids.reshape(-1).to(torch.long).contiguous(), torch.long, "ids")
+    T = ids.numel()
+    if out is None:
+        out = torch.empty((T, K), dtype=torch.float16, device=ids.device)
+    else:
+        _need(out, torch.float16, "out")
+        if out.numel() < T * K:
+            raise SX8Error("out too small")
+    with torch.cuda.device(ids.device):
+        rc = _lib.lib().sx8_embed(ids.data_ptr(), T, hdr.data_ptr(), levels.data_ptr(), bases.data_ptr(),
+                                  scales.data_ptr(), K, N, n_cb, hdr_bytes, out.data_ptr(), _stream(ids))
+    _lib.check(rc, "sx8_embed")
+    return out
+
+
+def dequant_planes(dmin, dmax, config, coeff, hi, lo, bases, scales, out_f, in_f, n_cb, use_pca=True):
+    """(out_f,in_f) f16 from n-major file planes (float64 reference arithmetic)."""
+    out = torch.empty((out_f, in_f), dtype=torch.float16, device=hi.device)
+    with torch.cuda.device(hi.device):
+        rc = _lib.lib().sx8_dequant_planes(dmin.data_ptr(), dmax.data_ptr(), config.data_ptr(), coeff.data_ptr(),
+                                           hi.data_ptr(), lo.data_ptr(), bases.data_ptr(), scales.data_ptr(),
+                                           out_f, in_f, n_cb, int(use_pca), out.data_ptr(), _stream(hi))
+    _lib.check(rc, "sx8_dequant_planes")
+    return out
+
+
+def dequant_v44(hdr, levels, bases, scales, out_f, in_f, n_cb, hdr_bytes=6, use_pca=True):
+    out = torch.empty((out_f, in_f), dtype=torch.float16, device=hdr.device)
+    with torch.cuda.device(hdr.device):
+        rc = _lib.lib().sx8_dequant_v44(hdr.data_ptr(), levels.data_ptr(), bases.data_ptr(), scales.data_ptr(),
+                                        out_f, in_f, n_cb, hdr_bytes, int(use_pca), out.data_ptr(), _stream(hdr))
+    _lib.check(rc, "sx8_dequant_v44")
+    return out
+
+
+def quantize_blocks(w, want_levels=False):
+    """Per-block search + packing of w (out_f,in_f) f16|f32 -> dict of n-major planes
+    (dmin, dmax f16; config, levels_hi, levels_lo u8 [, levels (n_blk,32) u8])."""
+    if w.dtype not in (torch.float16, torch.float32):
+        raise SX8Error("w must be float16 or float32")
+    if not w.is_cuda or w.dim() != 2 or w.stride(1) != 1:
+        raise SX8Error("w must be a 2-D CUDA tensor with unit inner stride")
+    out_f, in_f = w.shape
+    n_cb = (in_f + 31) // 32
+    n_blk = out_f * n_cb
+    dev = w.device
+    dmin = torch.empty(n_blk, dtype=torch.float16, device=dev)
+    dmax = torch.empty(n_blk, dtype=torch.float16, device=dev)
+    config = torch.empty(n_blk, dtype=torch.uint8, device=dev)
+    hi = torch.empty(n_blk * 16, dtype=torch.uint8, device=dev)
+    lo = torch.empty(n_blk * 8, dtype=torch.uint8, device=dev)
+    lv = torch.empty((n_blk, 32), dtype=torch.uint8, device=dev) if want_levels else None
+    with torch.cuda.device(dev):
+        rc = _lib.lib().sx8_quantize_blocks(w.data_ptr(), int(w.dtype == torch.float16), out_f, in_f, w.stride(0),
+                                            dmin.data_ptr(), dmax.data_ptr(), config.data_ptr(), hi.data_ptr(),
+                                            lo.data_ptr(), lv.data_ptr() if lv is not None else None, _stream(w))
+    _lib.check(rc, "sx8_quantize_blocks")
+    out = {"dmin": dmin, "dmax": dmax, "config": config, "levels_hi": hi, "levels_lo": lo,
+           "n_cb": n_cb, "n_blocks": n_blk, "shape": (out_f, in_f)}
+    if lv is not None:
+        out["levels"] = lv
+    return out
+
+
+def repack_v44(dmin, dmax, config, coeff, hi, lo, out_f, n_cb, hdr_bytes=6):
+    """n-major file planes -> kb-major (hdr (n_blk,hdr_bytes), levels (n_blk,24)) on the device."""
+    dev = hi.device
+    n_blk = out_f * n_cb
+    hdr = torch.empty((n_blk, hdr_bytes), dtype=torch.uint8, device=dev)
+    lev = torch.empty((n_blk, 24), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().sx8_repack_v44(dmin.data_ptr(), dmax.data_ptr(), config.data_ptr(), coeff.data_ptr(),
+                                       hi.data_ptr(), lo.data_ptr(), out_f, n_cb, hdr_bytes, hdr.data_ptr(),
+                                       lev.data_ptr(), _stream(hi))
+    _lib.check(rc, "sx8_repack_v44")
+    return hdr, lev

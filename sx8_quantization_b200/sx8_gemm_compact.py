@@ -1,0 +1,32 @@
+"""Drop-in for the reference's scripts/sx8_gemm_compact.py (ref :42-74):
+
+    gemm_sx8_compact(X, qt, bases_info, hdr_t, lvl_t, bas_t, sca_t, hdr_bytes=6,
+                     in_f=None, n_cb=None) -> Y f32 (M, N)
+
+X (M, K) f16 CUDA; K shorter than n_cb*32 is zero-extended inside the kernel (the
+reference pads X on the host, ref :66-71).  The reference decodes tensors with fewer
+than 64 rows to fp16 and calls a library matmul (ref :54-59); here every N that is a
+multiple of 8 runs on the fused kernel and only a ragged N takes the decode + matmul
+route (with this library's own decode kernel)."""
+import torch
+
+from . import ops
+
+
+def gemm_sx8_compact(X, qt, bases_info, hdr_t=None, lvl_t=None, bas_t=None, sca_t=None,
+                     hdr_bytes=6, in_f=None, n_cb=None):
+    if in_f is None:
+        in_f = qt["shape"][1]
+    if n_cb is None:
+        n_cb = qt["n_cb"]
+    out_f = int(qt["shape"][0])
+    if hdr_t is None:
+        from .sx8_decode1_v3 import make_tensors_v44
+        hdr_t, lvl_t, bas_t, sca_t = make_tensors_v44(qt, bases_info, hdr_aligned=(hdr_bytes == 8),
+                                                      device=X.device)
+    Xc = X.contiguous().half()
+    K = min(int(Xc.shape[1]), int(n_cb) * 32)
+    if out_f % 8 != 0:
+        W = ops.dequant_v44(hdr_t, lvl_t, bas_t, sca_t, out_f, int(in_f), int(n_cb), hdr_bytes)
+        return torch.nn.functional.linear(Xc[:, :int(in_f)], W).float()
+    return ops.gemm(Xc, hdr_t, lvl_t, bas_t, sca_t, out_f, K, int(n_cb), hdr_bytes, out_dtype=torch.float32)
