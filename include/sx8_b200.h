@@ -10,11 +10,20 @@
  * Paths cited as "ref:" are files of the reference project
  * (MarlaLabsAI/sx8-quantization) whose interface the entry point replaces.
  *
- * Device layouts (ref: scripts/prepare_v44.py:35-79, "v4.4", kb-major, bid = kb*N + n):
- *   hdr     (n_cb*N, hdr_bytes) u8 : dmin f16 | dmax f16 | config u8 | coeff u8 [| 2 pad]
- *   levels  (n_cb*N, 24)        u8 : hi nibbles of sub-block 0..3 (4 B each), then
- *                                    lo pairs of sub-block 0..3 (2 B each)
- *   bases   (n_cb, 64) f32, scales (n_cb, 2) f32
+ * Device layout "T16" (this library's own; a byte/bit permutation of the reference's
+ * 30-byte block, docs/SX8_FLASH_V4_3_SPEC.md:13-25 -- still exactly 30 bytes per block):
+ *   wt16 = blob of ceil(N/16) * n_cb units of 480 bytes, unit (T, kb) at (T*n_cb + kb)*480,
+ *   holding block row kb of columns 16T..16T+15 (zero blocks past N).  Lane L = 4g+t
+ *   (g = 0..7, t = 0..3) owns sub-block t of column A = 16T+g and B = 16T+g+8; with
+ *   a_i / b_i the 6-bit level of weight 8t+i:
+ *     W0 @ +0   +4L : bytes [a0,a2,a1,a3] << 2 | bits 1:0 of [b4,b6,b5,b7]
+ *     W1 @ +128 +4L : bytes [a4,a6,a5,a7] << 2 | bits 3:2 of [b4,b6,b5,b7]
+ *     W2 @ +256 +4L : bytes [b0,b2,b1,b3] << 2 | bits 5:4 of [b4,b6,b5,b7]
+ *     H0[g] @ +384+4g : dmin(A) | dmax(A)<<16 ; H1[g] @ +416+4g : same for B ;
+ *     H2[g] @ +448+4g : config(A) | coeff(A)<<8 | config(B)<<16 | coeff(B)<<24
+ *   It replaces the reference's kb-major "v4.4" pair hdr (n_blk,6) + levels (n_blk,24)
+ *   (ref: scripts/prepare_v44.py:35-79), which sx8_repack_v44 still produces for
+ *   interchange.  bases (n_cb, 64) f32 and scales (n_cb, 2) f32 are as in the reference.
  * File planes (ref: scripts/sx8_container_v43.py:30-38, "v4.3", n-major, bid = n*n_cb + kb):
  *   dmin, dmax (n_blk) f16; config (n_blk) u8; levels_hi (n_blk*16) u8;
  *   levels_lo (n_blk*8) u8; coeff (n_blk) u8.
@@ -45,39 +54,39 @@ const char* sx8_last_error(void);
 
 /* ---- decode GEMV, batch 1..8 ------------------------------------------------------
  * y[m, n] = sum_k x[m, k] * W[n, k] with W decoded on the fly (PCA correction
- * included), fp32 accumulate.   x: (M, ldx) f16, row stride ldx >= n_cb*32 halfs is
- * not required: columns k >= K are treated as zero.   y: (M, N) f32 row-major.
+ * included), fp32 accumulate.   x: (M, K) f16 with row stride ldx (elements); columns
+ * k >= K count as zero.   y: (M, N) f32 row-major.
  * Replaces ref: cuda/sx8_decode1_v3.cu:185-246 (compute_z44, decode1_v44,
  * decode1_v44_combined) and, for M in 2..8, the small-M use of
  * ref: cuda/sx8_gemm_compact.cu:157-194.
  * workspace: sx8_gemv_workspace_bytes(n_cb, M) bytes of device scratch, 256-byte
- * aligned, private to this call until it completes on the stream.
- * flags: SX8_F_PDL launches the main kernel with programmatic dependent launch so
- * that its weight prefetch overlaps the preceding kernel on the stream.
- * Requires N % 8 == 0 and hdr_bytes in {6, 8}.                                      */
+ * aligned, private to this call until it completes on the stream (used to stage x when
+ * K is not a multiple of 32 or x is not 16-byte aligned row by row).
+ * flags: SX8_F_PDL launches with programmatic dependent launch so that the weight
+ * prefetch overlaps the preceding kernel on the stream.
+ * Requires n_cb <= 1024.                                                             */
 #define SX8_F_PDL 1u
 size_t sx8_gemv_workspace_bytes(int n_cb, int M);
-int sx8_gemv(const void* x_f16, int M, int K, long ldx, const void* hdr, const void* levels,
-             const float* bases, const float* scales, int N, int n_cb, int hdr_bytes,
-             float* y, void* workspace, size_t workspace_bytes, unsigned flags, void* stream);
+int sx8_gemv(const void* x_f16, int M, int K, long ldx, const void* wt16, const float* bases,
+             const float* scales, int N, int n_cb, float* y, void* workspace,
+             size_t workspace_bytes, unsigned flags, void* stream);
 
 /* ---- prefill GEMM, any M ----------------------------------------------------------
  * Y (M, N) = X (M, K) * W^T, fp32 accumulate; out_f16 != 0 writes Y as f16, else f32.
  * Replaces ref: cuda/sx8_gemm_compact.cu:157-194 (compute_z44_batch, gemm_compact) and
  * ref: cuda/sx8_fused_wmma.cu:134-154 (fused_forward).                               */
 size_t sx8_gemm_workspace_bytes(int M, int N, int n_cb);
-int sx8_gemm(const void* x_f16, int M, int K, long ldx, const void* hdr, const void* levels,
-             const float* bases, const float* scales, int N, int n_cb, int hdr_bytes,
-             void* y, int out_f16, void* workspace, size_t workspace_bytes, void* stream);
+int sx8_gemm(const void* x_f16, int M, int K, long ldx, const void* wt16, const float* bases,
+             const float* scales, int N, int n_cb, void* y, int out_f16, void* workspace,
+             size_t workspace_bytes, void* stream);
 
 /* ---- embedding rows ---------------------------------------------------------------
  * out[t, 0..K) = f16(decode(row ids[t])) in the reference kernel's float32 arithmetic.
  * Replaces ref: cuda/sx8_embed_v44.cu:80-94 (sx8_embed_v44).  ids: (T) int64 on the
  * device.  Rows with id outside [0, N) are written as zeros (the reference leaves them
  * untouched and does not guard negative ids).                                        */
-int sx8_embed(const int64_t* ids, long T, const void* hdr, const void* levels,
-              const float* bases, const float* scales, int K, int N, int n_cb, int hdr_bytes,
-              void* out_f16, void* stream);
+int sx8_embed(const int64_t* ids, long T, const void* wt16, const float* bases,
+              const float* scales, int K, int N, int n_cb, void* out_f16, void* stream);
 
 /* ---- full-tensor dequantisation ---------------------------------------------------
  * out (out_f, in_f) f16 = the reference decoder's result: float64 arithmetic, float32
@@ -87,10 +96,9 @@ int sx8_dequant_planes(const void* dmin_f16, const void* dmax_f16, const uint8_t
                        const uint8_t* coeff, const uint8_t* levels_hi, const uint8_t* levels_lo,
                        const float* bases, const float* scales, long out_f, long in_f, int n_cb,
                        int use_pca, void* out_f16, void* stream);
-/* Same result from the kb-major device layout. */
-int sx8_dequant_v44(const void* hdr, const void* levels, const float* bases, const float* scales,
-                    long out_f, long in_f, int n_cb, int hdr_bytes, int use_pca, void* out_f16,
-                    void* stream);
+/* Same result from the T16 device blob. */
+int sx8_dequant_t16(const void* wt16, const float* bases, const float* scales, long out_f,
+                    long in_f, int n_cb, int use_pca, void* out_f16, void* stream);
 
 /* ---- quantizer: per-block strategy search + bit packing ---------------------------
  * w: (out_f, in_f) row-major, f16 (w_is_f16 != 0) or f32, zero-padded on the fly to
@@ -103,7 +111,15 @@ int sx8_quantize_blocks(const void* w, int w_is_f16, long out_f, long in_f, long
                         uint8_t* levels_lo, uint8_t* levels_u8, void* stream);
 
 /* ---- file planes -> device layout -------------------------------------------------
- * Replaces ref: scripts/prepare_v44.py:35-79 (to_v44), done on the device.           */
+ * sx8_repack_t16 replaces ref: scripts/sx8_decode1_v3.py:57-66 (make_tensors_v44) /
+ * scripts/prepare_v44.py:35-79 (to_v44) as the load-time transform, done on the device.
+ * wt16_out: sx8_t16_bytes(out_f, n_cb) bytes, 16-byte aligned.                        */
+size_t sx8_t16_bytes(long N, int n_cb);
+int sx8_repack_t16(const void* dmin_f16, const void* dmax_f16, const uint8_t* config,
+                   const uint8_t* coeff, const uint8_t* levels_hi, const uint8_t* levels_lo,
+                   long out_f, int n_cb, void* wt16_out, void* stream);
+/* The reference's own kb-major "v4.4" pair, byte-identical to to_v44
+ * (ref: scripts/prepare_v44.py:35-79), for interchange with code that expects it.    */
 int sx8_repack_v44(const void* dmin_f16, const void* dmax_f16, const uint8_t* config,
                    const uint8_t* coeff, const uint8_t* levels_hi, const uint8_t* levels_lo,
                    long out_f, int n_cb, int hdr_bytes, void* hdr_out, void* levels_out,

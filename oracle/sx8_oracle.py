@@ -255,3 +255,69 @@ def matmul_ref(x, w_f16):
 
 def num_threads():
     return int(lib().sx8o_num_threads())
+
+
+# --------------------------------------------------------------------------- T16 device layout
+
+T16_UNIT = 480  # bytes per (16-column tile, kb) unit: 384 level bytes + 96 header bytes
+_T16_ORDER = (0, 2, 1, 3)  # byte j of a level word holds weight _T16_ORDER[j] of its group of four
+
+
+def t16_bytes(out_f, n_cb):
+    return ((out_f + 15) // 16) * n_cb * T16_UNIT
+
+
+def to_t16(qt):
+    """The library's own device layout ("T16"), restated in numpy as the checker for
+    sx8_repack_t16.  It is a byte/bit permutation of the reference's 30-byte block
+    (docs/SX8_FLASH_V4_3_SPEC.md:13-25): nothing is added or dropped.
+
+    blob[(T*n_cb + kb)*480 ...]: unit of tile T (columns 16T..16T+15) and block row kb.
+      lane L = 4g + t (g = 0..7, t = 0..3) owns sub-block t of column A = 16T+g and of
+      column B = 16T+g+8.  With a_i / b_i the 6-bit levels of weight 8t+i:
+        word W0 at unit + 0*128 + 4L : bytes [a0,a2,a1,a3] << 2, low 2 bits = bits 1:0 of [b4,b6,b5,b7]
+        word W1 at unit + 1*128 + 4L : bytes [a4,a6,a5,a7] << 2, low 2 bits = bits 3:2 of [b4,b6,b5,b7]
+        word W2 at unit + 2*128 + 4L : bytes [b0,b2,b1,b3] << 2, low 2 bits = bits 5:4 of [b4,b6,b5,b7]
+      header words at unit + 384: H0[g] = dmin(A) | dmax(A) << 16, H1[g] (+32) the same for B,
+        H2[g] (+64) = config(A) | coeff(A) << 8 | config(B) << 16 | coeff(B) << 24.
+    Columns past out_f are zero blocks."""
+    out_f, _ = qt["shape"]
+    n_cb = qt["n_cb"]
+    nt = (out_f + 15) // 16
+    npad = nt * 16
+    lv = np.zeros((npad, n_cb, 4, 8), np.uint32)
+    lv[:out_f] = extract_levels(qt).reshape(out_f, n_cb, 4, 8)
+    dmin = np.zeros((npad, n_cb), np.uint32); dmax = np.zeros((npad, n_cb), np.uint32)
+    cfg = np.zeros((npad, n_cb), np.uint32); co = np.zeros((npad, n_cb), np.uint32)
+    dmin[:out_f] = np.asarray(qt["dmin"], np.float16).view(np.uint16).reshape(out_f, n_cb)
+    dmax[:out_f] = np.asarray(qt["dmax"], np.float16).view(np.uint16).reshape(out_f, n_cb)
+    cfg[:out_f] = np.asarray(qt["config"], np.uint8).reshape(out_f, n_cb)
+    co[:out_f] = np.asarray(qt["coeff"], np.uint8).reshape(out_f, n_cb)
+    # (tile, half, g, kb, ...) views: column = 16T + 8*half + g
+    lv = lv.reshape(nt, 2, 8, n_cb, 4, 8)
+    a, b = lv[:, 0], lv[:, 1]                     # (nt, g, kb, t, 8)
+    o = list(_T16_ORDER)
+    e = b[..., [4 + j for j in o]]                # extras source bytes [b4,b6,b5,b7]
+
+    def word(src4, shift):
+        w = np.zeros(src4.shape[:-1], np.uint32)
+        for j in range(4):
+            byte = (src4[..., j] << 2) | ((e[..., j] >> shift) & 3)
+            w |= byte << (8 * j)
+        return w
+
+    w0 = word(a[..., o], 0)
+    w1 = word(a[..., [4 + j for j in o]], 2)
+    w2 = word(b[..., o], 4)
+    # -> (nt, kb, plane, g, t)
+    lev = np.stack([w0, w1, w2], axis=0).transpose(1, 3, 0, 2, 4)     # (nt, kb, 3, g, t)
+    hd = lambda x: x.reshape(nt, 2, 8, n_cb)
+    dm, dx, cf, cc = hd(dmin), hd(dmax), hd(cfg), hd(co)
+    h0 = dm[:, 0] | (dx[:, 0] << 16)
+    h1 = dm[:, 1] | (dx[:, 1] << 16)
+    h2 = cf[:, 0] | (cc[:, 0] << 8) | (cf[:, 1] << 16) | (cc[:, 1] << 24)
+    hdr = np.stack([h0, h1, h2], axis=0).transpose(1, 3, 0, 2)        # (nt, kb, 3, g)
+    blob = np.empty((nt, n_cb, 120), np.uint32)
+    blob[:, :, :96] = lev.reshape(nt, n_cb, 96)
+    blob[:, :, 96:] = hdr.reshape(nt, n_cb, 24)
+    return np.ascontiguousarray(blob).view(np.uint8).reshape(-1)

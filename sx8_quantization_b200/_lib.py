@@ -15,13 +15,15 @@ SIGNATURES = {
     "sx8_version": (_i, []),
     "sx8_last_error": (ctypes.c_char_p, []),
     "sx8_gemv_workspace_bytes": (_sz, [_i, _i]),
-    "sx8_gemv": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _sz, _u, _vp]),
+    "sx8_gemv": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _i, _i, _vp, _vp, _sz, _u, _vp]),
     "sx8_gemm_workspace_bytes": (_sz, [_i, _i, _i]),
-    "sx8_gemm": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp, _sz, _vp]),
-    "sx8_embed": (_i, [_vp, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "sx8_gemm": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _sz, _vp]),
+    "sx8_embed": (_i, [_vp, _l, _vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "sx8_dequant_planes": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _l, _l, _i, _i, _vp, _vp]),
-    "sx8_dequant_v44": (_i, [_vp, _vp, _vp, _vp, _l, _l, _i, _i, _i, _vp, _vp]),
+    "sx8_dequant_t16": (_i, [_vp, _vp, _vp, _l, _l, _i, _i, _vp, _vp]),
     "sx8_quantize_blocks": (_i, [_vp, _i, _l, _l, _l, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "sx8_t16_bytes": (_sz, [_l, _i]),
+    "sx8_repack_t16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _l, _i, _vp, _vp]),
     "sx8_repack_v44": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _l, _i, _i, _vp, _vp, _vp]),
     "sx8_device_error_flag": (_i, [ctypes.POINTER(ctypes.c_uint)]),
 }

@@ -3,6 +3,7 @@
 // All four are HBM-bound byte/float work: one thread owns one 8-weight sub-block, so a
 // warp touches 8 consecutive blocks with 4-, 8- and 16-byte accesses.
 #include "sx8_common.cuh"
+#include "sx8_layout.cuh"
 
 namespace sx8 {
 
@@ -17,7 +18,7 @@ __device__ __forceinline__ void store8(__half* dst, const __half (&v)[8], int n_
 }
 
 // ------------------------------------------------------------------ dequant (float64)
-// LAYOUT 0: n-major file planes (bid = n*n_cb + kb); LAYOUT 1: kb-major hdr/levels.
+// LAYOUT 0: n-major file planes (bid = n*n_cb + kb); LAYOUT 1: the T16 device blob (in .levels).
 struct DequantArgs {
     const uint16_t* dmin;
     const uint16_t* dmax;
@@ -54,16 +55,17 @@ __global__ void __launch_bounds__(256) dequant_d64_kernel(DequantArgs a) {
         cfg = a.config[blk];
         co = a.coeff[blk];
     } else {
-        long bid = (long)kb * a.out_f + n;
-        const uint8_t* lv = a.levels + bid * 24;
-        hi4 = *reinterpret_cast<const uint32_t*>(lv + sb * 4);
-        lo2 = *reinterpret_cast<const uint16_t*>(lv + 16 + sb * 2);
-        const uint16_t* h = reinterpret_cast<const uint16_t*>(a.hdr + bid * a.hdr_bytes);
-        lo_f = h2f_bits(h[0]);
-        hi_f = h2f_bits(h[1]);
-        uint32_t cc = h[2];
-        cfg = cc & 0xFF;
-        co = cc >> 8;
+        T16Sub q = t16_read(a.levels, n, kb, sb, a.n_cb);
+        hi4 = 0; lo2 = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {   // back to the file-format words so both layouts share one decode
+            hi4 |= (q.lv[i] >> 2) << (4 * i);
+            lo2 |= (q.lv[i] & 3) << ((i >> 2) * 8 + (3 - (i & 3)) * 2);
+        }
+        lo_f = h2f_bits((uint16_t)q.dmin);
+        hi_f = h2f_bits((uint16_t)q.dmax);
+        cfg = q.cfg;
+        co = q.coeff;
     }
     RangeD64 r = range_d64(lo_f, hi_f, (cfg >> (sb * 2)) & 3);
     double p0 = 0.0, p1 = 0.0;
@@ -91,12 +93,13 @@ __global__ void __launch_bounds__(256) dequant_d64_kernel(DequantArgs a) {
 }
 
 // ------------------------------------------------------------------ embedding (float32)
-// grid (T, ceil(n_cb/64)), block 256: thread = (kb_local = tid>>2, sb = tid&3).
-template <int HDR>
+// grid (T, ceil(n_cb/64)), block 256: thread = (kb_local = tid>>2, sb = tid&3).  In the
+// T16 blob the consecutive kb of one row are 480 bytes apart (same tile), so a block's
+// reads stay within one 30 KB span per 64 kb.
 __global__ void __launch_bounds__(256)
-embed_d32_kernel(const int64_t* __restrict__ ids, const uint8_t* __restrict__ hdr,
-                 const uint8_t* __restrict__ levels, const float* __restrict__ bases,
-                 const float* __restrict__ scales, __half* __restrict__ out, int K, int N, int n_cb) {
+embed_d32_kernel(const int64_t* __restrict__ ids, const uint8_t* __restrict__ blob,
+                 const float* __restrict__ bases, const float* __restrict__ scales,
+                 __half* __restrict__ out, int K, int N, int n_cb) {
     long t = blockIdx.x;
     int kb = blockIdx.y * 64 + (threadIdx.x >> 2);
     int sb = threadIdx.x & 3;
@@ -114,20 +117,14 @@ embed_d32_kernel(const int64_t* __restrict__ ids, const uint8_t* __restrict__ hd
         store8(dst, v, (int)(nv > 8 ? 8 : nv), vec_ok);
         return;
     }
-    long bid = (long)kb * N + row;
-    const uint8_t* lv = levels + bid * 24;
-    uint32_t hi4 = *reinterpret_cast<const uint32_t*>(lv + sb * 4);
-    uint32_t lo2 = *reinterpret_cast<const uint16_t*>(lv + 16 + sb * 2);
-    const uint16_t* h = reinterpret_cast<const uint16_t*>(hdr + bid * HDR);
-    float lo_f = h2f_bits(h[0]), hi_f = h2f_bits(h[1]);
-    uint32_t cc = h[2];
-    uint32_t cfg = cc & 0xFF, co = cc >> 8;
+    T16Sub q = t16_read(blob, row, kb, sb, n_cb);
+    float lo_f = h2f_bits((uint16_t)q.dmin), hi_f = h2f_bits((uint16_t)q.dmax);
     float rlo, step;
-    range_d32(lo_f, hi_f, (cfg >> (sb * 2)) & 3, rlo, step);
+    range_d32(lo_f, hi_f, (q.cfg >> (sb * 2)) & 3, rlo, step);
     // ((float)c0 * scales) first, then one fused multiply-add per term, in the order
     // of the reference expression (ref cuda/sx8_embed_v44.cu:72-74).
-    float p0 = __fmul_rn((float)s4(co & 0xF), scales[kb * 2]);
-    float p1 = __fmul_rn((float)s4((co >> 4) & 0xF), scales[kb * 2 + 1]);
+    float p0 = __fmul_rn((float)s4(q.coeff & 0xF), scales[kb * 2]);
+    float p1 = __fmul_rn((float)s4((q.coeff >> 4) & 0xF), scales[kb * 2 + 1]);
     const float4* b0 = reinterpret_cast<const float4*>(bases + kb * 64 + sb * 8);
     const float4* b1 = reinterpret_cast<const float4*>(bases + kb * 64 + 32 + sb * 8);
     float4 b0a = b0[0], b0b = b0[1], b1a = b1[0], b1b = b1[1];
@@ -135,7 +132,7 @@ embed_d32_kernel(const int64_t* __restrict__ ids, const uint8_t* __restrict__ hd
     float bb1[8] = {b1a.x, b1a.y, b1a.z, b1a.w, b1b.x, b1b.y, b1b.z, b1b.w};
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        float w = __fmaf_rn(step, (float)level_of(hi4, lo2, i), rlo);
+        float w = __fmaf_rn(step, (float)q.lv[i], rlo);
         w = __fmaf_rn(p0, bb0[i], w);
         w = __fmaf_rn(p1, bb1[i], w);
         v[i] = __float2half_rn(w);
@@ -280,6 +277,61 @@ repack_v44_kernel(const uint16_t* __restrict__ dmin, const uint16_t* __restrict_
     if (HDR == 8) ho[3] = 0;
 }
 
+// ------------------------------------------------------------------ repack to T16
+// One thread per (tile, kb, lane): gathers the two sub-blocks it owns from the n-major
+// file planes and writes its three level words; lanes t = 0,1,2 also write H0,H1,H2.
+__global__ void __launch_bounds__(256)
+repack_t16_kernel(const uint16_t* __restrict__ dmin, const uint16_t* __restrict__ dmax,
+                  const uint8_t* __restrict__ config, const uint8_t* __restrict__ coeff,
+                  const uint8_t* __restrict__ hi, const uint8_t* __restrict__ lo, long N, int n_cb,
+                  uint8_t* __restrict__ blob) {
+    long gid = (long)blockIdx.x * 256 + threadIdx.x;
+    long n_units = t16_tiles(N) * n_cb;
+    long unit = gid >> 5;
+    if (unit >= n_units) return;
+    int L = (int)(gid & 31), g = L >> 2, t = L & 3;
+    long T = unit / n_cb, kb = unit - T * n_cb;
+    long colA = T * 16 + g, colB = colA + 8;
+    uint32_t a[8], b[8];
+    uint32_t hA = 0, hB = 0, ccA = 0, ccB = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) { a[i] = 0; b[i] = 0; }
+    if (colA < N) {
+        long bid = colA * n_cb + kb;
+        uint32_t hi4 = *reinterpret_cast<const uint32_t*>(hi + bid * 16 + t * 4);
+        uint32_t lo2 = *reinterpret_cast<const uint16_t*>(lo + bid * 8 + t * 2);
+#pragma unroll
+        for (int i = 0; i < 8; i++) a[i] = (uint32_t)level_of(hi4, lo2, i);
+        hA = (uint32_t)dmin[bid] | ((uint32_t)dmax[bid] << 16);
+        ccA = (uint32_t)config[bid] | ((uint32_t)coeff[bid] << 8);
+    }
+    if (colB < N) {
+        long bid = colB * n_cb + kb;
+        uint32_t hi4 = *reinterpret_cast<const uint32_t*>(hi + bid * 16 + t * 4);
+        uint32_t lo2 = *reinterpret_cast<const uint16_t*>(lo + bid * 8 + t * 2);
+#pragma unroll
+        for (int i = 0; i < 8; i++) b[i] = (uint32_t)level_of(hi4, lo2, i);
+        hB = (uint32_t)dmin[bid] | ((uint32_t)dmax[bid] << 16);
+        ccB = (uint32_t)config[bid] | ((uint32_t)coeff[bid] << 8);
+    }
+    const int ord[4] = {0, 2, 1, 3};
+    uint32_t W0 = 0, W1 = 0, W2 = 0;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        uint32_t e = b[4 + ord[j]];
+        W0 |= ((a[ord[j]] << 2) | (e & 3)) << (8 * j);
+        W1 |= ((a[4 + ord[j]] << 2) | ((e >> 2) & 3)) << (8 * j);
+        W2 |= ((b[ord[j]] << 2) | ((e >> 4) & 3)) << (8 * j);
+    }
+    uint32_t* u = reinterpret_cast<uint32_t*>(blob + unit * T16_UNIT);
+    u[L] = W0;
+    u[32 + L] = W1;
+    u[64 + L] = W2;
+    if (t == 0) u[96 + g] = hA;
+    if (t == 1) u[104 + g] = hB;
+    if (t == 2) u[112 + g] = ccA | (ccB << 16);
+}
+
 }  // namespace sx8
 
 // =================================================================== C ABI
@@ -305,39 +357,49 @@ extern "C" int sx8_dequant_planes(const void* dmin, const void* dmax, const uint
     return SX8_OK;
 }
 
-extern "C" int sx8_dequant_v44(const void* hdr, const void* levels, const float* bases,
-                               const float* scales, long out_f, long in_f, int n_cb, int hdr_bytes,
-                               int use_pca, void* out, void* stream) {
-    SX8_REQUIRE(hdr && levels && out, "sx8_dequant_v44: null pointer");
-    SX8_REQUIRE(!use_pca || (bases && scales), "sx8_dequant_v44: use_pca needs bases and scales");
-    SX8_REQUIRE(hdr_bytes == 6 || hdr_bytes == 8, "sx8_dequant_v44: hdr_bytes must be 6 or 8 (got %d)", hdr_bytes);
+extern "C" int sx8_dequant_t16(const void* wt16, const float* bases, const float* scales, long out_f,
+                               long in_f, int n_cb, int use_pca, void* out, void* stream) {
+    SX8_REQUIRE(wt16 && out, "sx8_dequant_t16: null pointer");
+    SX8_REQUIRE(!use_pca || (bases && scales), "sx8_dequant_t16: use_pca needs bases and scales");
     SX8_REQUIRE(out_f > 0 && in_f > 0 && n_cb == (in_f + 31) / 32,
-                "sx8_dequant_v44: need out_f>0, in_f>0, n_cb == ceil(in_f/32) (got %ld, %ld, %d)", out_f, in_f, n_cb);
-    SX8_REQUIRE(aligned(hdr, 2) && aligned(levels, 4) && aligned(out, 2), "sx8_dequant_v44: misaligned pointer");
-    DequantArgs a{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, (const uint8_t*)hdr,
-                  (const uint8_t*)levels, bases, scales, out_f, in_f, n_cb, hdr_bytes, use_pca, (__half*)out};
+                "sx8_dequant_t16: need out_f>0, in_f>0, n_cb == ceil(in_f/32) (got %ld, %ld, %d)", out_f, in_f, n_cb);
+    SX8_REQUIRE(aligned(wt16, 16) && aligned(out, 2), "sx8_dequant_t16: misaligned pointer");
+    DequantArgs a{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, (const uint8_t*)wt16,
+                  bases, scales, out_f, in_f, n_cb, 6, use_pca, (__half*)out};
     long threads = out_f * n_cb * 4;
     dequant_d64_kernel<1><<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(a);
-    SX8_LAUNCH_CHECK("dequant_d64_kernel<v44>");
+    SX8_LAUNCH_CHECK("dequant_d64_kernel<t16>");
     return SX8_OK;
 }
 
-extern "C" int sx8_embed(const int64_t* ids, long T, const void* hdr, const void* levels,
-                         const float* bases, const float* scales, int K, int N, int n_cb,
-                         int hdr_bytes, void* out, void* stream) {
+extern "C" int sx8_embed(const int64_t* ids, long T, const void* wt16, const float* bases,
+                         const float* scales, int K, int N, int n_cb, void* out, void* stream) {
     if (T == 0) return SX8_OK;
-    SX8_REQUIRE(ids && hdr && levels && bases && scales && out, "sx8_embed: null pointer");
+    SX8_REQUIRE(ids && wt16 && bases && scales && out, "sx8_embed: null pointer");
     SX8_REQUIRE(T > 0 && T <= 0x7FFFFFFF, "sx8_embed: T out of range (%ld)", T);
-    SX8_REQUIRE(hdr_bytes == 6 || hdr_bytes == 8, "sx8_embed: hdr_bytes must be 6 or 8 (got %d)", hdr_bytes);
     SX8_REQUIRE(K > 0 && N > 0 && n_cb == (K + 31) / 32, "sx8_embed: need K>0, N>0, n_cb == ceil(K/32) (got %d, %d, %d)", K, N, n_cb);
-    SX8_REQUIRE(aligned(hdr, 2) && aligned(levels, 4) && aligned(bases, 16) && aligned(out, 2) && aligned(ids, 8),
+    SX8_REQUIRE(aligned(wt16, 16) && aligned(bases, 16) && aligned(out, 2) && aligned(ids, 8),
                 "sx8_embed: misaligned pointer");
     dim3 grid((unsigned)T, (unsigned)((n_cb + 63) / 64));
-    if (hdr_bytes == 6)
-        embed_d32_kernel<6><<<grid, 256, 0, (cudaStream_t)stream>>>(ids, (const uint8_t*)hdr, (const uint8_t*)levels, bases, scales, (__half*)out, K, N, n_cb);
-    else
-        embed_d32_kernel<8><<<grid, 256, 0, (cudaStream_t)stream>>>(ids, (const uint8_t*)hdr, (const uint8_t*)levels, bases, scales, (__half*)out, K, N, n_cb);
+    embed_d32_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(ids, (const uint8_t*)wt16, bases, scales, (__half*)out, K, N, n_cb);
     SX8_LAUNCH_CHECK("embed_d32_kernel");
+    return SX8_OK;
+}
+
+extern "C" size_t sx8_t16_bytes(long N, int n_cb) { return (N > 0 && n_cb > 0) ? t16_bytes(N, n_cb) : 0; }
+
+extern "C" int sx8_repack_t16(const void* dmin, const void* dmax, const uint8_t* config,
+                              const uint8_t* coeff, const uint8_t* hi, const uint8_t* lo, long out_f,
+                              int n_cb, void* wt16_out, void* stream) {
+    SX8_REQUIRE(dmin && dmax && config && coeff && hi && lo && wt16_out, "sx8_repack_t16: null pointer");
+    SX8_REQUIRE(out_f > 0 && n_cb > 0, "sx8_repack_t16: need out_f>0, n_cb>0");
+    SX8_REQUIRE(aligned(hi, 4) && aligned(lo, 2) && aligned(dmin, 2) && aligned(dmax, 2) && aligned(wt16_out, 16),
+                "sx8_repack_t16: misaligned pointer");
+    long threads = t16_tiles(out_f) * n_cb * 32;
+    SX8_REQUIRE((threads + 255) / 256 <= 0x7FFFFFFFL, "sx8_repack_t16: tensor too large for one launch");
+    repack_t16_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        (const uint16_t*)dmin, (const uint16_t*)dmax, config, coeff, hi, lo, out_f, n_cb, (uint8_t*)wt16_out);
+    SX8_LAUNCH_CHECK("repack_t16_kernel");
     return SX8_OK;
 }
 

@@ -5,17 +5,16 @@
 #include "sx8_common.cuh"
 
 namespace sx8 {
-int gemv_launch(const void* x, int M, int K, long ldx, const void* hdr, const void* levels,
-                const float* bases, const float* scales, int N, int n_cb, int hdr_bytes, float* y,
-                void* workspace, unsigned flags, cudaStream_t stream);
-int gemv_check(const char* who, const void* x, int M, int Mmax, int K, long ldx, const void* hdr,
-               const void* levels, const float* bases, const float* scales, int N, int n_cb, int hdr_bytes,
-               const void* y);
+int gemv_launch(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
+                const float* scales, int N, int n_cb, float* y, void* workspace, unsigned flags,
+                cudaStream_t stream);
+int gemv_check(const char* who, const void* x, int M, int Mmax, int K, long ldx, const void* wt16,
+               const float* bases, const float* scales, int N, int n_cb, const void* y);
 size_t gemm_tc_workspace_bytes(int M, int N, int n_cb);
-bool gemm_tc_supported(int M, int N, int K, int n_cb, int hdr_bytes);
-int gemm_tc_launch(const void* x, int M, int K, long ldx, const void* hdr, const void* levels,
-                   const float* bases, const float* scales, int N, int n_cb, int hdr_bytes, void* y,
-                   int out_f16, void* workspace, cudaStream_t stream);
+bool gemm_tc_supported(int M, int N, int K, int n_cb);
+int gemm_tc_launch(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
+                   const float* scales, int N, int n_cb, void* y, int out_f16, void* workspace,
+                   cudaStream_t stream);
 
 __global__ void __launch_bounds__(256) f32_to_f16_kernel(const float* __restrict__ in, __half* __restrict__ out, long n) {
     long i = ((long)blockIdx.x * 256 + threadIdx.x) * 4;
@@ -43,11 +42,11 @@ extern "C" size_t sx8_gemm_workspace_bytes(int M, int N, int n_cb) {
     return a > tc ? a : tc;
 }
 
-extern "C" int sx8_gemm(const void* x, int M, int K, long ldx, const void* hdr, const void* levels,
-                        const float* bases, const float* scales, int N, int n_cb, int hdr_bytes, void* y,
-                        int out_f16, void* workspace, size_t workspace_bytes, void* stream_) {
+extern "C" int sx8_gemm(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
+                        const float* scales, int N, int n_cb, void* y, int out_f16, void* workspace,
+                        size_t workspace_bytes, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
-    int rc = gemv_check("sx8_gemm", x, M, 0x7FFFFFFF, K, ldx, hdr, levels, bases, scales, N, n_cb, hdr_bytes, y);
+    int rc = gemv_check("sx8_gemm", x, M, 0x7FFFFFFF, K, ldx, wt16, bases, scales, N, n_cb, y);
     if (rc != SX8_OK) return rc;
     SX8_REQUIRE((long)M * (long)N < (1L << 40), "sx8_gemm: output too large");
     if (!workspace || workspace_bytes < sx8_gemm_workspace_bytes(M, N, n_cb) ||
@@ -56,15 +55,14 @@ extern "C" int sx8_gemm(const void* x, int M, int K, long ldx, const void* hdr, 
                   sx8_gemm_workspace_bytes(M, N, n_cb), workspace_bytes);
         return SX8_E_WORKSPACE;
     }
-    if (gemm_tc_supported(M, N, K, n_cb, hdr_bytes))
-        return gemm_tc_launch(x, M, K, ldx, hdr, levels, bases, scales, N, n_cb, hdr_bytes, y, out_f16, workspace,
-                              stream);
+    if (gemm_tc_supported(M, N, K, n_cb))
+        return gemm_tc_launch(x, M, K, ldx, wt16, bases, scales, N, n_cb, y, out_f16, workspace, stream);
     uint8_t* table = (uint8_t*)workspace;
     float* y32 = out_f16 ? (float*)((uint8_t*)workspace + round256(sx8_gemv_workspace_bytes(n_cb, 8))) : (float*)y;
     for (int m0 = 0; m0 < M; m0 += 8) {
         int mc = (M - m0 < 8) ? (M - m0) : 8;
-        rc = gemv_launch((const __half*)x + (long)m0 * ldx, mc, K, ldx, hdr, levels, bases, scales, N, n_cb,
-                         hdr_bytes, y32 + (long)m0 * N, table, 0u, stream);
+        rc = gemv_launch((const __half*)x + (long)m0 * ldx, mc, K, ldx, wt16, bases, scales, N, n_cb,
+                         y32 + (long)m0 * N, table, 0u, stream);
         if (rc != SX8_OK) return rc;
     }
     if (out_f16) {

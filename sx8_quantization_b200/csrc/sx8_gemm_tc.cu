@@ -3,9 +3,9 @@
 
 namespace sx8 {
 size_t gemm_tc_workspace_bytes(int, int, int) { return 0; }
-bool gemm_tc_supported(int, int, int, int, int) { return false; }
-int gemm_tc_launch(const void*, int, int, long, const void*, const void*, const float*, const float*, int, int,
-                   int, void*, int, void*, cudaStream_t) {
+bool gemm_tc_supported(int, int, int, int) { return false; }
+int gemm_tc_launch(const void*, int, int, long, const void*, const float*, const float*, int, int, void*, int,
+                   void*, cudaStream_t) {
     set_error("sx8_gemm: tcgen05 path not built");
     return SX8_E_UNSUPPORTED;
 }

@@ -1,4 +1,4 @@
-// sx8_gemv.cu -- S-X8 v4.3 decode GEMV for batch 1..8 on sm_100a.
+// sx8_gemv.cu -- S-X8 v4.3 decode GEMV for batch 1..8 on sm_100a (T16 device layout).
 //
 //   y[m, n] = sum_kb { base(kb,n) * D(kb,n,m) + lo(kb,n) * SxB(kb,m)
 //                      + c0(kb,n) * Z0(kb,m) + c1(kb,n) * Z1(kb,m) }
@@ -9,31 +9,35 @@
 //
 // This is the reference's reformulated decode (ref cuda/sx8_decode1_v3.cu:7-13,
 // :108-157: w = rlo + step*level, PCA as 2 multiply-adds per block) regrouped so that
-// the per-weight work is integer extraction only: rlo = lo + off*q and step =
+// the per-weight work is bit extraction only: rlo = lo + off*q and step =
 // mult*q*0.015873 with q = (dmax-dmin)/4, and off/0.015873 is taken as 63*off
-// (relative deviation 1e-6 on that term; the step clamp at 1e-10 only acts on
-// blocks with dmax == dmin, where it moves a weight by < 7e-9).  Products of fp16
+// (relative deviation 1e-6 on that term; the step clamp at 1e-10 only acts on blocks
+// with dmax == dmin, where it moves a weight by < 7e-9).  Products of small fp16
 // integers and fp16 activations are exact in the tensor-core fp32 accumulation, so the
 // result carries fp32-accumulate error only.
 //
-// Data movement: a producer thread streams [kb x TN-column] slabs of the kb-major
-// hdr/levels planes into shared memory with 1-D TMA bulk copies behind an mbarrier
-// ring; 8 consumer warps decode from shared memory and feed mma.sync m16n8k16 with
-// the <=8 activation rows as the n=8 operand, so batch 1..8 cost the same.  The
-// activation-side operands (permuted x, SxB and Z split into fp16 hi/lo) come from a
-// table built once per call by xprep_kernel.  Split-K across a thread-block cluster
-// is reduced through distributed shared memory in rank order (deterministic).
+// One launch per GEMV.  A producer warp streams, per pipeline stage, one contiguous
+// [kb-range x 480 B] slab per 16-column tile of the T16 blob plus the matching slice of
+// every activation row into shared memory with TMA bulk copies (one copy per lane)
+// behind an mbarrier ring; weights are requested before, activations after the
+// programmatic-dependent-launch wait.  Eight consumer warps first build the small table
+// of activation-side operands (SxB and Z, split into fp16 hi/lo) for the CTA's kb range,
+// then decode levels with byte-parallel masks and feed mma.sync m16n8k16 with the <= 8
+// activation rows as the n = 8 operand, so batch 1..8 cost the same.  Split-K across a
+// thread-block cluster is reduced through distributed shared memory in rank order
+// (deterministic).
+#include <stdlib.h>
+
 #include "sx8_common.cuh"
+#include "sx8_layout.cuh"
 
 namespace sx8 {
 
 constexpr int kConsumerWarps = 8;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
-constexpr int KB_S = 4;                 // kb rows per pipeline stage
-constexpr int TAB_X = 512;              // bytes per kb: x pairs  [m][t][4 x half2]
-constexpr int TAB_D = 128;              // bytes per kb: direct-term operands [m][t][half2]
-constexpr int TAB_KB = TAB_X + TAB_D;   // table stride per kb
 constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int kMaxKbPerCta = 256;   // capacity of the per-CTA activation table
+constexpr int DT_KB = 128;          // table bytes per kb: [m][t] words
 
 // ------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -96,15 +100,13 @@ __device__ __forceinline__ uint32_t lds32(uint32_t a) {
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
     return v;
 }
-__device__ __forceinline__ uint32_t lds16(uint32_t a) {
-    uint32_t v;
-    asm volatile("{ .reg .u16 t; ld.shared.u16 t, [%1]; cvt.u32.u16 %0, t; }" : "=r"(v) : "r"(a));
-    return v;
-}
 __device__ __forceinline__ uint4 lds128(uint32_t a) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
     return v;
+}
+__device__ __forceinline__ void sts32(uint32_t a, uint32_t v) {
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
 }
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -118,163 +120,77 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t local_addr, uint32_t ra
                  : "r"(ra));
     return v;
 }
-
-// fp32 -> (hi, lo) fp16 pair packed as half2 {hi, lo}: hi + lo == v to ~22 bits.
-__device__ __forceinline__ uint32_t split_hilo(float v) {
-    __half h = __float2half_rn(v);
-    __half l = __float2half_rn(v - __half2float(h));
-    return (uint32_t)__half_as_ushort(h) | ((uint32_t)__half_as_ushort(l) << 16);
+__device__ __forceinline__ void consumer_bar() {  // the 8 consumer warps only
+    asm volatile("bar.sync 1, 256;" ::: "memory");
 }
 
-// ------------------------------------------------------------------ xprep
-// One warp per kb; lane = (m = lane>>2, t = lane&3).  Writes for every row m < M:
-//   X part  [kb][m][t] : 4 x half2 { x[8t+p], x[8t+p+4] }, p = 0..3  (the k-slot order
-//                        in which the main kernel lays out a sub-block's weights)
-//   D part  [kb][m][t] : t=0 {SxB_hi, SxB_lo}; t=1 {Z0_hi, Z1_hi}; t=2 {Z0_lo, Z1_lo}; t=3 0
-//                        with Zj pre-multiplied by 1024 (the coefficient operand carries 2^-10).
-// Zj follows ref cuda/sx8_decode1_v3.cu:44-65 (compute_z44_kernel) in float32.
+// fp32 -> (hi, lo) fp16 pair: hi + lo == v to ~22 bits.
+__device__ __forceinline__ void split_hilo(float v, uint32_t& hi, uint32_t& lo) {
+    __half h = __float2half_rn(v);
+    __half l = __float2half_rn(v - __half2float(h));
+    hi = __half_as_ushort(h);
+    lo = __half_as_ushort(l);
+}
+
+// ------------------------------------------------------------------ x staging
+// Copies x (M, K) with row stride ldx into a dense, zero-padded (M, Kp) buffer
+// (Kp = 32*n_cb) when the rows cannot be fetched by 16-byte bulk copies as they are.
 __global__ void __launch_bounds__(256)
-xprep_kernel(const __half* __restrict__ x, int M, int K, long ldx, const float* __restrict__ bases,
-             const float* __restrict__ scales, int n_cb, uint8_t* __restrict__ table) {
+xpad_kernel(const __half* __restrict__ x, int M, int K, long ldx, int Kp, __half* __restrict__ out) {
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    int kb = blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (kb >= n_cb) return;
-    int lane = threadIdx.x & 31, m = lane >> 2, t = lane & 3;
-    float xv[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) xv[i] = 0.0f;
-    __align__(16) __half xh[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) xh[i] = __float2half_rn(0.0f);
-    if (m < M) {
-        long k0 = (long)kb * 32 + t * 8;
-        const __half* src = x + (long)m * ldx + k0;
-        if (k0 + 8 <= K && ((reinterpret_cast<uintptr_t>(src) & 15) == 0)) {
-            *reinterpret_cast<uint4*>(xh) = *reinterpret_cast<const uint4*>(src);
-        } else {
-            for (int i = 0; i < 8; i++)
-                if (k0 + i < K) xh[i] = src[i];
-        }
-#pragma unroll
-        for (int i = 0; i < 8; i++) xv[i] = __half2float(xh[i]);
-    }
-    const float4* b0p = reinterpret_cast<const float4*>(bases + (long)kb * 64 + t * 8);
-    const float4* b1p = reinterpret_cast<const float4*>(bases + (long)kb * 64 + 32 + t * 8);
-    float4 b0a = b0p[0], b0b = b0p[1], b1a = b1p[0], b1b = b1p[1];
-    float bb0[8] = {b0a.x, b0a.y, b0a.z, b0a.w, b0b.x, b0b.y, b0b.z, b0b.w};
-    float bb1[8] = {b1a.x, b1a.y, b1a.z, b1a.w, b1b.x, b1b.y, b1b.z, b1b.w};
-    float sx = 0.f, z0 = 0.f, z1 = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        sx += xv[i];
-        z0 = fmaf(xv[i], bb0[i], z0);
-        z1 = fmaf(xv[i], bb1[i], z1);
-    }
-#pragma unroll
-    for (int off = 1; off <= 2; off <<= 1) {
-        sx += __shfl_xor_sync(0xFFFFFFFFu, sx, off);
-        z0 += __shfl_xor_sync(0xFFFFFFFFu, z0, off);
-        z1 += __shfl_xor_sync(0xFFFFFFFFu, z1, off);
-    }
-    if (m >= M) return;
-    z0 = scales[kb * 2 + 0] * z0 * 1024.0f;
-    z1 = scales[kb * 2 + 1] * z1 * 1024.0f;
-    uint8_t* tk = table + (long)kb * TAB_KB;
-    uint4 xp;
-    const uint16_t* xb = reinterpret_cast<const uint16_t*>(xh);
-    xp.x = (uint32_t)xb[0] | ((uint32_t)xb[4] << 16);
-    xp.y = (uint32_t)xb[1] | ((uint32_t)xb[5] << 16);
-    xp.z = (uint32_t)xb[2] | ((uint32_t)xb[6] << 16);
-    xp.w = (uint32_t)xb[3] | ((uint32_t)xb[7] << 16);
-    *reinterpret_cast<uint4*>(tk + m * 64 + t * 16) = xp;
-    uint32_t s0 = split_hilo(z0), s1 = split_hilo(z1);
-    uint32_t dword;
-    if (t == 0) dword = split_hilo(sx);
-    else if (t == 1) dword = (s0 & 0xFFFFu) | (s1 << 16);
-    else if (t == 2) dword = (s0 >> 16) | (s1 & 0xFFFF0000u);
-    else dword = 0u;
-    *reinterpret_cast<uint32_t*>(tk + TAB_X + m * 16 + t * 4) = dword;
+    long i = (long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= (long)M * Kp) return;
+    int m = (int)(i / Kp), k = (int)(i - (long)m * Kp);
+    out[i] = (k < K) ? x[(long)m * ldx + k] : __float2half_rn(0.0f);
 }
 
 // ------------------------------------------------------------------ main kernel
 struct GemvParams {
-    const uint8_t* hdr;
-    const uint8_t* levels;
-    const uint8_t* table;
+    const uint8_t* blob;   // T16
+    const __half* x;       // (M, >= 32*n_cb), rows 16-byte aligned
+    const float* bases;
+    const float* scales;
     float* y;
-    int N, n_cb, M, split;
+    long ldx;
+    int N, n_cb, M, split, n_tiles, groups;
 };
 
-template <int HDR, int TN>
+template <int NT, int KB_S, int STAGES>
 struct GemvCfg {
-    static constexpr int NG = TN / 16;                 // 16-column groups per CTA
-    static constexpr int KS = kConsumerWarps / NG;     // warps sharing a group split the kb rows
-    static constexpr int LV_ROW = TN * 24, HD_ROW = TN * HDR;
-    static constexpr int STAGE = KB_S * (LV_ROW + HD_ROW + TAB_KB);
-    static constexpr int STAGES = (TN >= 128) ? 3 : 5;
-    static constexpr int OFF_LV = 0, OFF_HD = KB_S * LV_ROW, OFF_TX = OFF_HD + KB_S * HD_ROW,
-                         OFF_TD = OFF_TX + KB_S * TAB_X;
+    static constexpr int KS = kConsumerWarps / NT;        // warps sharing a tile split the kb rows
+    static constexpr int XROW = KB_S * 64 + 64;           // padded: conflict-free 128-bit x reads
+    static constexpr int OFF_X = NT * KB_S * T16_UNIT;
+    static constexpr int STAGE = OFF_X + 8 * XROW;
     static constexpr int RED_BYTES = kConsumerWarps * 32 * 16;
-    static constexpr int SMEM = STAGES * STAGE + RED_BYTES + 2 * STAGES * 8 + 16;
+    static constexpr int FIXED = STAGES * STAGE + RED_BYTES + 2 * STAGES * 8 + 16;
+    static int smem_bytes(int kb_per_cta) { return FIXED + kb_per_cta * DT_KB; }
 };
 
-// Expand one sub-block (8 six-bit levels) into 4 half2 registers holding
-// mult*level + 63*off for weights (p, p+4), p = 0..3.
-__device__ __forceinline__ void build_frags(uint32_t hi4, uint32_t lo2, uint32_t m2, uint32_t add2,
-                                            uint32_t (&f)[4]) {
-    uint32_t L = __byte_perm(lo2, 0u, 0x4140u);  // lo byte 0 at [7:0], lo byte 1 at [23:16]
-#pragma unroll
-    for (int p = 0; p < 4; p++) {
-        uint32_t a = (p == 0) ? (hi4 << 2) : (hi4 >> (4 * p - 2));
-        uint32_t b = L >> (2 * (3 - p));
-        uint32_t r = (a & 0x003C003Cu) | 0x64006400u;  // 1024 + (nibble << 2)
-        r |= (b & 0x00030003u);                         // + low two bits
-        f[p] = hfma2_u32(r, m2, add2);                  // (1024+lv)*mult + (63*off - 1024*mult), exact
-    }
-}
-
-struct ColOps {
-    uint32_t m2, add2, adir;
-    float base;
-};
-__device__ __forceinline__ ColOps col_ops(uint32_t h0, uint32_t h1, uint32_t h2, int t) {
-    ColOps c;
-    uint32_t s = (h2 >> (2 * t)) & 3u;
-    uint32_t sel = s * 0x2222u + 0x1010u;
-    c.m2 = __byte_perm(0x3C004400u, 0x40003C00u, sel);    // mult  = 4, 1, 1, 2
-    c.add2 = __byte_perm(0xE400EC00u, 0xE7C1E286u, sel);  // 63*off - 1024*mult = -4096,-1024,-835,-1985
-    uint32_t co = h2 >> 8;
-    uint32_t r = ((co * 0x1001u) & 0x000F000Fu) ^ 0x64086408u;  // 1024 + (c + 8) for both nibbles
-    uint32_t cc2 = hfma2_u32(r, 0x14001400u, 0xBC08BC08u);      // * 2^-10 - 1032 * 2^-10 = c * 2^-10
-    c.adir = (t == 0) ? (h0 * 0x10001u) : cc2;                  // {lo,lo} | {c0,c1} * 2^-10
-    float lo_f = h2f_bits((uint16_t)h0), hi_f = h2f_bits((uint16_t)h1);
-    c.base = (hi_f - lo_f) * (0.25f * 0.015873f);
-    return c;
-}
-
-template <int HDR, int TN>
-__global__ void __launch_bounds__(kThreads) gemv_kernel(GemvParams p) {
-    using C = GemvCfg<HDR, TN>;
+template <int NT, int KB_S, int STAGES>
+__global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
+    using C = GemvCfg<NT, KB_S, STAGES>;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
-    const uint32_t red = sbase + C::STAGES * C::STAGE;
+    const uint32_t red = sbase + STAGES * C::STAGE;
     const uint32_t bar_full = red + C::RED_BYTES;
-    const uint32_t bar_empty = bar_full + C::STAGES * 8;
+    const uint32_t bar_empty = bar_full + STAGES * 8;
+    const uint32_t dtab = bar_empty + STAGES * 8 + 16;
 
     asm volatile("griddepcontrol.launch_dependents;");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * TN;
-    const int ncols = min(TN, p.N - n0);
     const int rank = blockIdx.y;
     const int kb_per = (p.n_cb + p.split - 1) / p.split;
     const int kb_begin = min(p.n_cb, rank * kb_per);
     const int kb_end = min(p.n_cb, kb_begin + kb_per);
     const int n_iter = (kb_end - kb_begin + KB_S - 1) / KB_S;
+    const int my_groups = ((int)blockIdx.x < p.groups) ? (p.groups - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const int total_iters = my_groups * n_iter;
+    constexpr bool kDirectStore = (C::KS == 1);   // with split == 1 a warp owns its tile for all of K
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::STAGES; s++) {
+        for (int s = 0; s < STAGES; s++) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, kConsumerWarps);
         }
@@ -285,101 +201,199 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(GemvParams p) {
     float accF[4] = {0.f, 0.f, 0.f, 0.f}, accD[4] = {0.f, 0.f, 0.f, 0.f};
 
     if (warp == kConsumerWarps) {
-        // ------------------------------------------------ producer (one thread)
-        if (lane == 0) {
-            const uint32_t lv_bytes = (uint32_t)ncols * 24u, hd_bytes = (uint32_t)ncols * HDR;
-            const uint32_t tx_bytes = (uint32_t)p.M * 64u, td_bytes = (uint32_t)p.M * 16u;
-            bool ok = true;
-            auto issue_weights = [&](int it) {
-                int s = it % C::STAGES;
-                int kb0 = kb_begin + it * KB_S;
-                int rows = min(KB_S, kb_end - kb0);
-                uint32_t st = sbase + s * C::STAGE, bar = bar_full + 8 * s;
-                mbar_expect_tx(bar, (uint32_t)rows * (lv_bytes + hd_bytes + tx_bytes + td_bytes));
-                for (int r = 0; r < rows; r++) {
-                    long bid = (long)(kb0 + r) * p.N + n0;
-                    bulk_g2s(st + C::OFF_LV + r * C::LV_ROW, p.levels + bid * 24, lv_bytes, bar);
-                    bulk_g2s(st + C::OFF_HD + r * C::HD_ROW, p.hdr + bid * HDR, hd_bytes, bar);
-                }
-            };
-            auto issue_tables = [&](int it) {
-                int s = it % C::STAGES;
-                int kb0 = kb_begin + it * KB_S;
-                int rows = min(KB_S, kb_end - kb0);
-                uint32_t st = sbase + s * C::STAGE, bar = bar_full + 8 * s;
-                for (int r = 0; r < rows; r++) {
-                    const uint8_t* tk = p.table + (long)(kb0 + r) * TAB_KB;
-                    bulk_g2s(st + C::OFF_TX + r * TAB_X, tk, tx_bytes, bar);
-                    bulk_g2s(st + C::OFF_TD + r * TAB_D, tk + TAB_X, td_bytes, bar);
-                }
-            };
-            // Weights do not depend on the preceding kernel: start streaming them
-            // before waiting for it (programmatic dependent launch).
-            int pre = min(n_iter, C::STAGES);
-            for (int it = 0; it < pre; it++) issue_weights(it);
-            asm volatile("griddepcontrol.wait;" ::: "memory");
-            for (int it = 0; it < pre; it++) issue_tables(it);
-            for (int it = pre; it < n_iter; it++) {
-                int s = it % C::STAGES;
-                if (ok) ok = mbar_wait(bar_empty + 8 * s, ((it / C::STAGES) - 1) & 1, 1u);
-                issue_weights(it);
-                issue_tables(it);
-            }
+        // ---------------------------------------------- producer warp: lane i < NT copies
+        // the slab of tile i, lane 8+m the slice of activation row m.
+        auto coords = [&](int it, int& grp, int& kb0, int& rows) {
+            int gi = it / n_iter, j = it - gi * n_iter;
+            grp = (int)blockIdx.x + gi * (int)gridDim.x;
+            kb0 = kb_begin + j * KB_S;
+            rows = min(KB_S, kb_end - kb0);
+        };
+        auto arm = [&](int it) {   // lane 0: announce the bytes of stage `it`
+            int grp, kb0, rows;
+            coords(it, grp, kb0, rows);
+            int tiles = min(NT, p.n_tiles - grp * NT);
+            mbar_expect_tx(bar_full + 8 * (it % STAGES),
+                           (uint32_t)rows * ((uint32_t)tiles * T16_UNIT + (uint32_t)p.M * 64u));
+        };
+        auto issue_w = [&](int it) {
+            int grp, kb0, rows;
+            coords(it, grp, kb0, rows);
+            int s = it % STAGES;
+            long T = (long)grp * NT + lane;
+            if (lane < NT && T < p.n_tiles)
+                bulk_g2s(sbase + s * C::STAGE + lane * (KB_S * T16_UNIT),
+                         p.blob + (T * p.n_cb + kb0) * T16_UNIT, (uint32_t)rows * T16_UNIT, bar_full + 8 * s);
+        };
+        auto issue_x = [&](int it) {
+            int grp, kb0, rows;
+            coords(it, grp, kb0, rows);
+            int s = it % STAGES;
+            int m = lane - 8;
+            if (m >= 0 && m < p.M)
+                bulk_g2s(sbase + s * C::STAGE + C::OFF_X + m * C::XROW, p.x + (long)m * p.ldx + (long)kb0 * 32,
+                         (uint32_t)rows * 64u, bar_full + 8 * s);
+        };
+        bool ok = true;
+        // Weights do not depend on the preceding kernel: request them before waiting
+        // for it (programmatic dependent launch); activations after.
+        const int pre = min(total_iters, STAGES);
+        for (int it = 0; it < pre; it++) {
+            if (lane == 0) arm(it);
+            __syncwarp();
+            issue_w(it);
+        }
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        for (int it = 0; it < pre; it++) issue_x(it);
+        for (int it = pre; it < total_iters; it++) {
+            int s = it % STAGES;
+            if (ok) ok = mbar_wait(bar_empty + 8 * s, ((it / STAGES) - 1) & 1, 1u);
+            if (lane == 0) arm(it);
+            __syncwarp();
+            issue_w(it);
+            issue_x(it);
         }
     } else {
-        // ------------------------------------------------ consumers
-        const int grp = warp % C::NG, kpart = warp / C::NG;
+        // ---------------------------------------------- consumers
+        const int ti = warp % NT, kpart = warp / NT;
         const int g = lane >> 2, t = lane & 3;
         const bool row_ok = g < p.M;
-        const uint32_t colA = (uint32_t)(grp * 16 + g);
-        bool ok = true;
-        // From here on every wait is for data already requested, so the poll bound
-        // measures pipeline health, not the length of the preceding kernel.
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        for (int it = 0; it < n_iter; it++) {
-            int s = it % C::STAGES;
-            if (ok) ok = mbar_wait(bar_full + 8 * s, (it / C::STAGES) & 1, 2u);
-            int rows = min(KB_S, kb_end - (kb_begin + it * KB_S));
-            uint32_t st = sbase + s * C::STAGE;
-            for (int r = kpart; r < rows; r += C::KS) {
-                uint32_t lvA = st + C::OFF_LV + r * C::LV_ROW + colA * 24, lvB = lvA + 8 * 24;
-                uint32_t hdA = st + C::OFF_HD + r * C::HD_ROW + colA * HDR, hdB = hdA + 8 * HDR;
-                uint32_t hi4A = lds32(lvA + 4 * t), lo2A = lds16(lvA + 16 + 2 * t);
-                uint32_t hi4B = lds32(lvB + 4 * t), lo2B = lds16(lvB + 16 + 2 * t);
-                uint32_t a0 = lds16(hdA), a1 = lds16(hdA + 2), a2 = lds16(hdA + 4);
-                uint32_t b0 = lds16(hdB), b1 = lds16(hdB + 2), b2 = lds16(hdB + 4);
-                uint4 xq = make_uint4(0u, 0u, 0u, 0u);
-                uint32_t dq = 0u;
-                if (row_ok) {
-                    xq = lds128(st + C::OFF_TX + r * TAB_X + g * 64 + t * 16);
-                    dq = lds32(st + C::OFF_TD + r * TAB_D + g * 16 + t * 4);
-                }
-                ColOps ca = col_ops(a0, a1, a2, t), cb = col_ops(b0, b1, b2, t);
-                uint32_t fa[4], fb[4];
-                build_frags(hi4A, lo2A, ca.m2, ca.add2, fa);
-                build_frags(hi4B, lo2B, cb.m2, cb.add2, fb);
-                float d[4] = {0.f, 0.f, 0.f, 0.f};
-                mma16816(d, fa[0], fb[0], fa[1], fb[1], xq.x, xq.y);
-                mma16816(d, fa[2], fb[2], fa[3], fb[3], xq.z, xq.w);
-                mma1688(accD, ca.adir, cb.adir, dq);
-                accF[0] = fmaf(ca.base, d[0], accF[0]);
-                accF[1] = fmaf(ca.base, d[1], accF[1]);
-                accF[2] = fmaf(cb.base, d[2], accF[2]);
-                accF[3] = fmaf(cb.base, d[3], accF[3]);
+
+        // ---- activation-side table for kb_begin..kb_end: one warp per kb, lane = (m = g, t).
+        //   word[m][t]: t=0 {SxB_hi, SxB_lo}; t=1 {Z0_hi, Z1_hi}; t=2 {Z0_lo, Z1_lo}; t=3 0,
+        //   with Zj (ref cuda/sx8_decode1_v3.cu:44-65) pre-multiplied by 1024.
+        for (int kb = kb_begin + warp; kb < kb_end; kb += kConsumerWarps) {
+            float xv[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) xv[i] = 0.f;
+            if (row_ok) {
+                uint4 raw = *reinterpret_cast<const uint4*>(p.x + (long)g * p.ldx + (long)kb * 32 + t * 8);
+                const __half* hh = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+                for (int i = 0; i < 8; i++) xv[i] = __half2float(hh[i]);
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+            const float4* b0p = reinterpret_cast<const float4*>(p.bases + (long)kb * 64 + t * 8);
+            const float4* b1p = reinterpret_cast<const float4*>(p.bases + (long)kb * 64 + 32 + t * 8);
+            float4 b0a = b0p[0], b0b = b0p[1], b1a = b1p[0], b1b = b1p[1];
+            float bb0[8] = {b0a.x, b0a.y, b0a.z, b0a.w, b0b.x, b0b.y, b0b.z, b0b.w};
+            float bb1[8] = {b1a.x, b1a.y, b1a.z, b1a.w, b1b.x, b1b.y, b1b.z, b1b.w};
+            float sx = 0.f, z0 = 0.f, z1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                sx += xv[i];
+                z0 = fmaf(xv[i], bb0[i], z0);
+                z1 = fmaf(xv[i], bb1[i], z1);
+            }
+#pragma unroll
+            for (int off = 1; off <= 2; off <<= 1) {
+                sx += __shfl_xor_sync(0xFFFFFFFFu, sx, off);
+                z0 += __shfl_xor_sync(0xFFFFFFFFu, z0, off);
+                z1 += __shfl_xor_sync(0xFFFFFFFFu, z1, off);
+            }
+            z0 = p.scales[kb * 2 + 0] * z0 * 1024.0f;
+            z1 = p.scales[kb * 2 + 1] * z1 * 1024.0f;
+            uint32_t sh, sl, z0h, z0l, z1h, z1l;
+            split_hilo(sx, sh, sl);
+            split_hilo(z0, z0h, z0l);
+            split_hilo(z1, z1h, z1l);
+            uint32_t word = (t == 0) ? (sh | (sl << 16))
+                          : (t == 1) ? (z0h | (z1h << 16))
+                          : (t == 2) ? (z0l | (z1l << 16)) : 0u;
+            sts32(dtab + (kb - kb_begin) * DT_KB + lane * 4, row_ok ? word : 0u);
         }
-        // fold the two accumulators and park the warp's partial in shared memory
-        float4 v = make_float4(accF[0] + accD[0], accF[1] + accD[1], accF[2] + accD[2], accF[3] + accD[3]);
-        asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(red + (warp * 32 + lane) * 16), "f"(v.x),
-                     "f"(v.y), "f"(v.z), "f"(v.w)
-                     : "memory");
+        consumer_bar();
+
+        const uint32_t maskT0 = (t == 0) ? 0xFFFFFFFFu : 0u;
+        const uint32_t sh2 = 2u * (uint32_t)t;
+        bool ok = true;
+        int it = 0;
+        for (int gi = 0; gi < my_groups; gi++) {
+            const int grp = (int)blockIdx.x + gi * (int)gridDim.x;
+            for (int j = 0; j < n_iter; j++, it++) {
+                int s = it % STAGES;
+                if (ok) ok = mbar_wait(bar_full + 8 * s, (it / STAGES) & 1, 2u);
+                int rows = min(KB_S, kb_end - (kb_begin + j * KB_S));
+                uint32_t st = sbase + s * C::STAGE;
+                for (int r = kpart; r < rows; r += C::KS) {
+                    uint32_t unit = st + (ti * KB_S + r) * T16_UNIT;
+                    uint32_t W0 = lds32(unit + lane * 4), W1 = lds32(unit + 128 + lane * 4),
+                             W2 = lds32(unit + 256 + lane * 4);
+                    uint32_t H0 = lds32(unit + 384 + g * 4), H1 = lds32(unit + 416 + g * 4),
+                             H2 = lds32(unit + 448 + g * 4);
+                    uint4 xq = make_uint4(0u, 0u, 0u, 0u);
+                    if (row_ok) xq = lds128(st + C::OFF_X + g * C::XROW + r * 64 + t * 16);
+                    uint32_t dv = lds32(dtab + (j * KB_S + r) * DT_KB + lane * 4);
+
+                    // per sub-block constants looked up by range strategy:
+                    //   mult * 2^8  = 1024, 256, 256, 512     63*off * 2^-14 = 0, 0, 189*2^-14, 63*2^-14
+                    uint32_t u = (H2 >> sh2) & 0x00030003u;
+                    uint32_t sel = u * 0x2222u + 0x10101010u;
+                    uint32_t selB = sel >> 16;
+                    uint32_t mA = __byte_perm(0x5C006400u, 0x60005C00u, sel);
+                    uint32_t aA = __byte_perm(0x00000000u, 0x1BE021E8u, sel);
+                    uint32_t mB = __byte_perm(0x5C006400u, 0x60005C00u, selB);
+                    uint32_t aB = __byte_perm(0x00000000u, 0x1BE021E8u, selB);
+                    // bytes hold level << 2; read as fp16 bit patterns they are level * 2^-22, so
+                    // fma gives (mult*level + 63*off) * 2^-14, exact
+                    uint32_t V3 = ((W0 << 2) & 0x0C0C0C0Cu) | ((W1 << 4) & 0x30303030u) | ((W2 << 6) & 0xC0C0C0C0u);
+                    uint32_t fa0 = hfma2_u32(W0 & 0x00FC00FCu, mA, aA);
+                    uint32_t fa1 = hfma2_u32((W0 >> 8) & 0x00FC00FCu, mA, aA);
+                    uint32_t fa2 = hfma2_u32(W1 & 0x00FC00FCu, mA, aA);
+                    uint32_t fa3 = hfma2_u32((W1 >> 8) & 0x00FC00FCu, mA, aA);
+                    uint32_t fb0 = hfma2_u32(W2 & 0x00FC00FCu, mB, aB);
+                    uint32_t fb1 = hfma2_u32((W2 >> 8) & 0x00FC00FCu, mB, aB);
+                    uint32_t fb2 = hfma2_u32(V3 & 0x00FF00FFu, mB, aB);
+                    uint32_t fb3 = hfma2_u32((V3 >> 8) & 0x00FF00FFu, mB, aB);
+                    float d[4] = {0.f, 0.f, 0.f, 0.f};
+                    mma16816(d, fa0, fb0, fa1, fb1, xq.x, xq.y);
+                    mma16816(d, fa2, fb2, fa3, fb3, xq.z, xq.w);
+                    // direct terms: {lo,lo} x {SxB_hi,SxB_lo} on lane t=0; {c0,c1}*2^-10 x 1024*Z on t=1,2
+                    uint32_t rA = ((__byte_perm(H2, 0u, 0x4441u) * 0x1001u) & 0x000F000Fu) ^ 0x64086408u;
+                    uint32_t rB = (((H2 >> 24) * 0x1001u) & 0x000F000Fu) ^ 0x64086408u;
+                    uint32_t ccA = hfma2_u32(rA, 0x14001400u, 0xBC08BC08u);
+                    uint32_t ccB = hfma2_u32(rB, 0x14001400u, 0xBC08BC08u);
+                    uint32_t dA = (__byte_perm(H0, 0u, 0x1010u) & maskT0) | (ccA & ~maskT0);
+                    uint32_t dB = (__byte_perm(H1, 0u, 0x1010u) & maskT0) | (ccB & ~maskT0);
+                    mma1688(accD, dA, dB, dv);
+                    const float kBase = 0.25f * 0.015873f * 16384.0f;
+                    float baseA = (h2f_bits((uint16_t)(H0 >> 16)) - h2f_bits((uint16_t)H0)) * kBase;
+                    float baseB = (h2f_bits((uint16_t)(H1 >> 16)) - h2f_bits((uint16_t)H1)) * kBase;
+                    accF[0] = fmaf(baseA, d[0], accF[0]);
+                    accF[1] = fmaf(baseA, d[1], accF[1]);
+                    accF[2] = fmaf(baseB, d[2], accF[2]);
+                    accF[3] = fmaf(baseB, d[3], accF[3]);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+            }
+            if (kDirectStore && p.split == 1) {
+                int nA = (grp * NT + ti) * 16 + g, nB = nA + 8, m0 = 2 * t, m1 = m0 + 1;
+                float v0 = accF[0] + accD[0], v1 = accF[1] + accD[1], v2 = accF[2] + accD[2], v3 = accF[3] + accD[3];
+                if (nA < p.N) {
+                    if (m0 < p.M) p.y[(long)m0 * p.N + nA] = v0;
+                    if (m1 < p.M) p.y[(long)m1 * p.N + nA] = v1;
+                }
+                if (nB < p.N) {
+                    if (m0 < p.M) p.y[(long)m0 * p.N + nB] = v2;
+                    if (m1 < p.M) p.y[(long)m1 * p.N + nB] = v3;
+                }
+#pragma unroll
+                for (int i = 0; i < 4; i++) accF[i] = accD[i] = 0.f;
+            }
+        }
+        if (!(kDirectStore && p.split == 1)) {
+            float4 v = make_float4(accF[0] + accD[0], accF[1] + accD[1], accF[2] + accD[2], accF[3] + accD[3]);
+            asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(red + (warp * 32 + lane) * 16), "f"(v.x),
+                         "f"(v.y), "f"(v.z), "f"(v.w)
+                         : "memory");
+        }
     }
+    if (kDirectStore && p.split == 1) return;   // uniform over the whole grid
     __syncthreads();
 
-    // ---- reduce the KS kb-parts of each group, in fixed order, into slot kpart 0
-    if (warp < C::NG) {
+    // ---- reduce the KS kb-parts of each tile, in fixed order, into slot kpart 0
+    if (warp < NT) {
         uint32_t a = red + (warp * 32 + lane) * 16;
         float4 v;
         asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
@@ -387,7 +401,7 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(GemvParams p) {
             float4 u;
             asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
                          : "=f"(u.x), "=f"(u.y), "=f"(u.z), "=f"(u.w)
-                         : "r"(a + k * C::NG * 32 * 16));
+                         : "r"(a + k * NT * 32 * 16));
             v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
         }
         accF[0] = v.x; accF[1] = v.y; accF[2] = v.z; accF[3] = v.w;
@@ -396,7 +410,7 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(GemvParams p) {
     }
     if (p.split > 1) {
         cluster_sync_all();
-        if (rank == 0 && warp < C::NG) {
+        if (rank == 0 && warp < NT) {
             uint32_t a = red + (warp * 32 + lane) * 16;
             for (int rk = 1; rk < p.split; rk++) {
                 float4 u = ld_cluster_f4(a, (uint32_t)rk);
@@ -405,9 +419,9 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(GemvParams p) {
         }
         cluster_sync_all();  // peers keep their shared memory alive until rank 0 has read it
     }
-    if (rank == 0 && warp < C::NG) {
+    if (rank == 0 && warp < NT && (int)blockIdx.x < p.groups) {
         const int g = lane >> 2, t = lane & 3;
-        int nA = n0 + warp * 16 + g, nB = nA + 8;
+        int nA = ((int)blockIdx.x * NT + warp) * 16 + g, nB = nA + 8;
         int m0 = 2 * t, m1 = 2 * t + 1;
         if (nA < p.N) {
             if (m0 < p.M) p.y[(long)m0 * p.N + nA] = accF[0];
@@ -427,8 +441,10 @@ using namespace sx8;
 
 namespace {
 
+constexpr int kSMs = 148;
+
 struct Choice {
-    int tn, split;
+    int nt, split, grid_x;
 };
 
 int env_int(const char* name) {
@@ -436,38 +452,63 @@ int env_int(const char* name) {
     return v ? atoi(v) : 0;
 }
 
-// Tile width and cluster split: widest tile that still yields >= ~3 CTAs per SM,
-// then the smallest power-of-two split-K (<= 8, >= 8 kb per rank) that fills the GPU.
+// Tile-group width NT (x16 columns), cluster split-K and grid size.  Large N: 128-column
+// CTAs, no split, a persistent grid of 3 CTAs per SM that loops over tile groups.
+// Otherwise the (NT, split) whose CTA count fills whole multiples of the SM count best.
 Choice choose(int N, int n_cb) {
-    static const int force_tn = env_int("SX8_GEMV_TN"), force_split = env_int("SX8_GEMV_SPLIT");
-    Choice c;
-    c.tn = (N >= 148 * 128) ? 128 : ((N >= 74 * 64) ? 64 : 32);
-    if (force_tn == 32 || force_tn == 64 || force_tn == 128) c.tn = force_tn;
-    int tiles = (N + c.tn - 1) / c.tn;
-    int split_max = 1;
-    while (split_max < 8 && n_cb / (split_max * 2) >= 8) split_max *= 2;
-    c.split = 1;
-    while (c.split < split_max && tiles * c.split < 444) c.split *= 2;
-    if (force_split == 1 || force_split == 2 || force_split == 4 || force_split == 8) c.split = force_split;
-    return c;
+    static const int f_nt = env_int("SX8_GEMV_NT"), f_split = env_int("SX8_GEMV_SPLIT"),
+                     f_grid = env_int("SX8_GEMV_GRID");
+    const int n_tiles = (int)t16_tiles(N);
+    const int min_split = (n_cb + kMaxKbPerCta - 1) / kMaxKbPerCta;
+    Choice best{8, min_split, 0};
+    double best_score = -1.0;
+    const int nts[3] = {8, 4, 2};
+    for (int a = 0; a < 3; a++) {
+        int nt = nts[a];
+        if (f_nt && nt != f_nt) continue;
+        int groups = (n_tiles + nt - 1) / nt;
+        for (int split = min_split; split <= 8; split++) {
+            if (f_split && split != f_split) continue;
+            if (split > 1 && n_cb / split < 4) break;
+            long ctas = (long)groups * split;
+            double fill = (double)ctas / ((double)((ctas + kSMs - 1) / kSMs) * kSMs);
+            if (ctas > 4L * kSMs && !(nt == 8 && split == min_split)) fill *= 0.5;  // more than 4 waves of work units
+            if (nt == 8 && split == 1 && ctas >= 2 * kSMs) fill = 1.0;             // persistent grid: always balanced
+            double score = fill + 0.02 * nt - 0.015 * split;
+            if (ctas < kSMs) score -= 1.0;
+            if (score > best_score) {
+                best_score = score;
+                best = Choice{nt, split, 0};
+            }
+        }
+    }
+    int groups = (n_tiles + best.nt - 1) / best.nt;
+    best.grid_x = groups;
+    if (best.nt == 8 && best.split == 1) {
+        int cap = f_grid > 0 ? f_grid : 3 * kSMs;
+        if (groups > cap) best.grid_x = cap;
+    }
+    return best;
 }
 
-template <int HDR, int TN>
-int launch_gemv(const GemvParams& p, unsigned flags, cudaStream_t stream) {
-    using C = GemvCfg<HDR, TN>;
+template <int NT, int KB_S, int STAGES>
+int launch_gemv(const GemvParams& p, int grid_x, unsigned flags, cudaStream_t stream) {
+    using C = GemvCfg<NT, KB_S, STAGES>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        e = cudaFuncSetAttribute(gemv_kernel<HDR, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        e = cudaFuncSetAttribute(gemv_kernel<NT, KB_S, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 C::smem_bytes(kMaxKbPerCta));
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemv smem)");
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
+    int kb_per = (p.n_cb + p.split - 1) / p.split;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)((p.N + TN - 1) / TN), (unsigned)p.split, 1);
+    cfg.gridDim = dim3((unsigned)grid_x, (unsigned)p.split, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = C::SMEM;
+    cfg.dynamicSmemBytes = (size_t)C::smem_bytes(kb_per);
     cfg.stream = stream;
     cudaLaunchAttribute attrs[2];
     unsigned na = 0;
@@ -485,7 +526,7 @@ int launch_gemv(const GemvParams& p, unsigned flags, cudaStream_t stream) {
     }
     cfg.attrs = attrs;
     cfg.numAttrs = na;
-    e = cudaLaunchKernelEx(&cfg, gemv_kernel<HDR, TN>, p);
+    e = cudaLaunchKernelEx(&cfg, gemv_kernel<NT, KB_S, STAGES>, p);
     if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(gemv_kernel)");
     return SX8_OK;
 }
@@ -493,18 +534,22 @@ int launch_gemv(const GemvParams& p, unsigned flags, cudaStream_t stream) {
 }  // namespace
 
 extern "C" size_t sx8_gemv_workspace_bytes(int n_cb, int M) {
-    (void)M;
-    return n_cb > 0 ? (size_t)n_cb * TAB_KB : 0;
+    if (n_cb <= 0 || M <= 0) return 0;
+    size_t b = (size_t)(M > 8 ? 8 : M) * (size_t)n_cb * 64;   // staged activations (M, 32*n_cb) f16
+    return (b + 255) & ~(size_t)255;
 }
 
 namespace sx8 {
-// Shared by sx8_gemv and the chunked small-M path of sx8_gemm.
-int gemv_launch(const void* x, int M, int K, long ldx, const void* hdr, const void* levels,
-                const float* bases, const float* scales, int N, int n_cb, int hdr_bytes, float* y,
-                void* workspace, unsigned flags, cudaStream_t stream) {
-    {
+// Shared by sx8_gemv and the 8-row passes of sx8_gemm.  Arguments already validated.
+int gemv_launch(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
+                const float* scales, int N, int n_cb, float* y, void* workspace, unsigned flags,
+                cudaStream_t stream) {
+    const __half* xp = (const __half*)x;
+    long ld = ldx;
+    const int Kp = n_cb * 32;
+    if (K != Kp || (ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x) % 16) != 0) {
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)((n_cb + 7) / 8), 1, 1);
+        cfg.gridDim = dim3((unsigned)(((long)M * Kp + 255) / 256), 1, 1);
         cfg.blockDim = dim3(256, 1, 1);
         cfg.stream = stream;
         cudaLaunchAttribute attr;
@@ -512,33 +557,29 @@ int gemv_launch(const void* x, int M, int K, long ldx, const void* hdr, const vo
         attr.val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = &attr;
         cfg.numAttrs = (flags & SX8_F_PDL) ? 1 : 0;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, xprep_kernel, (const __half*)x, M, K, ldx, bases, scales, n_cb,
-                                           (uint8_t*)workspace);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(xprep_kernel)");
+        cudaError_t e = cudaLaunchKernelEx(&cfg, xpad_kernel, (const __half*)x, M, K, ldx, Kp, (__half*)workspace);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(xpad_kernel)");
+        xp = (const __half*)workspace;
+        ld = Kp;
     }
     Choice c = choose(N, n_cb);
-    GemvParams p{(const uint8_t*)hdr, (const uint8_t*)levels, (const uint8_t*)workspace, y, N, n_cb, M, c.split};
-    if (hdr_bytes == 6) {
-        if (c.tn == 128) return launch_gemv<6, 128>(p, flags, stream);
-        if (c.tn == 64) return launch_gemv<6, 64>(p, flags, stream);
-        return launch_gemv<6, 32>(p, flags, stream);
-    }
-    if (c.tn == 128) return launch_gemv<8, 128>(p, flags, stream);
-    if (c.tn == 64) return launch_gemv<8, 64>(p, flags, stream);
-    return launch_gemv<8, 32>(p, flags, stream);
+    const int n_tiles = (int)t16_tiles(N);
+    GemvParams p{(const uint8_t*)wt16, xp, bases, scales, y, ld, N, n_cb, M, c.split, n_tiles,
+                 (n_tiles + c.nt - 1) / c.nt};
+    if (c.nt == 8) return launch_gemv<8, 4, 3>(p, c.grid_x, flags, stream);
+    if (c.nt == 4) return launch_gemv<4, 8, 3>(p, c.grid_x, flags, stream);
+    return launch_gemv<2, 8, 4>(p, c.grid_x, flags, stream);
 }
 
-int gemv_check(const char* who, const void* x, int M, int Mmax, int K, long ldx, const void* hdr,
-               const void* levels, const float* bases, const float* scales, int N, int n_cb, int hdr_bytes,
-               const void* y) {
-    SX8_REQUIRE(x && hdr && levels && bases && scales && y, "%s: null pointer", who);
+int gemv_check(const char* who, const void* x, int M, int Mmax, int K, long ldx, const void* wt16,
+               const float* bases, const float* scales, int N, int n_cb, const void* y) {
+    SX8_REQUIRE(x && wt16 && bases && scales && y, "%s: null pointer", who);
     SX8_REQUIRE(M >= 1 && M <= Mmax, "%s: M must be in 1..%d (got %d)", who, Mmax, M);
-    SX8_REQUIRE(hdr_bytes == 6 || hdr_bytes == 8, "%s: hdr_bytes must be 6 or 8 (got %d)", who, hdr_bytes);
-    SX8_REQUIRE(N > 0 && N % 8 == 0, "%s: N must be a positive multiple of 8 (got %d)", who, N);
+    SX8_REQUIRE(N > 0, "%s: N must be positive (got %d)", who, N);
     SX8_REQUIRE(K > 0 && n_cb == (K + 31) / 32, "%s: need K>0 and n_cb == ceil(K/32) (got K=%d n_cb=%d)", who, K, n_cb);
+    SX8_REQUIRE(n_cb <= 8 * kMaxKbPerCta, "%s: K too large (n_cb=%d, limit %d)", who, n_cb, 8 * kMaxKbPerCta);
     SX8_REQUIRE(ldx >= K, "%s: ldx (%ld) < K (%d)", who, ldx, K);
-    SX8_REQUIRE((reinterpret_cast<uintptr_t>(hdr) % 16) == 0 && (reinterpret_cast<uintptr_t>(levels) % 16) == 0,
-                "%s: hdr and levels must be 16-byte aligned (TMA bulk copies)", who);
+    SX8_REQUIRE((reinterpret_cast<uintptr_t>(wt16) % 16) == 0, "%s: wt16 must be 16-byte aligned (TMA bulk copies)", who);
     SX8_REQUIRE((reinterpret_cast<uintptr_t>(bases) % 16) == 0 && (reinterpret_cast<uintptr_t>(x) % 2) == 0 &&
                     (reinterpret_cast<uintptr_t>(y) % 4) == 0,
                 "%s: misaligned x / bases / y", who);
@@ -546,11 +587,10 @@ int gemv_check(const char* who, const void* x, int M, int Mmax, int K, long ldx,
 }
 }  // namespace sx8
 
-extern "C" int sx8_gemv(const void* x, int M, int K, long ldx, const void* hdr, const void* levels,
-                        const float* bases, const float* scales, int N, int n_cb, int hdr_bytes, float* y,
-                        void* workspace, size_t workspace_bytes, unsigned flags, void* stream) {
-    int rc = gemv_check("sx8_gemv", x, M, SX8_GEMV_MAX_BATCH, K, ldx, hdr, levels, bases, scales, N, n_cb,
-                        hdr_bytes, y);
+extern "C" int sx8_gemv(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
+                        const float* scales, int N, int n_cb, float* y, void* workspace,
+                        size_t workspace_bytes, unsigned flags, void* stream) {
+    int rc = gemv_check("sx8_gemv", x, M, SX8_GEMV_MAX_BATCH, K, ldx, wt16, bases, scales, N, n_cb, y);
     if (rc != SX8_OK) return rc;
     if (!workspace || workspace_bytes < sx8_gemv_workspace_bytes(n_cb, M) ||
         (reinterpret_cast<uintptr_t>(workspace) % 256) != 0) {
@@ -558,6 +598,5 @@ extern "C" int sx8_gemv(const void* x, int M, int K, long ldx, const void* hdr, 
                   sx8_gemv_workspace_bytes(n_cb, M), workspace_bytes);
         return SX8_E_WORKSPACE;
     }
-    return gemv_launch(x, M, K, ldx, hdr, levels, bases, scales, N, n_cb, hdr_bytes, y, workspace, flags,
-                       (cudaStream_t)stream);
+    return gemv_launch(x, M, K, ldx, wt16, bases, scales, N, n_cb, y, workspace, flags, (cudaStream_t)stream);
 }

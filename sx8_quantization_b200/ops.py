@@ -36,8 +36,16 @@ class Workspace:
         return b
 
 
-def gemv(x, hdr, levels, bases, scales, N, K, n_cb, hdr_bytes=6, out=None, flags=0, workspace=None):
-    """y (M,N) f32 = x (M,K) f16 times the packed matrix; M in 1..8."""
+def _wt(wt16, N, n_cb):
+    _need(wt16, torch.uint8, "wt16")
+    need = _lib.lib().sx8_t16_bytes(N, n_cb)
+    if wt16.numel() != need:
+        raise SX8Error("wt16 has %d bytes, the T16 layout of (N=%d, n_cb=%d) has %d" % (wt16.numel(), N, n_cb, need))
+    return wt16
+
+
+def gemv(x, wt16, bases, scales, N, K, n_cb, out=None, flags=0, workspace=None):
+    """y (M,N) f32 = x (M,K) f16 times the packed matrix (T16 blob); M in 1..8."""
     if x.dim() == 1:
         x = x.unsqueeze(0)
     if not x.is_cuda or x.dtype != torch.float16:
@@ -45,7 +53,7 @@ def gemv(x, hdr, levels, bases, scales, N, K, n_cb, hdr_bytes=6, out=None, flags
     if x.stride(1) != 1 or x.stride(0) < x.shape[1]:
         x = x.contiguous()
     M = x.shape[0]
-    _need(hdr, torch.uint8, "hdr"); _need(levels, torch.uint8, "levels")
+    _wt(wt16, N, n_cb)
     _need(bases, torch.float32, "bases"); _need(scales, torch.float32, "scales")
     if out is None:
         out = torch.empty((M, N), dtype=torch.float32, device=x.device)
@@ -57,18 +65,17 @@ def gemv(x, hdr, levels, bases, scales, N, K, n_cb, hdr_bytes=6, out=None, flags
     need = L.sx8_gemv_workspace_bytes(n_cb, M)
     ws = workspace if workspace is not None else Workspace.get(x.device, need)
     with torch.cuda.device(x.device):
-        rc = L.sx8_gemv(x.data_ptr(), M, K, x.stride(0), hdr.data_ptr(), levels.data_ptr(), bases.data_ptr(),
-                        scales.data_ptr(), N, n_cb, hdr_bytes, out.data_ptr(), ws.data_ptr(), ws.numel(),
-                        flags, _stream(x))
+        rc = L.sx8_gemv(x.data_ptr(), M, K, x.stride(0), wt16.data_ptr(), bases.data_ptr(), scales.data_ptr(),
+                        N, n_cb, out.data_ptr(), ws.data_ptr(), ws.numel(), flags, _stream(x))
     _lib.check(rc, "sx8_gemv")
     return out
 
 
-def gemm(x, hdr, levels, bases, scales, N, K, n_cb, hdr_bytes=6, out_dtype=torch.float32, out=None):
+def gemm(x, wt16, bases, scales, N, K, n_cb, out_dtype=torch.float32, out=None):
     """Y (M,N) = X (M,K) f16 times the packed matrix, any M >= 1; fp32 accumulate."""
     x = _need(x.contiguous(), torch.float16, "x")
     M = x.shape[0]
-    _need(hdr, torch.uint8, "hdr"); _need(levels, torch.uint8, "levels")
+    _wt(wt16, N, n_cb)
     _need(bases, torch.float32, "bases"); _need(scales, torch.float32, "scales")
     if out_dtype not in (torch.float32, torch.float16):
         raise SX8Error("out_dtype must be float32 or float16")
@@ -82,17 +89,18 @@ def gemm(x, hdr, levels, bases, scales, N, K, n_cb, hdr_bytes=6, out_dtype=torch
     need = L.sx8_gemm_workspace_bytes(M, N, n_cb)
     ws = Workspace.get(x.device, need, "gemm")
     with torch.cuda.device(x.device):
-        rc = L.sx8_gemm(x.data_ptr(), M, K, x.stride(0), hdr.data_ptr(), levels.data_ptr(), bases.data_ptr(),
-                        scales.data_ptr(), N, n_cb, hdr_bytes, out.data_ptr(), int(out_dtype == torch.float16),
-                        ws.data_ptr(), ws.numel(), _stream(x))
+        rc = L.sx8_gemm(x.data_ptr(), M, K, x.stride(0), wt16.data_ptr(), bases.data_ptr(), scales.data_ptr(),
+                        N, n_cb, out.data_ptr(), int(out_dtype == torch.float16), ws.data_ptr(), ws.numel(),
+                        _stream(x))
     _lib.check(rc, "sx8_gemm")
     return out
 
 
-def embed(ids, hdr, levels, bases, scales, K, N, n_cb, hdr_bytes=6, out=None):
+def embed(ids, wt16, bases, scales, K, N, n_cb, out=None):
     """out (T,K) f16 = decoded rows ids[t] (float32 reference arithmetic)."""
     ids = _need(ids.reshape(-1).to(torch.long).contiguous(), torch.long, "ids")
     T = ids.numel()
+    _wt(wt16, N, n_cb)
     if out is None:
         out = torch.empty((T, K), dtype=torch.float16, device=ids.device)
     else:
@@ -100,8 +108,8 @@ def embed(ids, hdr, levels, bases, scales, K, N, n_cb, hdr_bytes=6, out=None):
         if out.numel() < T * K:
             raise SX8Error("out too small")
     with torch.cuda.device(ids.device):
-        rc = _lib.lib().sx8_embed(ids.data_ptr(), T, hdr.data_ptr(), levels.data_ptr(), bases.data_ptr(),
-                                  scales.data_ptr(), K, N, n_cb, hdr_bytes, out.data_ptr(), _stream(ids))
+        rc = _lib.lib().sx8_embed(ids.data_ptr(), T, wt16.data_ptr(), bases.data_ptr(), scales.data_ptr(),
+                                  K, N, n_cb, out.data_ptr(), _stream(ids))
     _lib.check(rc, "sx8_embed")
     return out
 
@@ -117,12 +125,14 @@ def dequant_planes(dmin, dmax, config, coeff, hi, lo, bases, scales, out_f, in_f
     return out
 
 
-def dequant_v44(hdr, levels, bases, scales, out_f, in_f, n_cb, hdr_bytes=6, use_pca=True):
-    out = torch.empty((out_f, in_f), dtype=torch.float16, device=hdr.device)
-    with torch.cuda.device(hdr.device):
-        rc = _lib.lib().sx8_dequant_v44(hdr.data_ptr(), levels.data_ptr(), bases.data_ptr(), scales.data_ptr(),
-                                        out_f, in_f, n_cb, hdr_bytes, int(use_pca), out.data_ptr(), _stream(hdr))
-    _lib.check(rc, "sx8_dequant_v44")
+def dequant_t16(wt16, bases, scales, out_f, in_f, n_cb, use_pca=True):
+    """(out_f,in_f) f16 from the T16 device blob (float64 reference arithmetic)."""
+    _wt(wt16, out_f, n_cb)
+    out = torch.empty((out_f, in_f), dtype=torch.float16, device=wt16.device)
+    with torch.cuda.device(wt16.device):
+        rc = _lib.lib().sx8_dequant_t16(wt16.data_ptr(), bases.data_ptr(), scales.data_ptr(), out_f, in_f, n_cb,
+                                        int(use_pca), out.data_ptr(), _stream(wt16))
+    _lib.check(rc, "sx8_dequant_t16")
     return out
 
 
@@ -153,6 +163,18 @@ def quantize_blocks(w, want_levels=False):
     if lv is not None:
         out["levels"] = lv
     return out
+
+
+def repack_t16(dmin, dmax, config, coeff, hi, lo, out_f, n_cb):
+    """n-major file planes -> T16 device blob, (ceil(out_f/16)*n_cb, 480) u8."""
+    dev = hi.device
+    nbytes = _lib.lib().sx8_t16_bytes(out_f, n_cb)
+    blob = torch.empty((nbytes // 480, 480), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().sx8_repack_t16(dmin.data_ptr(), dmax.data_ptr(), config.data_ptr(), coeff.data_ptr(),
+                                       hi.data_ptr(), lo.data_ptr(), out_f, n_cb, blob.data_ptr(), _stream(hi))
+    _lib.check(rc, "sx8_repack_t16")
+    return blob
 
 
 def repack_v44(dmin, dmax, config, coeff, hi, lo, out_f, n_cb, hdr_bytes=6):

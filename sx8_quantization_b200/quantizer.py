@@ -11,7 +11,7 @@ device.  Mirrors the per-tensor loop body of the reference's quantizer script
      eigenvectors of E^T E, so the bases span the same subspace; their signs (and
      hence the coefficient signs) are arbitrary in both.  Functional parity only:
      neither implementation's coeff/bases bytes are reproducible across LAPACK builds;
-  3. kb-major device layout (sx8_repack_v44).
+  3. T16 device layout (sx8_repack_t16).
 
 `quantize_tensor` returns device tensors ready for the GEMV/GEMM/embed kernels;
 `to_host_dicts` converts to the reference's pkl/container dict format."""
@@ -57,10 +57,10 @@ def _pca_correct(w32, q, n_cb):
     return coeff, basis.reshape(n_cb, 64).contiguous(), scales.contiguous()
 
 
-def quantize_tensor(w, with_pca=True, hdr_bytes=6, keep_planes=False):
-    """w: (out_f, in_f) CUDA f16 or f32.  Returns a dict with the kb-major device layout
-    {hdr, levels, bases, scales, N, K, n_cb, hdr_bytes} and, with keep_planes, the
-    n-major file planes under "planes"."""
+def quantize_tensor(w, with_pca=True, keep_planes=False):
+    """w: (out_f, in_f) CUDA f16 or f32.  Returns a dict with the T16 device layout
+    {wt16, bases, scales, N, K, n_cb} and, with keep_planes, the n-major file planes
+    under "planes"."""
     out_f, in_f = w.shape
     q = ops.quantize_blocks(w, want_levels=with_pca)
     n_cb = q["n_cb"]
@@ -76,10 +76,8 @@ def quantize_tensor(w, with_pca=True, hdr_bytes=6, keep_planes=False):
         coeff = torch.zeros(out_f * n_cb, dtype=torch.uint8, device=dev)
         bases = torch.zeros(n_cb, 64, device=dev)
         scales = torch.zeros(n_cb, 2, device=dev)
-    hdr, lev = ops.repack_v44(q["dmin"], q["dmax"], q["config"], coeff, q["levels_hi"], q["levels_lo"],
-                              out_f, n_cb, hdr_bytes)
-    t = {"hdr": hdr, "levels": lev, "bases": bases, "scales": scales, "N": out_f, "K": in_f, "n_cb": n_cb,
-         "hdr_bytes": hdr_bytes}
+    wt16 = ops.repack_t16(q["dmin"], q["dmax"], q["config"], coeff, q["levels_hi"], q["levels_lo"], out_f, n_cb)
+    t = {"wt16": wt16, "bases": bases, "scales": scales, "N": out_f, "K": in_f, "n_cb": n_cb}
     if keep_planes:
         q["coeff"] = coeff
         t["planes"] = q

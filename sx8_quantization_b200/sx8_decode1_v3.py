@@ -8,8 +8,12 @@ libsx8b200.so instead of a JIT-compiled torch extension.
         -> (Y f32 (N,), tensors)
 
 Differences, all outside the numerical contract: the file planes are uploaded once and
-transposed to the kb-major layout by a device kernel (the reference transposes with
-numpy on the host, ref scripts/prepare_v44.py:35-79); X may also be (M, K) with
+permuted on the device into this library's T16 layout (the reference transposes with
+numpy on the host into its kb-major v4.4 pair, ref scripts/prepare_v44.py:35-79), so
+in the returned tuple `lvl_t` is the T16 blob and `hdr_t` a small descriptor
+[N, n_cb]; callers treat the tuple as opaque, as the reference's do; hdr_aligned /
+hdr_bytes=8 (the reference's padded-header experiment) are accepted and map to the same
+30-byte layout; X may also be (M, K) with
 M <= 8, in which case Y is (M, N); split_k is accepted and ignored exactly as the
 reference ignores it (ref cuda/sx8_decode1_v3.cu:206-218) -- the kernel picks its own
 deterministic cluster split."""
@@ -26,16 +30,17 @@ def _dev_u8(a, device):
 
 
 def make_tensors_v44(qt, bases_info, hdr_aligned=False, device=None):
-    """ref scripts/sx8_decode1_v3.py:57-66.  Returns CUDA tensors hdr (n_blk,6|8) u8,
-    levels (n_blk,24) u8, bases (n_cb,64) f32, scales (n_cb,2) f32, kb-major."""
+    """ref scripts/sx8_decode1_v3.py:57-66.  Returns (hdr_t, lvl_t, bas_t, sca_t):
+    hdr_t = int64 descriptor [N, n_cb] (host), lvl_t = T16 blob (units, 480) u8 CUDA,
+    bas_t (n_cb,64) f32, sca_t (n_cb,2) f32."""
     device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
     out_f, _ = qt["shape"]
     n_cb = int(qt["n_cb"])
     f16 = lambda a: _dev_u8(np.asarray(a).reshape(-1).astype(np.float16, copy=False), device)
     u8 = lambda a: _dev_u8(np.asarray(a).reshape(-1).astype(np.uint8, copy=False), device)
-    hdr_t, lvl_t = ops.repack_v44(f16(qt["dmin"]), f16(qt["dmax"]), u8(qt["config"]), u8(qt["coeff"]),
-                                  u8(qt["levels_hi"]), u8(qt["levels_lo"]), out_f, n_cb,
-                                  8 if hdr_aligned else 6)
+    lvl_t = ops.repack_t16(f16(qt["dmin"]), f16(qt["dmax"]), u8(qt["config"]), u8(qt["coeff"]),
+                           u8(qt["levels_hi"]), u8(qt["levels_lo"]), int(out_f), n_cb)
+    hdr_t = torch.tensor([int(out_f), n_cb], dtype=torch.int64)
     bas_t = torch.from_numpy(np.ascontiguousarray(np.asarray(bases_info["data"]).reshape(-1, 64),
                                                   dtype=np.float32)).to(device)
     sca_t = torch.from_numpy(np.ascontiguousarray(np.asarray(bases_info["scales"]).reshape(-1, 2),
@@ -68,7 +73,7 @@ def _buf(key, shape, device):
 def decode1_v44(X, qt, bases_info, hdr_t=None, lvl_t=None, bas_t=None, sca_t=None,
                 hdr_bytes=6, split_k=1):
     """ref scripts/sx8_decode1_v3.py:91-110."""
-    if hdr_t is None:
+    if lvl_t is None:
         hdr_t, lvl_t, bas_t, sca_t = make_tensors_v44(qt, bases_info, hdr_aligned=(hdr_bytes == 8),
                                                       device=X.device if X.is_cuda else None)
     n_cb = int(qt["n_cb"])
@@ -78,5 +83,5 @@ def decode1_v44(X, qt, bases_info, hdr_t=None, lvl_t=None, bas_t=None, sca_t=Non
     K = Xc.shape[-1]
     M = 1 if one_d else Xc.shape[0]
     Y = _buf(("Y", N, M), (M, N), Xc.device)
-    ops.gemv(Xc, hdr_t, lvl_t, bas_t, sca_t, N, K, n_cb, hdr_bytes, out=Y)
+    ops.gemv(Xc, lvl_t, bas_t, sca_t, N, min(K, n_cb * 32), n_cb, out=Y)
     return (Y[0] if one_d else Y), (hdr_t, lvl_t, bas_t, sca_t)

@@ -34,6 +34,5 @@ class SX8EmbeddingV44(nn.Module):
         if self._out is None or self._out.shape[0] < T:
             self._out = torch.empty(T, self.K, dtype=torch.float16, device=dev)
         out = self._out[:T]
-        ops.embed(ids, self._hdr, self._lvl, self._bas, self._sca, self.K, self.N, self.n_cb,
-                  self.hdr_bytes, out=out)
+        ops.embed(ids, self._lvl, self._bas, self._sca, self.K, self.N, self.n_cb, out=out)
         return out.reshape(*ids.shape, self.K)

@@ -7,7 +7,7 @@
 
 The reference keeps ten planar kb-major arrays per tensor (44 B/block more than the
 packed data, ref :69-87).  Here the dict carries the same keys for the planes the
-callers may look at, and the kernels run from the 30 B/block hdr/levels pair that is
+callers may look at, and the kernels run from the 30 B/block T16 blob that is
 assembled once, on the device, from those planes."""
 import numpy as np
 import torch
@@ -31,26 +31,26 @@ def make_tensors(qt_kbmajor, bases_info, device):
     return t
 
 
-def _v44(tensors):
-    v = tensors.get("_v44")
+def _t16(tensors, n_cb):
+    """Planar kb-major arrays (bid = kb*N + n) -> T16 blob, once per tensor, on the device."""
+    v = tensors.get("_t16")
     if v is None:
         n_blk = tensors["config"].numel()
-        hdr = torch.cat([tensors["dmin"].view(torch.uint8).reshape(n_blk, 2),
-                         tensors["dmax"].view(torch.uint8).reshape(n_blk, 2),
-                         tensors["config"].reshape(n_blk, 1), tensors["coeff"].reshape(n_blk, 1)], dim=1).contiguous()
-        lev = torch.cat([tensors["hi"].reshape(n_blk, 16), tensors["lo"].reshape(n_blk, 8)], dim=1).contiguous()
-        v = (hdr, lev, tensors["basis"].reshape(-1, 64), tensors["scales"].reshape(-1, 2))
-        tensors["_v44"] = v
+        N = n_blk // n_cb
+        nm = lambda a, per: a.reshape(n_cb, N, per).transpose(0, 1).contiguous().reshape(-1)
+        wt = ops.repack_t16(nm(tensors["dmin"].view(torch.uint8), 2), nm(tensors["dmax"].view(torch.uint8), 2),
+                            nm(tensors["config"], 1), nm(tensors["coeff"], 1), nm(tensors["hi"], 16),
+                            nm(tensors["lo"], 8), N, n_cb)
+        v = (wt, tensors["basis"].reshape(-1, 64), tensors["scales"].reshape(-1, 2), N)
+        tensors["_t16"] = v
     return v
 
 
 def gemm_sx8_wmma_cached(X, tensors, n_cb):
-    hdr, lev, bas, sca = _v44(tensors)
     n_cb = int(n_cb)
-    N = hdr.shape[0] // n_cb
+    wt, bas, sca, N = _t16(tensors, n_cb)
     Xc = X.contiguous().half()
-    return ops.gemm(Xc, hdr, lev, bas, sca, N, min(int(Xc.shape[1]), n_cb * 32), n_cb, 6,
-                    out_dtype=torch.float32)
+    return ops.gemm(Xc, wt, bas, sca, N, min(int(Xc.shape[1]), n_cb * 32), n_cb, out_dtype=torch.float32)
 
 
 def gemm_sx8_wmma(X, qt_kbmajor, bases_info, n_cb):
@@ -58,8 +58,7 @@ def gemm_sx8_wmma(X, qt_kbmajor, bases_info, n_cb):
 
 
 def decode1_sx8_cached(X, tensors, n_cb):
-    hdr, lev, bas, sca = _v44(tensors)
     n_cb = int(n_cb)
-    N = hdr.shape[0] // n_cb
+    wt, bas, sca, N = _t16(tensors, n_cb)
     Xc = X.contiguous().half().reshape(1, -1)
-    return ops.gemv(Xc, hdr, lev, bas, sca, N, min(int(Xc.shape[1]), n_cb * 32), n_cb, 6)[0]
+    return ops.gemv(Xc, wt, bas, sca, N, min(int(Xc.shape[1]), n_cb * 32), n_cb)[0]

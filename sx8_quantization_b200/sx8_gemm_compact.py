@@ -5,9 +5,8 @@
 
 X (M, K) f16 CUDA; K shorter than n_cb*32 is zero-extended inside the kernel (the
 reference pads X on the host, ref :66-71).  The reference decodes tensors with fewer
-than 64 rows to fp16 and calls a library matmul (ref :54-59); here every N that is a
-multiple of 8 runs on the fused kernel and only a ragged N takes the decode + matmul
-route (with this library's own decode kernel)."""
+than 64 rows to fp16 and calls a library matmul (ref :54-59); here every N runs on the
+fused kernels (the T16 layout pads the last 16-column tile with zero blocks)."""
 import torch
 
 from . import ops
@@ -20,13 +19,10 @@ def gemm_sx8_compact(X, qt, bases_info, hdr_t=None, lvl_t=None, bas_t=None, sca_
     if n_cb is None:
         n_cb = qt["n_cb"]
     out_f = int(qt["shape"][0])
-    if hdr_t is None:
+    if lvl_t is None:
         from .sx8_decode1_v3 import make_tensors_v44
         hdr_t, lvl_t, bas_t, sca_t = make_tensors_v44(qt, bases_info, hdr_aligned=(hdr_bytes == 8),
                                                       device=X.device)
     Xc = X.contiguous().half()
     K = min(int(Xc.shape[1]), int(n_cb) * 32)
-    if out_f % 8 != 0:
-        W = ops.dequant_v44(hdr_t, lvl_t, bas_t, sca_t, out_f, int(in_f), int(n_cb), hdr_bytes)
-        return torch.nn.functional.linear(Xc[:, :int(in_f)], W).float()
-    return ops.gemm(Xc, hdr_t, lvl_t, bas_t, sca_t, out_f, K, int(n_cb), hdr_bytes, out_dtype=torch.float32)
+    return ops.gemm(Xc, lvl_t, bas_t, sca_t, out_f, K, int(n_cb), out_dtype=torch.float32)

@@ -2,12 +2,13 @@
 exchange.  The reference has no multi-GPU code; this is the sharding its format
 implies:
 
-  column-parallel (q, k, v, gate, up, lm_head): shard the output rows N.  In the
-      kb-major layout a row shard is a strided slice per kb, re-materialised
-      contiguously per rank at load; bases/scales are replicated.
+  column-parallel (q, k, v, gate, up, lm_head): shard the output rows N in multiples
+      of 16.  The T16 blob is tile-major, so a row shard is one contiguous byte range;
+      bases/scales are replicated.
   row-parallel (o, down): shard K on 32-weight block boundaries.  A kb range is a
-      contiguous slice of hdr/levels and of bases/scales; every rank produces a partial
-      y (its own PCA term included) and the partials are summed with one all-reduce.
+      strided slice per tile, re-materialised contiguously per rank at load, together
+      with the matching rows of bases/scales; every rank produces a partial y (its own
+      PCA term included) and the partials are summed with one all-reduce.
 
 Tensors are quantised before slicing, so shards are byte-identical to slices of the
 single-GPU tensors (the PCA bases of a kb depend on all N rows)."""
@@ -34,21 +35,19 @@ def shard_tensor(t, style, rank, world):
         out = dict(t)
         out["style"] = style
         return out
-    N, K, n_cb, hb = t["N"], t["K"], t["n_cb"], t["hdr_bytes"]
-    hdr = t["hdr"].reshape(n_cb, N, hb)
-    lev = t["levels"].reshape(n_cb, N, 24)
+    N, K, n_cb = t["N"], t["K"], t["n_cb"]
+    blob = t["wt16"].reshape(-1, n_cb, 480)          # (tiles, kb, unit)
     if style == "col":
-        n0, n1 = shard_bounds(N, rank, world, 8)
-        return {"hdr": hdr[:, n0:n1].contiguous().reshape(-1, hb), "levels": lev[:, n0:n1].contiguous().reshape(-1, 24),
-                "bases": t["bases"], "scales": t["scales"], "N": n1 - n0, "K": K, "n_cb": n_cb, "hdr_bytes": hb,
-                "style": "col", "n_range": (n0, n1), "global": (N, K)}
+        n0, n1 = shard_bounds(N, rank, world, 16)
+        return {"wt16": blob[n0 // 16:n1 // 16].contiguous().reshape(-1, 480), "bases": t["bases"],
+                "scales": t["scales"], "N": n1 - n0, "K": K, "n_cb": n_cb, "style": "col", "n_range": (n0, n1),
+                "global": (N, K)}
     if style == "row":
         kb0, kb1 = shard_bounds(n_cb, rank, world, 1)
         k0, k1 = kb0 * 32, min(K, kb1 * 32)
-        return {"hdr": hdr[kb0:kb1].contiguous().reshape(-1, hb), "levels": lev[kb0:kb1].contiguous().reshape(-1, 24),
-                "bases": t["bases"][kb0:kb1].contiguous(), "scales": t["scales"][kb0:kb1].contiguous(),
-                "N": N, "K": k1 - k0, "n_cb": kb1 - kb0, "hdr_bytes": hb, "style": "row", "k_range": (k0, k1),
-                "global": (N, K)}
+        return {"wt16": blob[:, kb0:kb1].contiguous().reshape(-1, 480), "bases": t["bases"][kb0:kb1].contiguous(),
+                "scales": t["scales"][kb0:kb1].contiguous(), "N": N, "K": k1 - k0, "n_cb": kb1 - kb0,
+                "style": "row", "k_range": (k0, k1), "global": (N, K)}
     raise ops.SX8Error("unknown tensor-parallel style %r" % (style,))
 
 
@@ -58,11 +57,10 @@ def linear(x, t, out=None, flags=0, group=None, reduce=True):
     reduce=False.  M <= 8 runs the decode GEMV, larger M the GEMM."""
     M = x.shape[0]
     if M <= 8:
-        y = ops.gemv(x, t["hdr"], t["levels"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"], t["hdr_bytes"],
-                     out=out, flags=flags)
+        y = ops.gemv(x, t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"], out=out, flags=flags)
     else:
-        y = ops.gemm(x, t["hdr"], t["levels"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"], t["hdr_bytes"],
-                     out_dtype=torch.float32, out=out)
+        y = ops.gemm(x, t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"], out_dtype=torch.float32,
+                     out=out)
     if reduce and t.get("style") == "row" and torch.distributed.is_initialized() \
             and torch.distributed.get_world_size(group) > 1:
         torch.distributed.all_reduce(y, group=group)

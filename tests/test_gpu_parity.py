@@ -50,7 +50,13 @@ def planes_dev(qt):
 
 
 def v44_dev(v44):
+    """The reference's kb-major pair (only the reference's own kernels consume it)."""
     return dev(v44["hdr"]), dev(v44["levels"]), dev(v44["bases"]), dev(v44["scales"])
+
+
+def t16_dev(qt, v44):
+    """T16 blob built by the CPU oracle + bases/scales."""
+    return dev(orc.to_t16(qt)), dev(v44["bases"]), dev(v44["scales"])
 
 
 @pytest.fixture(scope="module")
@@ -74,6 +80,15 @@ def test_repack_bit_exact(ops, shape, aligned):
     assert np.array_equal(lev.cpu().numpy(), v44["levels"])
 
 
+@pytest.mark.parametrize("shape", [(8, 32), (40, 96), (48, 80), (136, 1000), (1024, 2560)])
+def test_repack_t16_bit_exact(ops, shape):
+    _, qt, bi, v44 = case(shape[0], shape[1], 31)
+    blob = ops.repack_t16(*planes_dev(qt), shape[0], qt["n_cb"])
+    ref = orc.to_t16(qt)
+    assert blob.numel() == ref.size == orc.t16_bytes(shape[0], qt["n_cb"])
+    assert np.array_equal(blob.cpu().numpy().reshape(-1), ref)
+
+
 @pytest.mark.parametrize("shape", [(48, 80), (64, 256), (136, 1000), (1024, 2560)])
 @pytest.mark.parametrize("use_pca", [True, False])
 def test_dequant_bit_exact(ops, shape, use_pca):
@@ -82,8 +97,8 @@ def test_dequant_bit_exact(ops, shape, use_pca):
     p = planes_dev(qt)
     got = ops.dequant_planes(*p, dev(v44["bases"]), dev(v44["scales"]), shape[0], shape[1], qt["n_cb"], use_pca)
     assert np.array_equal(got.cpu().numpy().view(np.uint16), ref.view(np.uint16))
-    h, l, b, s = v44_dev(v44)
-    got2 = ops.dequant_v44(h, l, b, s, shape[0], shape[1], qt["n_cb"], 6, use_pca)
+    wt, b, s = t16_dev(qt, v44)
+    got2 = ops.dequant_t16(wt, b, s, shape[0], shape[1], qt["n_cb"], use_pca)
     assert np.array_equal(got2.cpu().numpy().view(np.uint16), ref.view(np.uint16))
 
 
@@ -99,22 +114,21 @@ def test_dequant_golden_special_rows(ops, golden_dir):
 
 
 @pytest.mark.parametrize("shape", [(48, 80), (64, 256), (136, 1000), (1024, 2560)])
-@pytest.mark.parametrize("aligned", [False, True])
-def test_embed_bit_exact(ops, shape, aligned):
-    _, qt, bi, v44 = case(shape[0], shape[1], 33, aligned)
+def test_embed_bit_exact(ops, shape):
+    _, qt, bi, v44 = case(shape[0], shape[1], 33)
     rng = np.random.default_rng(5)
     ids = rng.integers(0, shape[0], 37)
     ref = orc.embed_d32(ids, v44, contract=True)
-    h, l, b, s = v44_dev(v44)
-    got = ops.embed(dev(ids), h, l, b, s, shape[1], shape[0], qt["n_cb"], 8 if aligned else 6)
+    wt, b, s = t16_dev(qt, v44)
+    got = ops.embed(dev(ids), wt, b, s, shape[1], shape[0], qt["n_cb"])
     assert np.array_equal(got.cpu().numpy().view(np.uint16), ref.view(np.uint16))
 
 
 def test_embed_out_of_range_ids_give_zero_rows(ops):
     _, qt, bi, v44 = case(64, 256, 33)
     ids = np.array([0, -1, 64, 63, 10 ** 9], dtype=np.int64)
-    h, l, b, s = v44_dev(v44)
-    got = ops.embed(dev(ids), h, l, b, s, 256, 64, qt["n_cb"]).cpu().numpy()
+    wt, b, s = t16_dev(qt, v44)
+    got = ops.embed(dev(ids), wt, b, s, 256, 64, qt["n_cb"]).cpu().numpy()
     ref = orc.embed_d32(ids, v44)
     assert np.array_equal(got.view(np.uint16), ref.view(np.uint16))
     assert not got[[1, 2, 4]].any()
@@ -133,7 +147,8 @@ def test_embed_vs_reference_kernel_build(ops):
     h, l, b, s = v44_dev(v44)
     out_ref = torch.zeros(64, 2560, dtype=torch.float16, device="cuda")
     ref_mod.sx8_embed_v44(ids, h, l, b, s, 2560, 1024, qt["n_cb"], out_ref)
-    got = ops.embed(ids, h, l, b, s, 2560, 1024, qt["n_cb"])
+    wt, _, _ = t16_dev(qt, v44)
+    got = ops.embed(ids, wt, b, s, 2560, 1024, qt["n_cb"])
     torch.cuda.synchronize()
     assert torch.equal(got.view(torch.int16), out_ref.view(torch.int16))
     cpu = orc.embed_d32(ids.cpu().numpy(), v44, contract=True)
@@ -190,6 +205,14 @@ def test_quantize_and_repack_golden_checksums(ops, name):
                               c["out_f"], q["n_cb"], 6)
     assert sha(hdr.cpu().numpy()) == c["hdr6"]
     assert sha(lev.cpu().numpy()) == c["levels44"]
+    # T16 is a permutation of the same bytes: decoding it back must give the same tensor
+    wt = ops.repack_t16(q["dmin"], q["dmax"], q["config"], coeff, q["levels_hi"], q["levels_lo"],
+                        c["out_f"], q["n_cb"])
+    z64 = torch.zeros(q["n_cb"], 64, device="cuda"); z2 = torch.zeros(q["n_cb"], 2, device="cuda")
+    a = ops.dequant_t16(wt, z64, z2, c["out_f"], c["in_f"], q["n_cb"], False)
+    b = ops.dequant_planes(q["dmin"], q["dmax"], q["config"], coeff, q["levels_hi"], q["levels_lo"], z64, z2,
+                           c["out_f"], c["in_f"], q["n_cb"], False)
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
 
 
 def _gemv_check(ops, shape, M, seed, aligned=False, xscale=1.0):
@@ -197,8 +220,8 @@ def _gemv_check(ops, shape, M, seed, aligned=False, xscale=1.0):
     x = orc.synth_x(M, shape[1], seed + 1000 + M, scale=xscale)
     y_cmp = orc.matmul_ref(x, orc.dequant_d64(qt, bi))
     y_krn = orc.gemv_d32(x, v44)
-    h, l, b, s = v44_dev(v44)
-    y = ops.gemv(dev(x), h, l, b, s, shape[0], shape[1], qt["n_cb"], 8 if aligned else 6).cpu().numpy()
+    wt, b, s = t16_dev(qt, v44)
+    y = ops.gemv(dev(x), wt, b, s, shape[0], shape[1], qt["n_cb"]).cpu().numpy()
     scale = np.abs(y_cmp).max()
     assert np.isfinite(y).all()
     assert np.abs(y - y_cmp).max() <= TOL_VS_COMPARATOR * scale
@@ -212,16 +235,13 @@ def test_gemv_batches(ops, M):
 
 
 @pytest.mark.parametrize("shape", [(8, 32), (48, 80), (136, 1000), (64, 256), (2560, 4096), (4096, 2560),
-                                   (4736, 512), (19008, 256), (2560, 9728)])
+                                   (4736, 512), (9728, 2560), (2560, 9728), (60, 64), (60000, 64)])
 def test_gemv_shapes(ops, shape):
-    """Covers every tile width (32/64/128 columns), ragged N tiles, K not a multiple of
-    32, one-block K, and every cluster split (1/2/4/8)."""
+    """Covers every tile-group width (32/64/128 columns), ragged last tiles and groups,
+    N not a multiple of 8, K not a multiple of 32 (staged activations), one-block K,
+    cluster splits, and the persistent no-split grid looping over tile groups (60000 columns)."""
     _gemv_check(ops, shape, 1, 52)
     _gemv_check(ops, shape, 8, 52)
-
-
-def test_gemv_hdr8_variant(ops):
-    _gemv_check(ops, (1024, 2560), 4, 53, aligned=True)
 
 
 @pytest.mark.parametrize("xscale", [0.02, 30.0])
@@ -242,20 +262,20 @@ def test_gemv_pdl_flag_and_graph(ops):
     """Programmatic dependent launch and CUDA-graph replay give the same bits."""
     w, qt, bi, v44 = case(1024, 2560, 56)
     x = dev(orc.synth_x(4, 2560, 7))
-    h, l, b, s = v44_dev(v44)
-    y0 = ops.gemv(x, h, l, b, s, 1024, 2560, qt["n_cb"]).clone()
-    y1 = ops.gemv(x, h, l, b, s, 1024, 2560, qt["n_cb"], flags=ops.SX8_F_PDL).clone()
+    wt, b, s = t16_dev(qt, v44)
+    y0 = ops.gemv(x, wt, b, s, 1024, 2560, qt["n_cb"]).clone()
+    y1 = ops.gemv(x, wt, b, s, 1024, 2560, qt["n_cb"], flags=ops.SX8_F_PDL).clone()
     assert torch.equal(y0, y1)
     out = torch.zeros(4, 1024, device="cuda")
     st = torch.cuda.Stream()
     st.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(st):
-        ops.gemv(x, h, l, b, s, 1024, 2560, qt["n_cb"], out=out, flags=ops.SX8_F_PDL)
+        ops.gemv(x, wt, b, s, 1024, 2560, qt["n_cb"], out=out, flags=ops.SX8_F_PDL)
         st.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=st):
             for _ in range(3):
-                ops.gemv(x, h, l, b, s, 1024, 2560, qt["n_cb"], out=out, flags=ops.SX8_F_PDL)
+                ops.gemv(x, wt, b, s, 1024, 2560, qt["n_cb"], out=out, flags=ops.SX8_F_PDL)
     out.zero_()
     graph.replay()
     torch.cuda.synchronize()
@@ -273,7 +293,8 @@ def test_gemv_matches_reference_kernel_build(ops):
     Z = torch.empty(qt["n_cb"], 2, device="cuda")
     Y = torch.empty(1024, device="cuda")
     ref_mod.decode1_v44_combined(x[0], h, l, b, s, qt["n_cb"], 6, Z, Y)
-    y = ops.gemv(x, h, l, b, s, 1024, 2560, qt["n_cb"])[0]
+    wt, _, _ = t16_dev(qt, v44)
+    y = ops.gemv(x, wt, b, s, 1024, 2560, qt["n_cb"])[0]
     torch.cuda.synchronize()
     assert (y - Y).abs().max().item() <= TOL_VS_KERNEL_FORMULA * Y.abs().max().item()
 
@@ -284,8 +305,8 @@ def test_gemm_small_m(ops, M, f16out):
     w, qt, bi, v44 = case(1024, 2560, 58)
     x = orc.synth_x(M, 2560, 9)
     y_cmp = orc.matmul_ref(x, orc.dequant_d64(qt, bi))
-    h, l, b, s = v44_dev(v44)
-    y = ops.gemm(dev(x), h, l, b, s, 1024, 2560, qt["n_cb"], 6,
+    wt, b, s = t16_dev(qt, v44)
+    y = ops.gemm(dev(x), wt, b, s, 1024, 2560, qt["n_cb"],
                  out_dtype=torch.float16 if f16out else torch.float32).float().cpu().numpy()
     scale = np.abs(y_cmp).max()
     tol = TOL_VS_COMPARATOR + (2.0 ** -10 if f16out else 0.0)
@@ -294,15 +315,15 @@ def test_gemm_small_m(ops, M, f16out):
 
 def test_argument_errors_raise(ops):
     w, qt, bi, v44 = case(64, 256, 59)
-    h, l, b, s = v44_dev(v44)
+    wt, b, s = t16_dev(qt, v44)
     x = dev(orc.synth_x(9, 256, 1))
     with pytest.raises(ops.SX8Error):
-        ops.gemv(x, h, l, b, s, 64, 256, qt["n_cb"])           # M > 8
+        ops.gemv(x, wt, b, s, 64, 256, qt["n_cb"])             # M > 8
     with pytest.raises(ops.SX8Error):
-        ops.gemv(x[:1], h, l, b, s, 60, 256, qt["n_cb"])       # N not a multiple of 8
+        ops.gemv(x[:1], wt, b, s, 128, 256, qt["n_cb"])        # blob size does not match N
     with pytest.raises(ops.SX8Error):
-        ops.gemv(x[:1], h, l, b, s, 64, 256, qt["n_cb"], hdr_bytes=7)
+        ops.gemv(x[:1], wt, b, s, 64, 256, qt["n_cb"] + 1)     # n_cb != ceil(K/32)
     with pytest.raises(ops.SX8Error):
-        ops.gemv(x[:1], h, l, b, s, 64, 256, qt["n_cb"], workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
+        ops.gemv(x[:1], wt, b, s, 64, 256, qt["n_cb"], workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
     with pytest.raises(ops.SX8Error):
-        ops.gemv(x[:1].float(), h, l, b, s, 64, 256, qt["n_cb"])
+        ops.gemv(x[:1].float(), wt, b, s, 64, 256, qt["n_cb"])
