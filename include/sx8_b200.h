@@ -20,7 +20,8 @@
  *     W1 @ +128 +4L : bytes [a4,a6,a5,a7] << 2 | bits 3:2 of [b4,b6,b5,b7]
  *     W2 @ +256 +4L : bytes [b0,b2,b1,b3] << 2 | bits 5:4 of [b4,b6,b5,b7]
  *     H0[g] @ +384+4g : dmin(A) | dmax(A)<<16 ; H1[g] @ +416+4g : same for B ;
- *     H2[g] @ +448+4g : config(A) | coeff(A)<<8 | config(B)<<16 | coeff(B)<<24
+ *     H2[g] @ +448+4g : c0(A) | c0(B)<<4 | config(A)<<8 | c1(A)<<16 | c1(B)<<20 | config(B)<<24
+ *                       (c0 / c1 = low / high nibble of the coeff byte)
  *   It replaces the reference's kb-major "v4.4" pair hdr (n_blk,6) + levels (n_blk,24)
  *   (ref: scripts/prepare_v44.py:35-79), which sx8_repack_v44 still produces for
  *   interchange.  bases (n_cb, 64) f32 and scales (n_cb, 2) f32 are as in the reference.

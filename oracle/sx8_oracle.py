@@ -279,7 +279,8 @@ def to_t16(qt):
         word W1 at unit + 1*128 + 4L : bytes [a4,a6,a5,a7] << 2, low 2 bits = bits 3:2 of [b4,b6,b5,b7]
         word W2 at unit + 2*128 + 4L : bytes [b0,b2,b1,b3] << 2, low 2 bits = bits 5:4 of [b4,b6,b5,b7]
       header words at unit + 384: H0[g] = dmin(A) | dmax(A) << 16, H1[g] (+32) the same for B,
-        H2[g] (+64) = config(A) | coeff(A) << 8 | config(B) << 16 | coeff(B) << 24.
+        H2[g] (+64) = c0(A) | c0(B) << 4 | config(A) << 8 | c1(A) << 16 | c1(B) << 20 | config(B) << 24,
+        c0 / c1 being the low / high nibble of the coeff byte.
     Columns past out_f are zero blocks."""
     out_f, _ = qt["shape"]
     n_cb = qt["n_cb"]
@@ -315,7 +316,8 @@ def to_t16(qt):
     dm, dx, cf, cc = hd(dmin), hd(dmax), hd(cfg), hd(co)
     h0 = dm[:, 0] | (dx[:, 0] << 16)
     h1 = dm[:, 1] | (dx[:, 1] << 16)
-    h2 = cf[:, 0] | (cc[:, 0] << 8) | (cf[:, 1] << 16) | (cc[:, 1] << 24)
+    h2 = ((cc[:, 0] & 15) | ((cc[:, 1] & 15) << 4) | (cf[:, 0] << 8) | ((cc[:, 0] >> 4) << 16)
+          | ((cc[:, 1] >> 4) << 20) | (cf[:, 1] << 24))
     hdr = np.stack([h0, h1, h2], axis=0).transpose(1, 3, 0, 2)        # (nt, kb, 3, g)
     blob = np.empty((nt, n_cb, 120), np.uint32)
     blob[:, :, :96] = lev.reshape(nt, n_cb, 96)

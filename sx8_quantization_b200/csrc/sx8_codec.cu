@@ -329,7 +329,10 @@ repack_t16_kernel(const uint16_t* __restrict__ dmin, const uint16_t* __restrict_
     u[64 + L] = W2;
     if (t == 0) u[96 + g] = hA;
     if (t == 1) u[104 + g] = hB;
-    if (t == 2) u[112 + g] = ccA | (ccB << 16);
+    if (t == 2) {
+        uint32_t cfA = ccA & 0xFF, coA = ccA >> 8, cfB = ccB & 0xFF, coB = ccB >> 8;
+        u[112 + g] = (coA & 15) | ((coB & 15) << 4) | (cfA << 8) | ((coA >> 4) << 16) | ((coB >> 4) << 20) | (cfB << 24);
+    }
 }
 
 }  // namespace sx8

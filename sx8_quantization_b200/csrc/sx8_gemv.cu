@@ -124,6 +124,14 @@ __device__ __forceinline__ void consumer_bar() {  // the 8 consumer warps only
     asm volatile("bar.sync 1, 256;" ::: "memory");
 }
 
+// x >> 8.  With SX8_UMULHI the shift runs as a multiply-high on the FMA pipe, taking load
+// off the integer/logic pipe that bounds this kernel.
+#ifdef SX8_UMULHI
+#define SHR8(x) __umulhi((x), 0x01000000u)
+#else
+#define SHR8(x) ((x) >> 8)
+#endif
+
 // fp32 -> (hi, lo) fp16 pair: hi + lo == v to ~22 bits.
 __device__ __forceinline__ void split_hilo(float v, uint32_t& hi, uint32_t& lo) {
     __half h = __float2half_rn(v);
@@ -305,7 +313,7 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
         consumer_bar();
 
         const uint32_t maskT0 = (t == 0) ? 0xFFFFFFFFu : 0u;
-        const uint32_t sh2 = 2u * (uint32_t)t;
+        const uint32_t sh2 = 8u + 2u * (uint32_t)t;
         bool ok = true;
         int it = 0;
         for (int gi = 0; gi < my_groups; gi++) {
@@ -324,6 +332,7 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
                     uint4 xq = make_uint4(0u, 0u, 0u, 0u);
                     if (row_ok) xq = lds128(st + C::OFF_X + g * C::XROW + r * 64 + t * 16);
                     uint32_t dv = lds32(dtab + (j * KB_S + r) * DT_KB + lane * 4);
+                    uint32_t dv0 = dv & maskT0, dv1 = dv & ~maskT0;
 
                     // per sub-block constants looked up by range strategy:
                     //   mult * 2^8  = 1024, 256, 256, 512     63*off * 2^-14 = 0, 0, 189*2^-14, 63*2^-14
@@ -338,24 +347,23 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
                     // fma gives (mult*level + 63*off) * 2^-14, exact
                     uint32_t V3 = ((W0 << 2) & 0x0C0C0C0Cu) | ((W1 << 4) & 0x30303030u) | ((W2 << 6) & 0xC0C0C0C0u);
                     uint32_t fa0 = hfma2_u32(W0 & 0x00FC00FCu, mA, aA);
-                    uint32_t fa1 = hfma2_u32((W0 >> 8) & 0x00FC00FCu, mA, aA);
+                    uint32_t fa1 = hfma2_u32(SHR8(W0) & 0x00FC00FCu, mA, aA);
                     uint32_t fa2 = hfma2_u32(W1 & 0x00FC00FCu, mA, aA);
-                    uint32_t fa3 = hfma2_u32((W1 >> 8) & 0x00FC00FCu, mA, aA);
+                    uint32_t fa3 = hfma2_u32(SHR8(W1) & 0x00FC00FCu, mA, aA);
                     uint32_t fb0 = hfma2_u32(W2 & 0x00FC00FCu, mB, aB);
-                    uint32_t fb1 = hfma2_u32((W2 >> 8) & 0x00FC00FCu, mB, aB);
+                    uint32_t fb1 = hfma2_u32(SHR8(W2) & 0x00FC00FCu, mB, aB);
                     uint32_t fb2 = hfma2_u32(V3 & 0x00FF00FFu, mB, aB);
-                    uint32_t fb3 = hfma2_u32((V3 >> 8) & 0x00FF00FFu, mB, aB);
+                    uint32_t fb3 = hfma2_u32(SHR8(V3) & 0x00FF00FFu, mB, aB);
                     float d[4] = {0.f, 0.f, 0.f, 0.f};
                     mma16816(d, fa0, fb0, fa1, fb1, xq.x, xq.y);
                     mma16816(d, fa2, fb2, fa3, fb3, xq.z, xq.w);
-                    // direct terms: {lo,lo} x {SxB_hi,SxB_lo} on lane t=0; {c0,c1}*2^-10 x 1024*Z on t=1,2
-                    uint32_t rA = ((__byte_perm(H2, 0u, 0x4441u) * 0x1001u) & 0x000F000Fu) ^ 0x64086408u;
-                    uint32_t rB = (((H2 >> 24) * 0x1001u) & 0x000F000Fu) ^ 0x64086408u;
-                    uint32_t ccA = hfma2_u32(rA, 0x14001400u, 0xBC08BC08u);
-                    uint32_t ccB = hfma2_u32(rB, 0x14001400u, 0xBC08BC08u);
-                    uint32_t dA = (__byte_perm(H0, 0u, 0x1010u) & maskT0) | (ccA & ~maskT0);
-                    uint32_t dB = (__byte_perm(H1, 0u, 0x1010u) & maskT0) | (ccB & ~maskT0);
-                    mma1688(accD, dA, dB, dv);
+                    // direct terms: {lo,lo} x {SxB_hi,SxB_lo} (table word of lane t=0) and
+                    // {c0,c1} * 2^-10 x 1024*Z (table words of lanes t=1,2); the table holds zeros
+                    // where a lane contributes nothing, so every lane feeds the same operands
+                    uint32_t ccA = hfma2_u32((H2 & 0x000F000Fu) ^ 0x64086408u, 0x14001400u, 0xBC08BC08u);
+                    uint32_t ccB = hfma2_u32(((H2 >> 4) & 0x000F000Fu) ^ 0x64086408u, 0x14001400u, 0xBC08BC08u);
+                    mma1688(accD, __byte_perm(H0, 0u, 0x1010u), __byte_perm(H1, 0u, 0x1010u), dv0);
+                    mma1688(accD, ccA, ccB, dv1);
                     const float kBase = 0.25f * 0.015873f * 16384.0f;
                     float baseA = (h2f_bits((uint16_t)(H0 >> 16)) - h2f_bits((uint16_t)H0)) * kBase;
                     float baseB = (h2f_bits((uint16_t)(H1 >> 16)) - h2f_bits((uint16_t)H1)) * kBase;
@@ -486,7 +494,10 @@ Choice choose(int N, int n_cb) {
     best.grid_x = groups;
     if (best.nt == 8 && best.split == 1) {
         int cap = f_grid > 0 ? f_grid : 3 * kSMs;
-        if (groups > cap) best.grid_x = cap;
+        if (groups > cap) {   // equal number of tile groups per CTA
+            int per = (groups + cap - 1) / cap;
+            best.grid_x = (groups + per - 1) / per;
+        }
     }
     return best;
 }
@@ -566,9 +577,9 @@ int gemv_launch(const void* x, int M, int K, long ldx, const void* wt16, const f
     const int n_tiles = (int)t16_tiles(N);
     GemvParams p{(const uint8_t*)wt16, xp, bases, scales, y, ld, N, n_cb, M, c.split, n_tiles,
                  (n_tiles + c.nt - 1) / c.nt};
-    if (c.nt == 8) return launch_gemv<8, 4, 3>(p, c.grid_x, flags, stream);
-    if (c.nt == 4) return launch_gemv<4, 8, 3>(p, c.grid_x, flags, stream);
-    return launch_gemv<2, 8, 4>(p, c.grid_x, flags, stream);
+    if (c.nt == 8) return launch_gemv<8, 2, 6>(p, c.grid_x, flags, stream);
+    if (c.nt == 4) return launch_gemv<4, 4, 6>(p, c.grid_x, flags, stream);
+    return launch_gemv<2, 4, 8>(p, c.grid_x, flags, stream);
 }
 
 int gemv_check(const char* who, const void* x, int M, int Mmax, int K, long ldx, const void* wt16,

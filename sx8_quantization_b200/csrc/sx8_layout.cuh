@@ -14,7 +14,8 @@
 //     W2 @ unit + 256 + 4L : bytes [b0,b2,b1,b3] << 2 | bits 5:4 of [b4,b6,b5,b7]
 //     H0[g] @ unit + 384 + 4g : dmin(A) | dmax(A) << 16      (fp16 bits)
 //     H1[g] @ unit + 416 + 4g : dmin(B) | dmax(B) << 16
-//     H2[g] @ unit + 448 + 4g : config(A) | coeff(A) << 8 | config(B) << 16 | coeff(B) << 24
+//     H2[g] @ unit + 448 + 4g : c0(A) | c0(B)<<4 | config(A)<<8 | c1(A)<<16 | c1(B)<<20 | config(B)<<24
+//                               (c0 / c1 = low / high nibble of the coeff byte)
 //   Columns >= N are zero blocks.  Exactly 30 bytes per block.
 #pragma once
 #include <stdint.h>
@@ -50,11 +51,11 @@ __device__ __forceinline__ T16Sub t16_read(const uint8_t* __restrict__ blob, lon
         s.lv[4] = (V3 >> 2) & 63;  s.lv[5] = (V3 >> 18) & 63; s.lv[6] = (V3 >> 10) & 63; s.lv[7] = (V3 >> 26) & 63;
     }
     uint32_t h = u[96 + isB * 8 + g];
-    uint32_t h2 = u[112 + g] >> (16 * isB);
+    uint32_t h2 = u[112 + g];
     s.dmin = h & 0xFFFFu;
     s.dmax = h >> 16;
-    s.cfg = h2 & 0xFFu;
-    s.coeff = (h2 >> 8) & 0xFFu;
+    s.cfg = (h2 >> (8 + 16 * isB)) & 0xFFu;
+    s.coeff = ((h2 >> (4 * isB)) & 0xFu) | (((h2 >> (16 + 4 * isB)) & 0xFu) << 4);
     return s;
 }
 
