@@ -37,7 +37,7 @@ constexpr int kConsumerWarps = 8;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr int kMaxKbPerCta = 256;   // capacity of the per-CTA activation table
-constexpr int DT_KB = 128;          // table bytes per kb: [m][t] words
+constexpr int DT_KB = 128;          // table bytes per kb: [m][t = 0,1] x {lo-term word, coefficient-term word}
 
 // ------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -162,6 +162,7 @@ struct GemvParams {
     float* y;
     long ldx;
     int N, n_cb, M, split, n_tiles, groups;
+    int debug;   // bit 0: consumers skip the math (pipeline-only timing experiments)
 };
 
 template <int NT, int KB_S, int STAGES>
@@ -269,50 +270,63 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
 
         // ---- activation-side table for kb_begin..kb_end: one warp per kb, lane = (m = g, t).
-        //   word[m][t]: t=0 {SxB_hi, SxB_lo}; t=1 {Z0_hi, Z1_hi}; t=2 {Z0_lo, Z1_lo}; t=3 0,
-        //   with Zj (ref cuda/sx8_decode1_v3.cu:44-65) pre-multiplied by 1024.
-        for (int kb = kb_begin + warp; kb < kb_end; kb += kConsumerWarps) {
-            float xv[8];
+        // Two 8-byte entries per row m, read by lanes t = 0 and t = 1 of the main loop:
+        //   entry t=0: { {SxB_hi, 0}, {Z0_hi, Z1_hi} }    entry t=1: { {SxB_lo, 0}, {Z0_lo, Z1_lo} }
+        // The first word multiplies the {dmin, dmax} pair of a column (the zero half cancels
+        // dmax), the second the {c0, c1} * 2^-10 pair; Zj (ref cuda/sx8_decode1_v3.cu:44-65)
+        // is pre-multiplied by 1024.  Loads of two kb are issued together to hide their latency.
+        for (int kb0 = kb_begin + 2 * warp; kb0 < kb_end; kb0 += 2 * kConsumerWarps) {
+            uint4 raw[2];
+            float4 bq[2][4];
+            float sc[2][2];
 #pragma unroll
-            for (int i = 0; i < 8; i++) xv[i] = 0.f;
-            if (row_ok) {
-                uint4 raw = *reinterpret_cast<const uint4*>(p.x + (long)g * p.ldx + (long)kb * 32 + t * 8);
-                const __half* hh = reinterpret_cast<const __half*>(&raw);
-#pragma unroll
-                for (int i = 0; i < 8; i++) xv[i] = __half2float(hh[i]);
-            }
-            const float4* b0p = reinterpret_cast<const float4*>(p.bases + (long)kb * 64 + t * 8);
-            const float4* b1p = reinterpret_cast<const float4*>(p.bases + (long)kb * 64 + 32 + t * 8);
-            float4 b0a = b0p[0], b0b = b0p[1], b1a = b1p[0], b1b = b1p[1];
-            float bb0[8] = {b0a.x, b0a.y, b0a.z, b0a.w, b0b.x, b0b.y, b0b.z, b0b.w};
-            float bb1[8] = {b1a.x, b1a.y, b1a.z, b1a.w, b1b.x, b1b.y, b1b.z, b1b.w};
-            float sx = 0.f, z0 = 0.f, z1 = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                sx += xv[i];
-                z0 = fmaf(xv[i], bb0[i], z0);
-                z1 = fmaf(xv[i], bb1[i], z1);
+            for (int u = 0; u < 2; u++) {
+                int kb = min(kb0 + u, kb_end - 1);
+                raw[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (row_ok) raw[u] = *reinterpret_cast<const uint4*>(p.x + (long)g * p.ldx + (long)kb * 32 + t * 8);
+                const float4* b0p = reinterpret_cast<const float4*>(p.bases + (long)kb * 64 + t * 8);
+                const float4* b1p = reinterpret_cast<const float4*>(p.bases + (long)kb * 64 + 32 + t * 8);
+                bq[u][0] = b0p[0]; bq[u][1] = b0p[1]; bq[u][2] = b1p[0]; bq[u][3] = b1p[1];
+                sc[u][0] = p.scales[kb * 2 + 0];
+                sc[u][1] = p.scales[kb * 2 + 1];
             }
 #pragma unroll
-            for (int off = 1; off <= 2; off <<= 1) {
-                sx += __shfl_xor_sync(0xFFFFFFFFu, sx, off);
-                z0 += __shfl_xor_sync(0xFFFFFFFFu, z0, off);
-                z1 += __shfl_xor_sync(0xFFFFFFFFu, z1, off);
+            for (int u = 0; u < 2; u++) {
+                int kb = kb0 + u;
+                const __half* hh = reinterpret_cast<const __half*>(&raw[u]);
+                float bb0[8] = {bq[u][0].x, bq[u][0].y, bq[u][0].z, bq[u][0].w, bq[u][1].x, bq[u][1].y, bq[u][1].z, bq[u][1].w};
+                float bb1[8] = {bq[u][2].x, bq[u][2].y, bq[u][2].z, bq[u][2].w, bq[u][3].x, bq[u][3].y, bq[u][3].z, bq[u][3].w};
+                float sx = 0.f, z0 = 0.f, z1 = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    float xv = __half2float(hh[i]);
+                    sx += xv;
+                    z0 = fmaf(xv, bb0[i], z0);
+                    z1 = fmaf(xv, bb1[i], z1);
+                }
+#pragma unroll
+                for (int off = 1; off <= 2; off <<= 1) {
+                    sx += __shfl_xor_sync(0xFFFFFFFFu, sx, off);
+                    z0 += __shfl_xor_sync(0xFFFFFFFFu, z0, off);
+                    z1 += __shfl_xor_sync(0xFFFFFFFFu, z1, off);
+                }
+                z0 = sc[u][0] * z0 * 1024.0f;
+                z1 = sc[u][1] * z1 * 1024.0f;
+                uint32_t sh, sl, z0h, z0l, z1h, z1l;
+                split_hilo(sx, sh, sl);
+                split_hilo(z0, z0h, z0l);
+                split_hilo(z1, z1h, z1l);
+                if (t < 2 && kb < kb_end) {
+                    uint32_t w0 = (t == 0) ? sh : sl;
+                    uint32_t w1 = (t == 0) ? (z0h | (z1h << 16)) : (z0l | (z1l << 16));
+                    uint32_t a = dtab + (kb - kb_begin) * DT_KB + g * 16 + t * 8;
+                    sts32(a, w0);
+                    sts32(a + 4, w1);
+                }
             }
-            z0 = p.scales[kb * 2 + 0] * z0 * 1024.0f;
-            z1 = p.scales[kb * 2 + 1] * z1 * 1024.0f;
-            uint32_t sh, sl, z0h, z0l, z1h, z1l;
-            split_hilo(sx, sh, sl);
-            split_hilo(z0, z0h, z0l);
-            split_hilo(z1, z1h, z1l);
-            uint32_t word = (t == 0) ? (sh | (sl << 16))
-                          : (t == 1) ? (z0h | (z1h << 16))
-                          : (t == 2) ? (z0l | (z1l << 16)) : 0u;
-            sts32(dtab + (kb - kb_begin) * DT_KB + lane * 4, row_ok ? word : 0u);
         }
         consumer_bar();
 
-        const uint32_t maskT0 = (t == 0) ? 0xFFFFFFFFu : 0u;
         const uint32_t sh2 = 8u + 2u * (uint32_t)t;
         bool ok = true;
         int it = 0;
@@ -323,7 +337,7 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
                 if (ok) ok = mbar_wait(bar_full + 8 * s, (it / STAGES) & 1, 2u);
                 int rows = min(KB_S, kb_end - (kb_begin + j * KB_S));
                 uint32_t st = sbase + s * C::STAGE;
-                for (int r = kpart; r < rows; r += C::KS) {
+                for (int r = kpart; r < rows && !(p.debug & 1); r += C::KS) {
                     uint32_t unit = st + (ti * KB_S + r) * T16_UNIT;
                     uint32_t W0 = lds32(unit + lane * 4), W1 = lds32(unit + 128 + lane * 4),
                              W2 = lds32(unit + 256 + lane * 4);
@@ -331,8 +345,11 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
                              H2 = lds32(unit + 448 + g * 4);
                     uint4 xq = make_uint4(0u, 0u, 0u, 0u);
                     if (row_ok) xq = lds128(st + C::OFF_X + g * C::XROW + r * 64 + t * 16);
-                    uint32_t dv = lds32(dtab + (j * KB_S + r) * DT_KB + lane * 4);
-                    uint32_t dv0 = dv & maskT0, dv1 = dv & ~maskT0;
+                    uint32_t dv0 = 0u, dv1 = 0u;
+                    if (t < 2) {
+                        uint32_t a = dtab + (j * KB_S + r) * DT_KB + g * 16 + t * 8;
+                        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(dv0), "=r"(dv1) : "r"(a));
+                    }
 
                     // per sub-block constants looked up by range strategy:
                     //   mult * 2^8  = 1024, 256, 256, 512     63*off * 2^-14 = 0, 0, 189*2^-14, 63*2^-14
@@ -357,12 +374,11 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
                     float d[4] = {0.f, 0.f, 0.f, 0.f};
                     mma16816(d, fa0, fb0, fa1, fb1, xq.x, xq.y);
                     mma16816(d, fa2, fb2, fa3, fb3, xq.z, xq.w);
-                    // direct terms: {lo,lo} x {SxB_hi,SxB_lo} (table word of lane t=0) and
-                    // {c0,c1} * 2^-10 x 1024*Z (table words of lanes t=1,2); the table holds zeros
-                    // where a lane contributes nothing, so every lane feeds the same operands
+                    // direct terms: {dmin,dmax} x {SxB_hi|lo, 0} and {c0,c1} * 2^-10 x 1024*Z; lanes
+                    // t = 0,1 carry the hi and lo halves of the activation sums, lanes 2,3 zeros
                     uint32_t ccA = hfma2_u32((H2 & 0x000F000Fu) ^ 0x64086408u, 0x14001400u, 0xBC08BC08u);
                     uint32_t ccB = hfma2_u32(((H2 >> 4) & 0x000F000Fu) ^ 0x64086408u, 0x14001400u, 0xBC08BC08u);
-                    mma1688(accD, __byte_perm(H0, 0u, 0x1010u), __byte_perm(H1, 0u, 0x1010u), dv0);
+                    mma1688(accD, H0, H1, dv0);
                     mma1688(accD, ccA, ccB, dv1);
                     const float kBase = 0.25f * 0.015873f * 16384.0f;
                     float baseA = (h2f_bits((uint16_t)(H0 >> 16)) - h2f_bits((uint16_t)H0)) * kBase;
@@ -575,11 +591,16 @@ int gemv_launch(const void* x, int M, int K, long ldx, const void* wt16, const f
     }
     Choice c = choose(N, n_cb);
     const int n_tiles = (int)t16_tiles(N);
+    static const int dbg = env_int("SX8_GEMV_DEBUG");
     GemvParams p{(const uint8_t*)wt16, xp, bases, scales, y, ld, N, n_cb, M, c.split, n_tiles,
-                 (n_tiles + c.nt - 1) / c.nt};
-    if (c.nt == 8) return launch_gemv<8, 2, 6>(p, c.grid_x, flags, stream);
-    if (c.nt == 4) return launch_gemv<4, 4, 6>(p, c.grid_x, flags, stream);
-    return launch_gemv<2, 4, 8>(p, c.grid_x, flags, stream);
+                 (n_tiles + c.nt - 1) / c.nt, dbg};
+    static const int var = env_int("SX8_GEMV_VAR");
+    if (c.nt == 8 && var == 1) return launch_gemv<8, 2, 6>(p, c.grid_x, flags, stream);
+    if (c.nt == 8 && var == 2) return launch_gemv<8, 8, 3>(p, c.grid_x, flags, stream);
+    if (c.nt == 8 && var == 3) return launch_gemv<8, 4, 5>(p, c.grid_x, flags, stream);
+    if (c.nt == 8) return launch_gemv<8, 4, 3>(p, c.grid_x, flags, stream);
+    if (c.nt == 4) return launch_gemv<4, 8, 3>(p, c.grid_x, flags, stream);
+    return launch_gemv<2, 8, 4>(p, c.grid_x, flags, stream);
 }
 
 int gemv_check(const char* who, const void* x, int M, int Mmax, int K, long ldx, const void* wt16,
