@@ -79,13 +79,13 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
 }
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void mma1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(b0));
@@ -97,12 +97,12 @@ __device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c
 }
 __device__ __forceinline__ uint32_t lds32(uint32_t a) {
     uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a) : "memory");
     return v;
 }
 __device__ __forceinline__ uint4 lds128(uint32_t a) {
     uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a) : "memory");
     return v;
 }
 __device__ __forceinline__ void sts32(uint32_t a, uint32_t v) {
@@ -337,7 +337,10 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
                 if (ok) ok = mbar_wait(bar_full + 8 * s, (it / STAGES) & 1, 2u);
                 int rows = min(KB_S, kb_end - (kb_begin + j * KB_S));
                 uint32_t st = sbase + s * C::STAGE;
-                for (int r = kpart; r < rows && !(p.debug & 1); r += C::KS) {
+#pragma unroll
+                for (int ri = 0; ri < KB_S / C::KS; ri++) {
+                    const int r = kpart + ri * C::KS;
+                    if (r >= rows || (p.debug & 1)) break;
                     uint32_t unit = st + (ti * KB_S + r) * T16_UNIT;
                     uint32_t W0 = lds32(unit + lane * 4), W1 = lds32(unit + 128 + lane * 4),
                              W2 = lds32(unit + 256 + lane * 4);
@@ -348,7 +351,7 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
                     uint32_t dv0 = 0u, dv1 = 0u;
                     if (t < 2) {
                         uint32_t a = dtab + (j * KB_S + r) * DT_KB + g * 16 + t * 8;
-                        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(dv0), "=r"(dv1) : "r"(a));
+                        asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(dv0), "=r"(dv1) : "r"(a) : "memory");
                     }
 
                     // per sub-block constants looked up by range strategy:
