@@ -154,3 +154,334 @@ struct Params {
     void* y;
     int M, N, n_cb, n_tiles, out_f16;
 };
+
+template <int MT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, Params p) {
+    using C = Cfg<MT>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sA = sbase + C::OFF_A, sB = sbase + C::OFF_B, sP = sbase + C::OFF_P;
+    const uint32_t bar0 = sbase + C::OFF_BAR;
+    const uint32_t a_full = bar0, a_empty = a_full + 8 * C::SA;
+    const uint32_t b_full = a_empty + 8 * C::SA, b_empty = b_full + 8 * C::SB;
+    const uint32_t p_full = b_empty + 8 * C::SB, p_empty = p_full + 8 * C::SP;
+    const uint32_t acc_full = p_empty + 8 * C::SP;
+    const uint32_t tmem_slot = sbase + C::OFF_TMEM;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BN;
+    const int m0 = blockIdx.y * (128 * MT);
+    const int tile0 = n0 >> 4;
+    const int n_ks = (p.n_cb + KB_STAGE - 1) / KB_STAGE;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::SA; s++) { mbar_init(a_full + 8 * s, 1); mbar_init(a_empty + 8 * s, 1); }
+        for (int s = 0; s < C::SB; s++) { mbar_init(b_full + 8 * s, kDecodeWarps); mbar_init(b_empty + 8 * s, 1); }
+        for (int s = 0; s < C::SP; s++) { mbar_init(p_full + 8 * s, 1); mbar_init(p_empty + 8 * s, kDecodeWarps); }
+        mbar_init(acc_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {   // TMEM: all 512 columns (two 128 x 256 fp32 accumulators)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = lds32(tmem_slot);
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        bool ok = true;
+        for (int ks = 0; ks < n_ks; ks++) {
+            const int kb0 = ks * KB_STAGE;
+            const int rows = min(KB_STAGE, p.n_cb - kb0);
+            {   // packed slabs + PCA table: lane i < 16 copies tile i, lane 16 the table
+                const int s = ks % C::SP;
+                if (ks >= C::SP && ok) ok = mbar_wait(p_empty + 8 * s, ((ks / C::SP) - 1) & 1, 0x10u);
+                const int tiles = min(16, p.n_tiles - tile0);
+                if (lane == 0)
+                    mbar_expect_tx(p_full + 8 * s, (uint32_t)rows * ((uint32_t)tiles * T16_UNIT + 128u));
+                __syncwarp();
+                const uint32_t dst = sP + s * P_STAGE;
+                if (lane < 16 && tile0 + lane < p.n_tiles)
+                    bulk_g2s(dst + lane * (KB_STAGE * T16_UNIT),
+                             p.blob + ((long)(tile0 + lane) * p.n_cb + kb0) * T16_UNIT, (uint32_t)rows * T16_UNIT,
+                             p_full + 8 * s);
+                if (lane == 16)
+                    bulk_g2s(dst + P_SLAB, p.pb + (long)kb0 * 64, (uint32_t)rows * 128u, p_full + 8 * s);
+            }
+            {   // X tiles: MT boxes of 64 (K) x 128 (rows); columns/rows out of range read as zero
+                const int s = ks % C::SA;
+                if (ks >= C::SA && ok) ok = mbar_wait(a_empty + 8 * s, ((ks / C::SA) - 1) & 1, 0x20u);
+                if (lane == 0) {
+                    mbar_expect_tx(a_full + 8 * s, (uint32_t)(MT * A_TILE));
+                    for (int mt = 0; mt < MT; mt++)
+                        tma_load_2d(sA + (s * MT + mt) * A_TILE, &xmap, ks * BK, m0 + mt * 128, a_full + 8 * s);
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        bool ok = true;
+        for (int ks = 0; ks < n_ks; ks++) {
+            const int sa = ks % C::SA, sb = ks % C::SB;
+            if (ok) ok = mbar_wait(a_full + 8 * sa, (ks / C::SA) & 1, 0x40u);
+            if (ok) ok = mbar_wait(b_full + 8 * sb, (ks / C::SB) & 1, 0x80u);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (lane == 0) {
+                const uint64_t bdesc = umma_desc(sB + sb * B_TILE);
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) {
+                    const uint64_t adesc = umma_desc(sA + (sa * MT + mt) * A_TILE);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; k++)   // +32 bytes along K inside the swizzle atom
+                        umma_f16(tmem_base + mt * BN, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2),
+                                 (ks > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(a_empty + 8 * sa);
+                umma_commit(b_empty + 8 * sb);
+                if (ks == n_ks - 1) umma_commit(acc_full);
+            }
+            __syncwarp();
+        }
+    } else {
+        // ------------------------------------------------------------ decoders
+        const int dw = warp - 2;                 // 0..7: tiles dw and dw + 8 of the CTA's 16
+        const int g = lane >> 2, t = lane & 3;
+        const uint32_t sh2 = 8u + 2u * (uint32_t)t;
+        const float kBase = 0.25f * 0.015873f * 512.0f;   // levels are formed scaled by 2^-9
+        bool ok = true;
+        for (int ks = 0; ks < n_ks; ks++) {
+            const int sp = ks % C::SP, sb = ks % C::SB;
+            const int rows = min(KB_STAGE, p.n_cb - ks * KB_STAGE);
+            if (ok) ok = mbar_wait(p_full + 8 * sp, (ks / C::SP) & 1, 0x100u);
+            if (ks >= C::SB && ok) ok = mbar_wait(b_empty + 8 * sb, ((ks / C::SB) - 1) & 1, 0x200u);
+            const uint32_t pst = sP + sp * P_STAGE, bst = sB + sb * B_TILE;
+#pragma unroll
+            for (int ti = 0; ti < 2; ti++) {
+                const int tl = dw + ti * 8;
+                const bool tile_ok = tile0 + tl < p.n_tiles;
+                const uint32_t rowA = (uint32_t)(tl * 16 + g), rowB = rowA + 8;
+#pragma unroll
+                for (int r = 0; r < KB_STAGE; r++) {
+                    uint4 wa = make_uint4(0u, 0u, 0u, 0u), wb = wa;
+                    if (r < rows && tile_ok) {
+                        const uint32_t unit = pst + (tl * KB_STAGE + r) * T16_UNIT;
+                        uint32_t W0 = lds32(unit + lane * 4), W1 = lds32(unit + 128 + lane * 4),
+                                 W2 = lds32(unit + 256 + lane * 4);
+                        uint32_t H0 = lds32(unit + 384 + g * 4), H1 = lds32(unit + 416 + g * 4),
+                                 H2 = lds32(unit + 448 + g * 4);
+                        uint4 s0 = lds128(pst + P_SLAB + r * 128 + t * 16);        // 1024*s0*b0[8t..8t+7]
+                        uint4 s1 = lds128(pst + P_SLAB + r * 128 + 64 + t * 16);   // 1024*s1*b1[8t..8t+7]
+                        uint32_t u = (H2 >> sh2) & 0x00030003u;
+                        uint32_t sel = u * 0x2222u + 0x10101010u;
+                        uint32_t selB = sel >> 16;
+                        // mult * 2^13 = 32768, 8192, 8192, 16384 ; 63*off * 2^-9 = 0, 0, 189/512, 63/512
+                        uint32_t mA = __byte_perm(0x70007800u, 0x74007000u, sel);
+                        uint32_t aA = __byte_perm(0x00000000u, 0x2FE035E8u, sel);
+                        uint32_t mB = __byte_perm(0x70007800u, 0x74007000u, selB);
+                        uint32_t aB = __byte_perm(0x00000000u, 0x2FE035E8u, selB);
+                        uint32_t V3 = ((W0 << 2) & 0x0C0C0C0Cu) | ((W1 << 4) & 0x30303030u) | ((W2 << 6) & 0xC0C0C0C0u);
+                        // (mult*level + 63*off) * 2^-9, exact (level bytes read as fp16 are level * 2^-22)
+                        wa.x = hfma2_u32(W0 & 0x00FC00FCu, mA, aA);
+                        wa.y = hfma2_u32((W0 >> 8) & 0x00FC00FCu, mA, aA);
+                        wa.z = hfma2_u32(W1 & 0x00FC00FCu, mA, aA);
+                        wa.w = hfma2_u32((W1 >> 8) & 0x00FC00FCu, mA, aA);
+                        wb.x = hfma2_u32(W2 & 0x00FC00FCu, mB, aB);
+                        wb.y = hfma2_u32((W2 >> 8) & 0x00FC00FCu, mB, aB);
+                        wb.z = hfma2_u32(V3 & 0x00FF00FFu, mB, aB);
+                        wb.w = hfma2_u32((V3 >> 8) & 0x00FF00FFu, mB, aB);
+                        // w = dmin + base * (...)   (fp16 pairs; base = (dmax-dmin)*0.25*0.015873*2^9)
+                        float bAf = (h2f_bits((uint16_t)(H0 >> 16)) - h2f_bits((uint16_t)H0)) * kBase;
+                        float bBf = (h2f_bits((uint16_t)(H1 >> 16)) - h2f_bits((uint16_t)H1)) * kBase;
+                        __half2 bA2 = __float2half2_rn(bAf), bB2 = __float2half2_rn(bBf);
+                        uint32_t bA = *reinterpret_cast<uint32_t*>(&bA2), bB = *reinterpret_cast<uint32_t*>(&bB2);
+                        uint32_t loA = dup_lo(H0), loB = dup_lo(H1);
+                        wa.x = hfma2_u32(wa.x, bA, loA); wa.y = hfma2_u32(wa.y, bA, loA);
+                        wa.z = hfma2_u32(wa.z, bA, loA); wa.w = hfma2_u32(wa.w, bA, loA);
+                        wb.x = hfma2_u32(wb.x, bB, loB); wb.y = hfma2_u32(wb.y, bB, loB);
+                        wb.z = hfma2_u32(wb.z, bB, loB); wb.w = hfma2_u32(wb.w, bB, loB);
+                        // PCA: + (c0 * 2^-10) * (1024*s0*b0[t]) + (c1 * 2^-10) * (1024*s1*b1[t])
+                        uint32_t ccA = hfma2_u32((H2 & 0x000F000Fu) ^ 0x64086408u, 0x14001400u, 0xBC08BC08u);
+                        uint32_t ccB = hfma2_u32(((H2 >> 4) & 0x000F000Fu) ^ 0x64086408u, 0x14001400u, 0xBC08BC08u);
+                        uint32_t c0A = dup_lo(ccA), c1A = dup_hi(ccA), c0B = dup_lo(ccB), c1B = dup_hi(ccB);
+                        wa.x = hfma2_u32(c0A, s0.x, wa.x); wa.y = hfma2_u32(c0A, s0.y, wa.y);
+                        wa.z = hfma2_u32(c0A, s0.z, wa.z); wa.w = hfma2_u32(c0A, s0.w, wa.w);
+                        wa.x = hfma2_u32(c1A, s1.x, wa.x); wa.y = hfma2_u32(c1A, s1.y, wa.y);
+                        wa.z = hfma2_u32(c1A, s1.z, wa.z); wa.w = hfma2_u32(c1A, s1.w, wa.w);
+                        wb.x = hfma2_u32(c0B, s0.x, wb.x); wb.y = hfma2_u32(c0B, s0.y, wb.y);
+                        wb.z = hfma2_u32(c0B, s0.z, wb.z); wb.w = hfma2_u32(c0B, s0.w, wb.w);
+                        wb.x = hfma2_u32(c1B, s1.x, wb.x); wb.y = hfma2_u32(c1B, s1.y, wb.y);
+                        wb.z = hfma2_u32(c1B, s1.z, wb.z); wb.w = hfma2_u32(c1B, s1.w, wb.w);
+                    }
+                    // 16-byte chunk c = 4r + t of the 128-byte row, XOR-swizzled with (row & 7)
+                    const uint32_t c = (uint32_t)(r * 4 + t);
+                    sts128(bst + rowA * 128 + ((c ^ (rowA & 7u)) << 4), wa);
+                    sts128(bst + rowB * 128 + ((c ^ (rowB & 7u)) << 4), wb);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic stores -> tensor-core reads
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(b_full + 8 * sb);
+                mbar_arrive(p_empty + 8 * sp);
+            }
+        }
+        // ------------------------------------------------------------ epilogue
+        if (ok) ok = mbar_wait(acc_full, 0u, 0x400u);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int quarter = warp & 3;            // TMEM lanes 32*quarter .. +31 are this warp's
+        const int half = dw >> 2;                // the two warps of a quarter split the columns
+#pragma unroll 1
+        for (int mt = 0; mt < MT; mt++) {
+            const long m = (long)m0 + mt * 128 + quarter * 32 + lane;
+#pragma unroll 1
+            for (int cc = 0; cc < 4; cc++) {
+                const int col = half * 128 + cc * 32;
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BN + col), v);
+                if (m < p.M) {
+                    const int n = n0 + col;
+                    if (p.out_f16) {
+                        __half* dst = reinterpret_cast<__half*>(p.y) + m * p.N + n;
+                        if (n + 32 <= p.N && (p.N % 8) == 0) {
+#pragma unroll
+                            for (int q = 0; q < 4; q++) {
+                                uint4 o;
+                                __half2 h0 = __floats2half2_rn(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1]));
+                                __half2 h1 = __floats2half2_rn(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
+                                __half2 h2 = __floats2half2_rn(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
+                                __half2 h3 = __floats2half2_rn(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
+                                o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+                                o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
+                                *reinterpret_cast<uint4*>(dst + 8 * q) = o;
+                            }
+                        } else {
+                            for (int q = 0; q < 32; q++)
+                                if (n + q < p.N) dst[q] = __float2half_rn(__uint_as_float(v[q]));
+                        }
+                    } else {
+                        float* dst = reinterpret_cast<float*>(p.y) + m * p.N + n;
+                        if (n + 32 <= p.N && (p.N % 4) == 0) {
+#pragma unroll
+                            for (int q = 0; q < 8; q++)
+                                *reinterpret_cast<uint4*>(dst + 4 * q) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                        } else {
+                            for (int q = 0; q < 32; q++)
+                                if (n + q < p.N) dst[q] = __uint_as_float(v[q]);
+                        }
+                    }
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+}  // namespace tc
+
+// =================================================================== host side
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)sym;
+    }
+    return fn;
+}
+
+size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+__global__ void __launch_bounds__(256)
+xstage_kernel(const __half* __restrict__ x, int M, int K, long ldx, int Kp, __half* __restrict__ out) {
+    long i = (long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= (long)M * Kp) return;
+    int m = (int)(i / Kp), k = (int)(i - (long)m * Kp);
+    out[i] = (k < K) ? x[(long)m * ldx + k] : __float2half_rn(0.0f);
+}
+
+template <int MT>
+int launch_tc(const CUtensorMap& map, const tc::Params& p, cudaStream_t stream) {
+    using C = tc::Cfg<MT>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        e = cudaFuncSetAttribute(tc::gemm_tc_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemm_tc smem)");
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    dim3 grid((unsigned)((p.N + tc::BN - 1) / tc::BN), (unsigned)((p.M + 128 * MT - 1) / (128 * MT)), 1);
+    tc::gemm_tc_kernel<MT><<<grid, tc::kThreads, C::SMEM, stream>>>(map, p);
+    SX8_LAUNCH_CHECK("gemm_tc_kernel");
+    return SX8_OK;
+}
+
+}  // namespace
+
+// workspace: [PCA table n_cb*128 B][staged x (M, 32*n_cb) f16, only when x is not TMA-addressable]
+size_t gemm_tc_workspace_bytes(int M, int N, int n_cb) {
+    (void)N;
+    return round256((size_t)n_cb * 128) + round256((size_t)M * (size_t)n_cb * 64);
+}
+
+bool gemm_tc_supported(int M, int N, int K, int n_cb) {
+    (void)N; (void)K; (void)n_cb;
+    static const int min_m = getenv("SX8_GEMM_TC_MIN_M") ? atoi(getenv("SX8_GEMM_TC_MIN_M")) : 32;
+    return M >= min_m && encode_fn() != nullptr;
+}
+
+int gemm_tc_launch(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
+                   const float* scales, int N, int n_cb, void* y, int out_f16, void* workspace,
+                   cudaStream_t stream) {
+    __half* pb = (__half*)workspace;
+    tc::pca_table_kernel<<<(unsigned)((n_cb * 64 + 255) / 256), 256, 0, stream>>>(bases, scales, n_cb, pb);
+    SX8_LAUNCH_CHECK("pca_table_kernel");
+    const __half* xp = (const __half*)x;
+    long ld = ldx;
+    int Kx = K;
+    if ((ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x) % 16) != 0) {
+        int Kp = n_cb * 32;
+        __half* xs = (__half*)((uint8_t*)workspace + round256((size_t)n_cb * 128));
+        xstage_kernel<<<(unsigned)(((long)M * Kp + 255) / 256), 256, 0, stream>>>((const __half*)x, M, K, ldx, Kp, xs);
+        SX8_LAUNCH_CHECK("xstage_kernel");
+        xp = xs; ld = Kp; Kx = Kp;
+    }
+    CUtensorMap map;
+    cuuint64_t gdim[2] = {(cuuint64_t)Kx, (cuuint64_t)M};
+    cuuint64_t gstr[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)tc::BK, 128u};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = encode_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)xp, gdim, gstr, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("sx8_gemm: cuTensorMapEncodeTiled failed (%d)", (int)r);
+        return SX8_E_CUDA;
+    }
+    tc::Params p{(const uint8_t*)wt16, pb, y, M, N, n_cb, (int)t16_tiles(N), out_f16};
+    if (M > 128) return launch_tc<2>(map, p, stream);
+    return launch_tc<1>(map, p, stream);
+}
+
+}  // namespace sx8
