@@ -299,9 +299,11 @@ def test_gemv_matches_reference_kernel_build(ops):
     assert (y - Y).abs().max().item() <= TOL_VS_KERNEL_FORMULA * Y.abs().max().item()
 
 
-@pytest.mark.parametrize("M", [9, 16, 33])
+@pytest.mark.parametrize("M", [9, 16, 33, 128, 200, 512])
 @pytest.mark.parametrize("f16out", [False, True])
-def test_gemm_small_m(ops, M, f16out):
+def test_gemm_m_sweep(ops, M, f16out):
+    """M < 32: 8-row passes of the GEMV kernel; M >= 32: the tcgen05 kernel (one or two
+    128-row accumulators, ragged last row tile)."""
     w, qt, bi, v44 = case(1024, 2560, 58)
     x = orc.synth_x(M, 2560, 9)
     y_cmp = orc.matmul_ref(x, orc.dequant_d64(qt, bi))
@@ -311,6 +313,49 @@ def test_gemm_small_m(ops, M, f16out):
     scale = np.abs(y_cmp).max()
     tol = TOL_VS_COMPARATOR + (2.0 ** -10 if f16out else 0.0)
     assert np.abs(y - y_cmp).max() <= tol * scale
+
+
+@pytest.mark.parametrize("shape,M", [((136, 1000), 130), ((48, 80), 64), ((4096, 2560), 256), ((2560, 4096), 1000),
+                                     ((60, 64), 33)])
+def test_gemm_shapes(ops, shape, M):
+    """tcgen05 path: ragged N (partial 256-column tile, N not a multiple of 16), K not a
+    multiple of 64 or 32 (zero-filled K tail), odd number of block rows."""
+    w, qt, bi, v44 = case(shape[0], shape[1], 60)
+    x = orc.synth_x(M, shape[1], 10)
+    y_cmp = orc.matmul_ref(x, orc.dequant_d64(qt, bi))
+    wt, b, s = t16_dev(qt, v44)
+    y = ops.gemm(dev(x), wt, b, s, shape[0], shape[1], qt["n_cb"]).cpu().numpy()
+    assert np.isfinite(y).all()
+    assert np.abs(y - y_cmp).max() <= TOL_VS_COMPARATOR * np.abs(y_cmp).max()
+
+
+def test_gemm_matches_reference_kernels_build(ops):
+    """Against the reference's own GEMM kernels (CUDA-core compact and WMMA) built in
+    oracle/_ref, on the layouts they expect."""
+    from oracle import build
+    ref_c = build.load_ref("ref_sx8_gemm_compact")
+    if ref_c is None:
+        pytest.skip("oracle/_ref not built")
+    w, qt, bi, v44 = case(1024, 2560, 61)
+    x = dev(orc.synth_x(128, 2560, 11))
+    h, l, b, s = v44_dev(v44)
+    Z = ref_c.compute_z44_batch(x, b, s, qt["n_cb"])
+    y_ref = ref_c.gemm_compact(x, h, l, Z, qt["n_cb"], 6)
+    wt, _, _ = t16_dev(qt, v44)
+    y = ops.gemm(x, wt, b, s, 1024, 2560, qt["n_cb"])
+    torch.cuda.synchronize()
+    assert (y - y_ref).abs().max().item() <= TOL_VS_COMPARATOR * y_ref.abs().max().item()
+
+
+def test_gemm_deterministic(ops):
+    w, qt, bi, v44 = case(1024, 2560, 58)
+    x = dev(orc.synth_x(300, 2560, 12))
+    wt, b, s = t16_dev(qt, v44)
+    y1 = ops.gemm(x, wt, b, s, 1024, 2560, qt["n_cb"]).clone()
+    y2 = ops.gemm(x, wt, b, s, 1024, 2560, qt["n_cb"]).clone()
+    assert torch.equal(y1, y2)
+    from sx8_quantization_b200 import _lib
+    assert _lib.device_error_flag() == 0
 
 
 def test_argument_errors_raise(ops):
