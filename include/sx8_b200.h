@@ -81,6 +81,22 @@ int sx8_gemm(const void* x_f16, int M, int K, long ldx, const void* wt16, const 
              const float* scales, int N, int n_cb, void* y, int out_f16, void* workspace,
              size_t workspace_bytes, void* stream);
 
+/* ---- prefill GEMM without any workspace -------------------------------------------
+ * No counterpart in the reference.  For callers that are not allowed to allocate device
+ * memory while running (a server that gave all of its memory to its own arena at
+ * start-up, a plug-in host that bans cudaMalloc in plug-ins): same result as sx8_gemm's
+ * tensor-core path, but the kernel's scratch lives in a fixed 128 KB array inside the
+ * library (held on every GPU that loads the library until the process exits), so the
+ * caller passes inputs and outputs only and the call allocates nothing.
+ * Limits: n_cb <= sx8_gemm_static_max_ncb() (1024, i.e. K <= 32768), x 16-byte aligned
+ * with ldx a multiple of 8; anything else is rejected with SX8_E_INVALID and a message.
+ * The array is shared by all calls: calls that overlap on the GPU race on it, so order
+ * them (one stream, or events).  The first call on each device looks up the array's
+ * device address; make that call before any stream capture begins.                   */
+size_t sx8_gemm_static_max_ncb(void);
+int sx8_gemm_static(const void* x_f16, int M, int K, long ldx, const void* wt16, const float* bases,
+                    const float* scales, int N, int n_cb, void* y, int out_f16, void* stream);
+
 /* ---- embedding rows ---------------------------------------------------------------
  * out[t, 0..K) = f16(decode(row ids[t])) in the reference kernel's float32 arithmetic.
  * Replaces ref: cuda/sx8_embed_v44.cu:80-94 (sx8_embed_v44).  ids: (T) int64 on the

@@ -18,6 +18,8 @@ SIGNATURES = {
     "sx8_gemv": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _i, _i, _vp, _vp, _sz, _u, _vp]),
     "sx8_gemm_workspace_bytes": (_sz, [_i, _i, _i]),
     "sx8_gemm": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _sz, _vp]),
+    "sx8_gemm_static_max_ncb": (_sz, []),
+    "sx8_gemm_static": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _i, _i, _vp, _i, _vp]),
     "sx8_embed": (_i, [_vp, _l, _vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "sx8_dequant_planes": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _l, _l, _i, _i, _vp, _vp]),
     "sx8_dequant_t16": (_i, [_vp, _vp, _vp, _l, _l, _i, _i, _vp, _vp]),

@@ -485,3 +485,93 @@ int gemm_tc_launch(const void* x, int M, int K, long ldx, const void* wt16, cons
 }
 
 }  // namespace sx8
+
+// =================================================================== allocation-free variant
+// sx8_gemm_static: the tensor-core GEMM with its scratch (the fp16 PCA table) held in a
+// fixed array inside the library image instead of a caller-supplied workspace.  Meant for
+// hosts that may not allocate device memory at all once they are running -- a serving
+// process that handed its whole memory budget to its own arena at start-up, or a plug-in
+// host that forbids cudaMalloc in plug-ins because an allocation synchronises the device
+// and can fail late.  Such a caller passes inputs and outputs only.
+//
+// The array costs kStaticPcaBytes of device memory on every GPU that loads the library,
+// until the process exits.  It is shared by every call and keeps the previous call's
+// contents; each call rewrites the part it uses (n_cb * 128 bytes) before reading it, so
+// nothing has to start at zero -- but two calls that overlap on the GPU (different
+// streams, or different threads) would overwrite each other's table: callers must order
+// them.  The device address of the array is looked up once per device by the first call
+// made with that device current; make that first call before starting any stream capture.
+namespace sx8 {
+namespace {
+
+constexpr int kStaticMaxNcb = 1024;                       // K <= 32768
+constexpr size_t kStaticPcaBytes = (size_t)kStaticMaxNcb * 128;
+static __device__ __align__(256) unsigned char g_static_pca[kStaticPcaBytes];
+
+// In host code `g_static_pca` is only a handle for the runtime, not a device address:
+// the address is obtained per device with cudaGetSymbolAddress and cached.
+int static_pca_ptr(__half** out) {
+    static void* cache[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64) {
+        set_error("sx8_gemm_static: device index %d out of range", dev);
+        return SX8_E_UNSUPPORTED;
+    }
+    if (!cache[dev]) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_pca);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static PCA table)");
+        cache[dev] = ptr;
+    }
+    *out = (__half*)cache[dev];
+    return SX8_OK;
+}
+
+}  // namespace
+}  // namespace sx8
+
+extern "C" size_t sx8_gemm_static_max_ncb(void) { return (size_t)sx8::kStaticMaxNcb; }
+
+extern "C" int sx8_gemm_static(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
+                               const float* scales, int N, int n_cb, void* y, int out_f16, void* stream_) {
+    using namespace sx8;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    SX8_REQUIRE(x && wt16 && bases && scales && y, "sx8_gemm_static: null pointer");
+    SX8_REQUIRE(M >= 1 && N > 0 && K > 0 && n_cb == (K + 31) / 32,
+                "sx8_gemm_static: need M>=1, N>0, K>0, n_cb == ceil(K/32) (got M=%d N=%d K=%d n_cb=%d)", M, N, K, n_cb);
+    SX8_REQUIRE(n_cb <= kStaticMaxNcb,
+                "sx8_gemm_static: n_cb=%d exceeds the built-in scratch (max n_cb %d, i.e. K <= %d); use sx8_gemm "
+                "with a caller workspace", n_cb, kStaticMaxNcb, kStaticMaxNcb * 32);
+    SX8_REQUIRE(ldx >= K && (ldx % 8) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0,
+                "sx8_gemm_static: x must be 16-byte aligned with a row stride that is a multiple of 8 elements "
+                "(no scratch is available to stage it); got ldx=%ld", ldx);
+    SX8_REQUIRE((reinterpret_cast<uintptr_t>(wt16) % 16) == 0 && (reinterpret_cast<uintptr_t>(bases) % 4) == 0 &&
+                    (reinterpret_cast<uintptr_t>(y) % (out_f16 ? 2 : 4)) == 0,
+                "sx8_gemm_static: misaligned wt16 / bases / y");
+    if (!encode_fn()) {
+        set_error("sx8_gemm_static: the driver does not provide cuTensorMapEncodeTiled");
+        return SX8_E_UNSUPPORTED;
+    }
+    __half* pb = nullptr;
+    int rc = static_pca_ptr(&pb);
+    if (rc != SX8_OK) return rc;
+    tc::pca_table_kernel<<<(unsigned)((n_cb * 64 + 255) / 256), 256, 0, stream>>>(bases, scales, n_cb, pb);
+    SX8_LAUNCH_CHECK("pca_table_kernel");
+    CUtensorMap map;
+    cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    cuuint64_t gstr[1] = {(cuuint64_t)ldx * 2};
+    cuuint32_t box[2] = {(cuuint32_t)tc::BK, 128u};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = encode_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), gdim, gstr, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("sx8_gemm_static: cuTensorMapEncodeTiled failed (%d)", (int)r);
+        return SX8_E_CUDA;
+    }
+    tc::Params p{(const uint8_t*)wt16, pb, y, M, N, n_cb, (int)t16_tiles(N), out_f16};
+    if (M > 128) return launch_tc<2>(map, p, stream);
+    return launch_tc<1>(map, p, stream);
+}
