@@ -72,6 +72,11 @@ int sx8_gemv(const void* x_f16, int M, int K, long ldx, const void* wt16, const 
              const float* scales, int N, int n_cb, float* y, void* workspace,
              size_t workspace_bytes, unsigned flags, void* stream);
 
+/* Tuning hook for experiments: force the GEMV's tile-group width (nt = 2, 4 or 8 tiles of 16
+ * columns), cluster split-K (1..8) and persistent grid size; 0 = automatic, -1 = take the
+ * SX8_GEMV_NT / SX8_GEMV_SPLIT / SX8_GEMV_GRID environment variables.  Process-wide.       */
+void sx8_gemv_tune(int nt, int split, int grid);
+
 /* ---- prefill GEMM, any M ----------------------------------------------------------
  * Y (M, N) = X (M, K) * W^T, fp32 accumulate; out_f16 != 0 writes Y as f16, else f32.
  * Replaces ref: cuda/sx8_gemm_compact.cu:157-194 (compute_z44_batch, gemm_compact) and

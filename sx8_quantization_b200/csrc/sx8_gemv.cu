@@ -474,35 +474,46 @@ struct Choice {
     int nt, split, grid_x;
 };
 
+int g_tune_nt = -1, g_tune_split = -1, g_tune_grid = -1;   // -1: take the environment / automatic choice
+
 int env_int(const char* name) {
     const char* v = getenv(name);
     return v ? atoi(v) : 0;
 }
 
-// Tile-group width NT (x16 columns), cluster split-K and grid size.  Large N: 128-column
-// CTAs, no split, a persistent grid of 3 CTAs per SM that loops over tile groups.
-// Otherwise the (NT, split) whose CTA count fills whole multiples of the SM count best.
+// Tile-group width NT (x16 columns), cluster split-K and grid size.  Measured on B200 over the
+// Qwen3-4B- and Llama-70B-shaped projections (and their tensor-parallel shards): the best
+// configurations put about 384 CTAs in flight per wave (3 CTAs per SM hold 444; ~2.6 per SM
+// leaves room for the next launch's prefetching CTAs), prefer wide tile groups, and use as
+// little split-K as that allows.  Very large N runs a persistent grid without split-K.
 Choice choose(int N, int n_cb) {
-    static const int f_nt = env_int("SX8_GEMV_NT"), f_split = env_int("SX8_GEMV_SPLIT"),
-                     f_grid = env_int("SX8_GEMV_GRID");
+    static const int e_nt = env_int("SX8_GEMV_NT"), e_split = env_int("SX8_GEMV_SPLIT"),
+                     e_grid = env_int("SX8_GEMV_GRID");
+    const int f_nt = g_tune_nt >= 0 ? g_tune_nt : e_nt, f_split = g_tune_split >= 0 ? g_tune_split : e_split,
+              f_grid = g_tune_grid >= 0 ? g_tune_grid : e_grid;
     const int n_tiles = (int)t16_tiles(N);
     const int min_split = (n_cb + kMaxKbPerCta - 1) / kMaxKbPerCta;
     Choice best{8, min_split, 0};
-    double best_score = -1.0;
+    double best_score = -1e30;
     const int nts[3] = {8, 4, 2};
+    const double nt_pen[3] = {0.0, 0.02, 0.08};
     for (int a = 0; a < 3; a++) {
         int nt = nts[a];
         if (f_nt && nt != f_nt) continue;
         int groups = (n_tiles + nt - 1) / nt;
         for (int split = min_split; split <= 8; split++) {
             if (f_split && split != f_split) continue;
-            if (split > 1 && n_cb / split < 4) break;
+            if (split > min_split && n_cb / split < 4) break;
             long ctas = (long)groups * split;
-            double fill = (double)ctas / ((double)((ctas + kSMs - 1) / kSMs) * kSMs);
-            if (ctas > 4L * kSMs && !(nt == 8 && split == min_split)) fill *= 0.5;  // more than 4 waves of work units
-            if (nt == 8 && split == 1 && ctas >= 2 * kSMs) fill = 1.0;             // persistent grid: always balanced
-            double score = fill + 0.02 * nt - 0.015 * split;
-            if (ctas < kSMs) score -= 1.0;
+            double score;
+            if (nt == 8 && split == 1 && groups >= 6 * kSMs) {
+                score = 1.0;   // persistent grid, balanced by construction
+            } else {
+                long waves = (ctas + 3 * kSMs - 1) / (3 * kSMs);
+                double per_wave = (double)ctas / (double)waves;
+                double dev = per_wave > 384.0 ? (per_wave - 384.0) / 384.0 : (384.0 - per_wave) / 384.0;
+                score = -(dev + 0.03 * (double)(waves - 1) + nt_pen[a] + 0.005 * split);
+            }
             if (score > best_score) {
                 best_score = score;
                 best = Choice{nt, split, 0};
@@ -562,6 +573,12 @@ int launch_gemv(const GemvParams& p, int grid_x, unsigned flags, cudaStream_t st
 }
 
 }  // namespace
+
+extern "C" void sx8_gemv_tune(int nt, int split, int grid) {
+    g_tune_nt = nt;
+    g_tune_split = split;
+    g_tune_grid = grid;
+}
 
 extern "C" size_t sx8_gemv_workspace_bytes(int n_cb, int M) {
     if (n_cb <= 0 || M <= 0) return 0;
