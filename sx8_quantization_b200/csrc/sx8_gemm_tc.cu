@@ -8,7 +8,7 @@
 //   warp 1      issuer   : one thread issues tcgen05.mma (M=128, N=256, K=16, kind::f16) on
 //                          shared-memory descriptors; accumulators live in TMEM (256 columns
 //                          per 128-row tile); tcgen05.commit releases the stages
-//   warps 2..9  decoders : bit-extract 6-bit levels from the packed slab, form fp16 weights
+//   warps 2..17 decoders : bit-extract 6-bit levels from the packed slab, form fp16 weights
 //                          w = dmin + base*(mult*level + 63*off) + c0*s0*b0[t] + c1*s1*b1[t]
 //                          (the arithmetic of ref cuda/sx8_fused_wmma.cu:83-96, in fp16 pairs)
 //                          and store them as the K-major, 128-byte-swizzled B operand tile;
@@ -25,7 +25,7 @@ namespace sx8 {
 namespace tc {
 
 constexpr int BN = 256, BK = 64, KB_STAGE = 2;
-constexpr int kWarps = 10, kThreads = kWarps * 32, kDecodeWarps = 8;
+constexpr int kDecodeWarps = 16, kWarps = kDecodeWarps + 2, kThreads = kWarps * 32;
 constexpr int A_TILE = 128 * 128;                 // 128 rows x 64 fp16, bytes
 constexpr int B_TILE = BN * 128;                  // 256 rows x 64 fp16
 constexpr int P_SLAB = 16 * KB_STAGE * T16_UNIT;  // 16 tiles x 2 kb
@@ -153,11 +153,19 @@ struct Params {
     const __half* pb;
     void* y;
     int M, N, n_cb, n_tiles, out_f16;
+    int tma_store;   // Y rows are 16-byte multiples: the epilogue stores through the Y tensor map
 };
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(src) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
 
 template <int MT>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, Params p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap, Params p) {
     using C = Cfg<MT>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -249,7 +257,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, Params p) {
         }
     } else {
         // ------------------------------------------------------------ decoders
-        const int dw = warp - 2;                 // 0..7: tiles dw and dw + 8 of the CTA's 16
+        const int dw = warp - 2;                 // 0..15: tile dw of the CTA's 16
         const int g = lane >> 2, t = lane & 3;
         const uint32_t sh2 = 8u + 2u * (uint32_t)t;
         const float kBase = 0.25f * 0.015873f * 512.0f;   // levels are formed scaled by 2^-9
@@ -260,11 +268,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, Params p) {
             if (ok) ok = mbar_wait(p_full + 8 * sp, (ks / C::SP) & 1, 0x100u);
             if (ks >= C::SB && ok) ok = mbar_wait(b_empty + 8 * sb, ((ks / C::SB) - 1) & 1, 0x200u);
             const uint32_t pst = sP + sp * P_STAGE, bst = sB + sb * B_TILE;
-#pragma unroll
-            for (int ti = 0; ti < 2; ti++) {
-                const int tl = dw + ti * 8;
+            {
+                const int tl = dw;
                 const bool tile_ok = tile0 + tl < p.n_tiles;
-                const uint32_t rowA = (uint32_t)(tl * 16 + g), rowB = rowA + 8;
+                // Column 16*tl + g sits in operand row 16*tl + rho(g), rho(g) = 4*(g&1) + (g>>1): the
+                // eight lanes of a quarter-warp then store to eight different 16-byte bank groups.
+                // The epilogue undoes the permutation when it reads the accumulator columns.
+                const uint32_t rowA = (uint32_t)(tl * 16 + (((g & 1) << 2) | (g >> 1))), rowB = rowA + 8;
 #pragma unroll
                 for (int r = 0; r < KB_STAGE; r++) {
                     uint4 wa = make_uint4(0u, 0u, 0u, 0u), wb = wa;
@@ -334,49 +344,80 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, Params p) {
         if (ok) ok = mbar_wait(acc_full, 0u, 0x400u);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int quarter = warp & 3;            // TMEM lanes 32*quarter .. +31 are this warp's
-        const int half = dw >> 2;                // the two warps of a quarter split the columns
+        const int part = dw >> 2;                // the four warps of a quarter split the 256 columns
+        // Staging for the TMA store: 4 KB per warp in the (now idle) B stages; rows of 128 bytes,
+        // 16-byte chunks XOR-swizzled with the row index (the Y tensor map uses the same swizzle).
+        const uint32_t stg = sB + (uint32_t)dw * 4096u;
 #pragma unroll 1
         for (int mt = 0; mt < MT; mt++) {
-            const long m = (long)m0 + mt * 128 + quarter * 32 + lane;
-#pragma unroll 1
-            for (int cc = 0; cc < 4; cc++) {
-                const int col = half * 128 + cc * 32;
-                uint32_t v[32];
+            const int mrow0 = m0 + mt * 128 + quarter * 32;
+            const long m = (long)mrow0 + lane;
+            if (p.tma_store && p.out_f16) {
+                // one 64-column x 32-row box of fp16 per accumulator
+                uint32_t v[32], w[32];
+                const int col = part * 64;
                 tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BN + col), v);
-                if (m < p.M) {
-                    const int n = n0 + col;
-                    if (p.out_f16) {
-                        __half* dst = reinterpret_cast<__half*>(p.y) + m * p.N + n;
-                        if (n + 32 <= p.N && (p.N % 8) == 0) {
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BN + col + 32), w);
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                __syncwarp();
+                uint32_t h[32];
 #pragma unroll
-                            for (int q = 0; q < 4; q++) {
-                                uint4 o;
-                                __half2 h0 = __floats2half2_rn(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1]));
-                                __half2 h1 = __floats2half2_rn(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
-                                __half2 h2 = __floats2half2_rn(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
-                                __half2 h3 = __floats2half2_rn(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
-                                o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
-                                o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
-                                *reinterpret_cast<uint4*>(dst + 8 * q) = o;
-                            }
-                        } else {
-                            for (int q = 0; q < 32; q++)
-                                if (n + q < p.N) dst[q] = __float2half_rn(__uint_as_float(v[q]));
+                for (int c = 0; c < 32; c += 2) {
+                    // inverse of col_of on the 8-group: accumulator index of output column c
+                    const int a0 = (c & ~7) | ((((c & 7) & 1) << 2) | ((c & 7) >> 1));
+                    const int a1 = ((c + 1) & ~7) | (((((c + 1) & 7) & 1) << 2) | (((c + 1) & 7) >> 1));
+                    __half2 lo = __floats2half2_rn(__uint_as_float(v[a0]), __uint_as_float(v[a1]));
+                    __half2 hi = __floats2half2_rn(__uint_as_float(w[a0]), __uint_as_float(w[a1]));
+                    h[c / 2] = *reinterpret_cast<uint32_t*>(&lo);
+                    h[16 + c / 2] = *reinterpret_cast<uint32_t*>(&hi);
+                }
+#pragma unroll
+                for (int q = 0; q < 8; q++)
+                    sts128(stg + lane * 128 + (((uint32_t)q ^ ((uint32_t)lane & 7u)) << 4),
+                           make_uint4(h[4 * q], h[4 * q + 1], h[4 * q + 2], h[4 * q + 3]));
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) tma_store_2d(&ymap, stg, n0 + col, mrow0);
+            } else {
+#pragma unroll 1
+                for (int cc = 0; cc < 2; cc++) {
+                    const int col = part * 64 + cc * 32;
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BN + col), v);
+                    if (p.tma_store) {
+                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // staging free again
+                        __syncwarp();
+#pragma unroll
+                        for (int q = 0; q < 8; q++) {
+                            // output columns 4q..4q+3 <- accumulator columns rho(g) of the same 8-group
+                            const int c0 = 4 * q;
+                            const int a0 = (c0 & ~7) | ((((c0 & 7) & 1) << 2) | ((c0 & 7) >> 1));
+                            const int a1 = ((c0 + 1) & ~7) | (((((c0 + 1) & 7) & 1) << 2) | (((c0 + 1) & 7) >> 1));
+                            const int a2 = ((c0 + 2) & ~7) | (((((c0 + 2) & 7) & 1) << 2) | (((c0 + 2) & 7) >> 1));
+                            const int a3 = ((c0 + 3) & ~7) | (((((c0 + 3) & 7) & 1) << 2) | (((c0 + 3) & 7) >> 1));
+                            sts128(stg + lane * 128 + (((uint32_t)q ^ ((uint32_t)lane & 7u)) << 4),
+                                   make_uint4(v[a0], v[a1], v[a2], v[a3]));
                         }
-                    } else {
-                        float* dst = reinterpret_cast<float*>(p.y) + m * p.N + n;
-                        if (n + 32 <= p.N && (p.N % 4) == 0) {
-#pragma unroll
-                            for (int q = 0; q < 8; q++)
-                                *reinterpret_cast<uint4*>(dst + 4 * q) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                        } else {
-                            for (int q = 0; q < 32; q++)
-                                if (n + q < p.N) dst[q] = __uint_as_float(v[q]);
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) tma_store_2d(&ymap, stg, n0 + col, mrow0);
+                    } else if (m < p.M) {
+                        // rows of Y are not 16-byte multiples: plain guarded stores
+                        const int n = n0 + col;
+                        for (int c = 0; c < 32; c++) {
+                            const int a = (c & ~7) | ((((c & 7) & 1) << 2) | ((c & 7) >> 1));
+                            if (n + c < p.N) {
+                                if (p.out_f16)
+                                    reinterpret_cast<__half*>(p.y)[m * p.N + n + c] = __float2half_rn(__uint_as_float(v[a]));
+                                else
+                                    reinterpret_cast<float*>(p.y)[m * p.N + n + c] = __uint_as_float(v[a]);
+                            }
                         }
                     }
                 }
             }
         }
+        if (p.tma_store && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     __syncthreads();
@@ -419,8 +460,26 @@ xstage_kernel(const __half* __restrict__ x, int M, int K, long ldx, int Kp, __ha
     out[i] = (k < K) ? x[(long)m * ldx + k] : __float2half_rn(0.0f);
 }
 
+// Tensor map of Y for the epilogue's TMA stores: boxes of 32 rows x 128 bytes (32 f32 or 64 f16
+// columns), 128-byte swizzle.  Returns false when Y's rows are not 16-byte multiples.
+bool make_ymap(CUtensorMap* map, void* y, int M, int N, int out_f16) {
+    const size_t es = out_f16 ? 2 : 4;
+    if (((size_t)N * es) % 16 != 0 || (reinterpret_cast<uintptr_t>(y) % 16) != 0) return false;
+    cuuint64_t gdim[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    cuuint64_t gstr[1] = {(cuuint64_t)N * es};
+    cuuint32_t box[2] = {out_f16 ? 64u : 32u, 32u};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = encode_fn()(map, out_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, y,
+                             gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 template <int MT>
-int launch_tc(const CUtensorMap& map, const tc::Params& p, cudaStream_t stream) {
+int launch_tc(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
+    CUtensorMap ymap;
+    memset(&ymap, 0, sizeof(ymap));
+    p.tma_store = make_ymap(&ymap, p.y, p.M, p.N, p.out_f16) ? 1 : 0;
     using C = tc::Cfg<MT>;
     static bool attr_set[64] = {};
     int dev = 0;
@@ -432,7 +491,7 @@ int launch_tc(const CUtensorMap& map, const tc::Params& p, cudaStream_t stream) 
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
     dim3 grid((unsigned)((p.N + tc::BN - 1) / tc::BN), (unsigned)((p.M + 128 * MT - 1) / (128 * MT)), 1);
-    tc::gemm_tc_kernel<MT><<<grid, tc::kThreads, C::SMEM, stream>>>(map, p);
+    tc::gemm_tc_kernel<MT><<<grid, tc::kThreads, C::SMEM, stream>>>(map, ymap, p);
     SX8_LAUNCH_CHECK("gemm_tc_kernel");
     return SX8_OK;
 }
@@ -479,7 +538,7 @@ int gemm_tc_launch(const void* x, int M, int K, long ldx, const void* wt16, cons
         set_error("sx8_gemm: cuTensorMapEncodeTiled failed (%d)", (int)r);
         return SX8_E_CUDA;
     }
-    tc::Params p{(const uint8_t*)wt16, pb, y, M, N, n_cb, (int)t16_tiles(N), out_f16};
+    tc::Params p{(const uint8_t*)wt16, pb, y, M, N, n_cb, (int)t16_tiles(N), out_f16, 0};
     if (M > 128) return launch_tc<2>(map, p, stream);
     return launch_tc<1>(map, p, stream);
 }
@@ -571,7 +630,7 @@ extern "C" int sx8_gemm_static(const void* x, int M, int K, long ldx, const void
         set_error("sx8_gemm_static: cuTensorMapEncodeTiled failed (%d)", (int)r);
         return SX8_E_CUDA;
     }
-    tc::Params p{(const uint8_t*)wt16, pb, y, M, N, n_cb, (int)t16_tiles(N), out_f16};
+    tc::Params p{(const uint8_t*)wt16, pb, y, M, N, n_cb, (int)t16_tiles(N), out_f16, 0};
     if (M > 128) return launch_tc<2>(map, p, stream);
     return launch_tc<1>(map, p, stream);
 }
