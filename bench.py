@@ -236,6 +236,10 @@ def run_single(args):
                                "GBps": round(tensor_bytes(group[0]) / us / 1e3, 1),
                                "resident_copies": len(group)}
 
+    # ---- the other rows of the hot path (BASELINE configs 2 and 4): prefill GEMM, quantizer,
+    #      embedding rows, full-tensor decode -- short device-timed loops, reported as extras
+    extras = {} if args.no_extras else other_kernels(dev, layers[0], head, fam)
+
     # ---- e2e: the drop-in wrapper with pinned host buffers, copies inside the timed region
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
     xh = {k: v.cpu().pin_memory() for k, v in xs.items()}
@@ -291,10 +295,64 @@ def run_single(args):
                 "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps,
                 "api": "sx8_decode1_v3.decode1_v44 with pinned host x and y"},
         "clocks": clocks,
+        "other_kernels": extras,
     }
     if not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(budget_s=args.cpu_seconds)
     print(json.dumps(line))
+
+
+def _time_us(fn, iters=10, warm=3):
+    import torch
+    for _ in range(warm):
+        fn()
+    a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record(); torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e3 / iters
+
+
+def other_kernels(dev, layer0, head, fam):
+    """Prefill GEMM on the gate projection (M = 128 .. 8192, f16 out), quantizer search,
+    embedding gather and full-tensor decode; fractions are of the measured peaks."""
+    import torch
+    from sx8_quantization_b200 import ops, quantizer
+    out = {}
+    pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(
+        os.path.join(ROOT, "MEASURED_PEAKS.json")) else {"bf16_tflops": 1590.0, "hbm_gbs": FALLBACK_HBM_GBS}
+    t = layer0["gate"]
+    g = torch.Generator(device=dev).manual_seed(77)
+    gem = {}
+    for M in (128, 512, 2048, 8192):
+        x = torch.randn(M, t["K"], generator=g, device=dev).half()
+        y = torch.empty(M, t["N"], dtype=torch.float16, device=dev)
+        us = _time_us(lambda: ops.gemm(x, t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"],
+                                       out_dtype=torch.float16, out=y))
+        tf = 2.0 * M * t["N"] * t["K"] / us / 1e6
+        gem[str(M)] = {"us": round(us, 1), "TFLOPs": round(tf, 1), "frac_of_bf16_burst": round(tf / pk["bf16_tflops"], 3)}
+        del x, y
+    out["prefill_gemm_gate_9728x2560"] = gem
+    w = quantizer.synth_weight_gpu(t["N"], t["K"], 4242, dev)
+    us = _time_us(lambda: ops.quantize_blocks(w))
+    n_blk = t["N"] * t["n_cb"]
+    out["quantizer_search"] = {"us": round(us, 1), "Mblocks_per_s": round(n_blk / us, 1),
+                               "GBps_in_plus_out": round(n_blk * (64 + 29) / us / 1e3, 1),
+                               "frac_of_hbm": round(n_blk * (64 + 29) / us / 1e3 / pk["hbm_gbs"], 3)}
+    us = _time_us(lambda: quantizer.quantize_tensor(w, with_pca=True), iters=3, warm=1)
+    out["quantizer_full_with_pca"] = {"us": round(us, 1), "Mblocks_per_s": round(n_blk / us, 1)}
+    del w
+    ids = torch.randint(0, head["N"], (512,), generator=g, device=dev)
+    o = torch.empty(512, head["K"], dtype=torch.float16, device=dev)
+    us = _time_us(lambda: ops.embed(ids, head["wt16"], head["bases"], head["scales"], head["K"], head["N"],
+                                    head["n_cb"], out=o))
+    out["embed_512_rows"] = {"us": round(us, 1), "GBps": round(512 * head["K"] * (30 / 32 + 2) / us / 1e3, 1)}
+    us = _time_us(lambda: ops.dequant_t16(t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"], True))
+    out["dequant_gate"] = {"us": round(us, 1), "GBps": round(n_blk * (30 + 64) / us / 1e3, 1),
+                           "frac_of_hbm": round(n_blk * (30 + 64) / us / 1e3 / pk["hbm_gbs"], 3)}
+    return out
 
 
 # ------------------------------------------------------------------------- CPU legs
@@ -501,6 +559,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extras", action="store_true", help="skip the GEMM / quantizer / embed / dequant extras")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--e2e-steps", type=int, default=10)
     args = ap.parse_args()
