@@ -542,10 +542,32 @@ def run_tp(args, rank, world, local_rank):
             "e2e": None,
             "clocks": clocks,
         }
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
+    # Tear-down: drop the captured graphs (they hold NCCL kernels) before leaving, and leave
+    # with a hard exit after a last barrier -- destroying the NCCL communicator while graphs
+    # that captured its collectives are still alive can block forever.
+    graphs.clear()
+    torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+
+def _watchdog(seconds):
+    """Abort the process if the whole run takes longer than `seconds` (a hung collective or
+    tear-down must not hold the GPUs)."""
+    import signal
+
+    def _die(signum, frame):
+        sys.stderr.write("bench.py: watchdog expired after %d s, aborting\n" % seconds)
+        sys.stderr.flush()
+        os._exit(3)
+
+    signal.signal(signal.SIGALRM, _die)
+    signal.alarm(int(seconds))
 
 
 def main():
@@ -562,8 +584,10 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMM / quantizer / embed / dequant extras")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--max-seconds", type=int, default=900, help="watchdog for the whole run")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    _watchdog(args.max_seconds)
     if args.impl == "reference":
         return run_reference(args)
     world = int(os.environ.get("WORLD_SIZE", "1"))
