@@ -508,12 +508,43 @@ def run_tp(args, rank, world, local_rank):
         torch.cuda.synchronize()
         t1 = time.monotonic()
     ms_local = e0.elapsed_time(e1) / args.steps
-    tm = torch.tensor([ms_local], device=dev, dtype=torch.float64)
+
+    # ---- e2e: the same pass through the public tp.linear call, activations coming from pinned
+    #      host memory every step and the last projection's result read back
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    xh = {k: v.cpu().pin_memory() for k, v in xs.items()}
+    last = fam["proj"][-1][0]
+    yh = {M: torch.empty(M, layers[0][last]["N"], dtype=torch.float32).pin_memory() for M in batches}
+    h2d = sum(v.numel() * 2 for v in xs.values()) * n_layers
+    d2h = sum(v.numel() * 4 for v in yh.values())
+
+    def e2e_step():
+        for M in batches:
+            for L in layers:
+                for name, _, _, style in fam["proj"]:
+                    xs[(M, name)].copy_(xh[(M, name)], non_blocking=True)
+                    y = tp.linear(xs[(M, name)], L[name], out=ys[(M, name)], flags=flags)
+            yh[M].copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e_step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    b.record(); torch.cuda.synchronize()
+    e2e_ms = a.elapsed_time(b) / e2e_steps
+
+    tm = torch.tensor([ms_local, e2e_ms], device=dev, dtype=torch.float64)
     tb = torch.tensor([float(bytes_rank)], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(tm, op=dist.ReduceOp.MAX)
         dist.all_reduce(tb, op=dist.ReduceOp.SUM)
-    ms_per_step = float(tm.item())
+    ms_per_step = float(tm[0].item())
+    e2e_ms = float(tm[1].item())
     bytes_step = float(tb.item()) * len(batches)
     value = bytes_step / (ms_per_step * 1e-3) / 1e9
     if rank == 0:
@@ -539,7 +570,9 @@ def run_tp(args, rank, world, local_rank):
             "roofline": {"bound": "hbm", "achieved": round(value / world, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(value / world / peak, 4), "traffic": None,
                          "note": "per-GPU packed weight bytes / step wall time incl. all-reduces, of %s peak" % peak_kind},
-            "e2e": None,
+            "e2e": {"value": round(bytes_step / (e2e_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 3),
+                    "steps": e2e_steps, "api": "tp.linear per projection, pinned host activations, NCCL all-reduce"},
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
