@@ -441,15 +441,24 @@ def run_tp(args, rank, world, local_rank):
                 ys[(M, name)] = torch.zeros(M, t["N"], dtype=torch.float32, device=dev)
     ws = ops.Workspace.get(dev, max(t["n_cb"] for L in layers for t in L.values()) * 512)
     flags = 0 if args.no_pdl else ops.SX8_F_PDL
+    exchange = None
+    if world > 1 and args.allreduce == "fused":
+        try:
+            exchange = tp.PeerExchange(8 * fam["hidden"], dev)
+        except Exception as e:
+            if rank == 0:
+                print("peer exchange unavailable, using NCCL:", repr(e)[:300], file=sys.stderr)
+            exchange = None
 
     def one_pass(M):
         for L in layers:
             for name, _, _, style in fam["proj"]:
                 t = L[name]
-                y = ops.gemv(xs[(M, name)], t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"],
-                             out=ys[(M, name)], flags=flags, workspace=ws)
                 if style == "row" and world > 1:
-                    dist.all_reduce(y)
+                    tp.linear(xs[(M, name)], t, out=ys[(M, name)], flags=flags, exchange=exchange)
+                else:
+                    ops.gemv(xs[(M, name)], t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"],
+                             out=ys[(M, name)], flags=flags, workspace=ws)
 
     st = torch.cuda.Stream(device=dev)
     graphs = {}
@@ -523,7 +532,7 @@ def run_tp(args, rank, world, local_rank):
             for L in layers:
                 for name, _, _, style in fam["proj"]:
                     xs[(M, name)].copy_(xh[(M, name)], non_blocking=True)
-                    y = tp.linear(xs[(M, name)], L[name], out=ys[(M, name)], flags=flags)
+                    y = tp.linear(xs[(M, name)], L[name], out=ys[(M, name)], flags=flags, exchange=exchange)
             yh[M].copy_(y, non_blocking=True)
         torch.cuda.synchronize()
 
@@ -560,7 +569,9 @@ def run_tp(args, rank, world, local_rank):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16 x u6 -> f32 accumulate", "data": "synthetic (random-init, quantised on the device)",
             "config": {"workload": "tp_decode_llama70b", "layers": n_layers, "batches": list(batches),
-                       "parallelism": "tp%d" % world, "allreduce": "nccl fp32 sum after o and down",
+                       "parallelism": "tp%d" % world,
+                       "allreduce": ("fused into the GEMV epilogue over peer memory (fp32, rank-ordered sum)"
+                                     if exchange is not None else "nccl fp32 sum") + " after o and down",
                        "packed_bytes_per_layer": full_layer,
                        "l2": "per-rank weights %.0f MB (> L2 when above 126 MB)" % (bytes_rank / 1e6),
                        "cuda_graph": bool(graphs), "pdl": not args.no_pdl},
@@ -617,6 +628,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMM / quantizer / embed / dequant extras")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
+                    help="row-parallel reduction: fused peer-memory exchange or NCCL")
     ap.add_argument("--max-seconds", type=int, default=900, help="watchdog for the whole run")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -72,6 +72,30 @@ int sx8_gemv(const void* x_f16, int M, int K, long ldx, const void* wt16, const 
              const float* scales, int N, int n_cb, float* y, void* workspace,
              size_t workspace_bytes, unsigned flags, void* stream);
 
+/* ---- row-parallel decode GEMV fused with its all-reduce ---------------------------
+ * No counterpart in the reference (it has no multi-GPU code).  One rank of a tensor-parallel
+ * group computes its partial y over its K range; the GEMV's epilogue stores every finished
+ * tile straight into slot `rank` of each peer's receive buffer (plain stores to peer-mapped
+ * memory over NVLink, overlapping the rest of the GEMV) and bumps the peer's arrival counter;
+ * a small second kernel waits -- bounded -- for all ranks' tiles and sums the slots in rank
+ * order (deterministic) into y, which then holds the full sum on every rank.
+ * peers: data[q]  = rank q's receive buffer as mapped in THIS process, 2*world*slot_elems f32
+ *                   (two parities x world slots), 16-byte aligned;
+ *        flags[q] = rank q's four u32 counters {arrive[2], done[2]}, zero before first use;
+ *        parity   = call counter & 1, advanced by the caller on every call that shares the
+ *                   buffers (all ranks make the same calls in the same order);
+ *        slot_elems >= M*N.
+ * All ranks must call with the same shapes.  world == 1 degenerates to sx8_gemv.          */
+typedef struct sx8_peers {
+    void* data[8];
+    void* flags[8];
+    long slot_elems;
+    int rank, world, parity;
+} sx8_peers_t;
+int sx8_gemv_allreduce(const void* x_f16, int M, int K, long ldx, const void* wt16, const float* bases,
+                       const float* scales, int N, int n_cb, float* y, void* workspace,
+                       size_t workspace_bytes, unsigned flags, const sx8_peers_t* peers, void* stream);
+
 /* Tuning hook for experiments: force the GEMV's tile-group width (nt = 2, 4 or 8 tiles of 16
  * columns), cluster split-K (1..8) and persistent grid size; 0 = automatic, -1 = take the
  * SX8_GEMV_NT / SX8_GEMV_SPLIT / SX8_GEMV_GRID environment variables.  Process-wide.       */

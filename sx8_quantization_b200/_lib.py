@@ -16,6 +16,7 @@ SIGNATURES = {
     "sx8_last_error": (ctypes.c_char_p, []),
     "sx8_gemv_workspace_bytes": (_sz, [_i, _i]),
     "sx8_gemv": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _i, _i, _vp, _vp, _sz, _u, _vp]),
+    "sx8_gemv_allreduce": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _i, _i, _vp, _vp, _sz, _u, _vp, _vp]),
     "sx8_gemv_tune": (None, [_i, _i, _i]),
     "sx8_gemm_workspace_bytes": (_sz, [_i, _i, _i]),
     "sx8_gemm": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _sz, _vp]),
@@ -32,6 +33,12 @@ SIGNATURES = {
 }
 
 SX8_F_PDL = 1
+
+
+class Peers(ctypes.Structure):
+    """sx8_peers_t of include/sx8_b200.h."""
+    _fields_ = [("data", ctypes.c_void_p * 8), ("flags", ctypes.c_void_p * 8), ("slot_elems", ctypes.c_long),
+                ("rank", ctypes.c_int), ("world", ctypes.c_int), ("parity", ctypes.c_int)]
 
 
 class SX8Error(RuntimeError):

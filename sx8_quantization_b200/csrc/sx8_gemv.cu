@@ -31,6 +31,8 @@
 #include "sx8_common.cuh"
 #include "sx8_layout.cuh"
 
+#define SX8_MAX_PEERS 8
+
 namespace sx8 {
 
 constexpr int kConsumerWarps = 8;
@@ -163,7 +165,32 @@ struct GemvParams {
     long ldx;
     int N, n_cb, M, split, n_tiles, groups;
     int debug;   // bit 0: consumers skip the math (pipeline-only timing experiments)
+    // Row-parallel exchange (world > 1): instead of y, every finished tile is stored into slot
+    // `rank` of each peer's receive buffer (peer memory, plain stores over NVLink), then a
+    // per-peer arrival counter is bumped; reduce_peers_kernel sums the slots.
+    float* peer_data[SX8_MAX_PEERS];       // base of each rank's receive buffer (this parity)
+    unsigned* peer_flag[SX8_MAX_PEERS];    // each rank's arrival counter (this parity)
+    long slot_elems;                       // elements per slot
+    int rank, world;
 };
+
+// Stores one finished value, locally or into every peer's slot.
+__device__ __forceinline__ void put_out(const GemvParams& p, long idx, float v) {
+    if (p.world <= 1) {
+        p.y[idx] = v;
+    } else {
+#pragma unroll 1
+        for (int q = 0; q < p.world; q++) p.peer_data[q][(long)p.rank * p.slot_elems + idx] = v;
+    }
+}
+// After a warp has stored a whole tile: make the stores visible system-wide, then count the
+// tile on every peer (lane q signals peer q).
+__device__ __forceinline__ void signal_tile(const GemvParams& p, int lane) {
+    if (p.world <= 1) return;
+    __threadfence_system();
+    __syncwarp();
+    if (lane < p.world) atomicAdd_system(p.peer_flag[lane], 1u);
+}
 
 template <int NT, int KB_S, int STAGES>
 struct GemvCfg {
@@ -398,13 +425,14 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
                 int nA = (grp * NT + ti) * 16 + g, nB = nA + 8, m0 = 2 * t, m1 = m0 + 1;
                 float v0 = accF[0] + accD[0], v1 = accF[1] + accD[1], v2 = accF[2] + accD[2], v3 = accF[3] + accD[3];
                 if (nA < p.N) {
-                    if (m0 < p.M) p.y[(long)m0 * p.N + nA] = v0;
-                    if (m1 < p.M) p.y[(long)m1 * p.N + nA] = v1;
+                    if (m0 < p.M) put_out(p, (long)m0 * p.N + nA, v0);
+                    if (m1 < p.M) put_out(p, (long)m1 * p.N + nA, v1);
                 }
                 if (nB < p.N) {
-                    if (m0 < p.M) p.y[(long)m0 * p.N + nB] = v2;
-                    if (m1 < p.M) p.y[(long)m1 * p.N + nB] = v3;
+                    if (m0 < p.M) put_out(p, (long)m0 * p.N + nB, v2);
+                    if (m1 < p.M) put_out(p, (long)m1 * p.N + nB, v3);
                 }
+                if (grp * NT + ti < p.n_tiles) signal_tile(p, lane);
 #pragma unroll
                 for (int i = 0; i < 4; i++) accF[i] = accD[i] = 0.f;
             }
@@ -451,12 +479,50 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
         int nA = ((int)blockIdx.x * NT + warp) * 16 + g, nB = nA + 8;
         int m0 = 2 * t, m1 = 2 * t + 1;
         if (nA < p.N) {
-            if (m0 < p.M) p.y[(long)m0 * p.N + nA] = accF[0];
-            if (m1 < p.M) p.y[(long)m1 * p.N + nA] = accF[1];
+            if (m0 < p.M) put_out(p, (long)m0 * p.N + nA, accF[0]);
+            if (m1 < p.M) put_out(p, (long)m1 * p.N + nA, accF[1]);
         }
         if (nB < p.N) {
-            if (m0 < p.M) p.y[(long)m0 * p.N + nB] = accF[2];
-            if (m1 < p.M) p.y[(long)m1 * p.N + nB] = accF[3];
+            if (m0 < p.M) put_out(p, (long)m0 * p.N + nB, accF[2]);
+            if (m1 < p.M) put_out(p, (long)m1 * p.N + nB, accF[3]);
+        }
+        if ((int)blockIdx.x * NT + warp < p.n_tiles) signal_tile(p, lane);
+    }
+}
+
+// Second half of the row-parallel exchange: waits (bounded) until every rank has delivered all
+// of its tiles into this rank's slots, then sums the slots in rank order -- deterministic --
+// into y.  The last CTA to finish re-arms the arrival counter for the call after next (the
+// buffers alternate between two parities, and no rank can run two calls ahead of a peer).
+__global__ void __launch_bounds__(256)
+reduce_peers_kernel(const float* __restrict__ slots, unsigned* flag, unsigned* done, float* __restrict__ y,
+                    long n_elems, long slot_elems, int world, unsigned expected) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // this rank's own GEMV has finished
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) {
+        int ok = 0;
+        for (uint32_t i = 0; i < (1u << 24); i++) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+            if (v >= expected) { ok = 1; break; }
+        }
+        if (!ok) atomicOr(&g_sx8_error_flag, 4u);
+        s_ok = ok;
+    }
+    __syncthreads();
+    for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < n_elems; i += (long)gridDim.x * 256) {
+        float acc = 0.f;
+        for (int r = 0; r < world; r++) acc += __ldcv(slots + (long)r * slot_elems + i);
+        y[i] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        unsigned prev = atomicAdd(done, 1u);
+        if (prev == gridDim.x - 1) {
+            *done = 0u;
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(0u) : "memory");
         }
     }
 }
@@ -588,9 +654,19 @@ extern "C" size_t sx8_gemv_workspace_bytes(int n_cb, int M) {
 
 namespace sx8 {
 // Shared by sx8_gemv and the 8-row passes of sx8_gemm.  Arguments already validated.
+int gemv_launch_ex(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
+                   const float* scales, int N, int n_cb, float* y, void* workspace, unsigned flags,
+                   const sx8_peers_t* peers, cudaStream_t stream);
+
 int gemv_launch(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
                 const float* scales, int N, int n_cb, float* y, void* workspace, unsigned flags,
                 cudaStream_t stream) {
+    return gemv_launch_ex(x, M, K, ldx, wt16, bases, scales, N, n_cb, y, workspace, flags, nullptr, stream);
+}
+
+int gemv_launch_ex(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
+                   const float* scales, int N, int n_cb, float* y, void* workspace, unsigned flags,
+                   const sx8_peers_t* peers, cudaStream_t stream) {
     const __half* xp = (const __half*)x;
     long ld = ldx;
     const int Kp = n_cb * 32;
@@ -612,15 +688,44 @@ int gemv_launch(const void* x, int M, int K, long ldx, const void* wt16, const f
     Choice c = choose(N, n_cb);
     const int n_tiles = (int)t16_tiles(N);
     static const int dbg = env_int("SX8_GEMV_DEBUG");
-    GemvParams p{(const uint8_t*)wt16, xp, bases, scales, y, ld, N, n_cb, M, c.split, n_tiles,
-                 (n_tiles + c.nt - 1) / c.nt, dbg};
-    static const int var = env_int("SX8_GEMV_VAR");
-    if (c.nt == 8 && var == 1) return launch_gemv<8, 2, 6>(p, c.grid_x, flags, stream);
-    if (c.nt == 8 && var == 2) return launch_gemv<8, 8, 3>(p, c.grid_x, flags, stream);
-    if (c.nt == 8 && var == 3) return launch_gemv<8, 4, 5>(p, c.grid_x, flags, stream);
-    if (c.nt == 8) return launch_gemv<8, 4, 3>(p, c.grid_x, flags, stream);
-    if (c.nt == 4) return launch_gemv<4, 8, 3>(p, c.grid_x, flags, stream);
-    return launch_gemv<2, 8, 4>(p, c.grid_x, flags, stream);
+    GemvParams p{};
+    p.blob = (const uint8_t*)wt16; p.x = xp; p.bases = bases; p.scales = scales; p.y = y; p.ldx = ld;
+    p.N = N; p.n_cb = n_cb; p.M = M; p.split = c.split; p.n_tiles = n_tiles;
+    p.groups = (n_tiles + c.nt - 1) / c.nt; p.debug = dbg;
+    p.rank = 0; p.world = 1; p.slot_elems = 0;
+    if (peers && peers->world > 1) {
+        const int par = peers->parity & 1;
+        for (int q = 0; q < peers->world; q++) {
+            p.peer_data[q] = (float*)peers->data[q] + (long)par * peers->world * peers->slot_elems;
+            p.peer_flag[q] = (unsigned*)peers->flags[q] + par;
+        }
+        p.slot_elems = peers->slot_elems; p.rank = peers->rank; p.world = peers->world;
+    }
+    int rc;
+    if (c.nt == 8) rc = launch_gemv<8, 4, 3>(p, c.grid_x, flags, stream);
+    else if (c.nt == 4) rc = launch_gemv<4, 8, 3>(p, c.grid_x, flags, stream);
+    else rc = launch_gemv<2, 8, 4>(p, c.grid_x, flags, stream);
+    if (rc != SX8_OK || p.world <= 1) return rc;
+    // second half of the exchange: sum the world slots of this rank's receive buffer into y
+    const int par = peers->parity & 1;
+    const long n_elems = (long)M * N;
+    cudaLaunchConfig_t cfg = {};
+    unsigned blocks = (unsigned)((n_elems + 1023) / 1024);
+    cfg.gridDim = dim3(blocks < 1 ? 1 : (blocks > 64 ? 64 : blocks), 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = (flags & SX8_F_PDL) ? 1 : 0;
+    unsigned* fl = (unsigned*)peers->flags[peers->rank];
+    cudaError_t e = cudaLaunchKernelEx(&cfg, reduce_peers_kernel,
+                                       (const float*)peers->data[peers->rank] + (long)par * peers->world * peers->slot_elems,
+                                       fl + par, fl + 2 + par, y, n_elems, (long)peers->slot_elems, peers->world,
+                                       (unsigned)(peers->world * n_tiles));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(reduce_peers_kernel)");
+    return SX8_OK;
 }
 
 int gemv_check(const char* who, const void* x, int M, int Mmax, int K, long ldx, const void* wt16,
@@ -651,4 +756,28 @@ extern "C" int sx8_gemv(const void* x, int M, int K, long ldx, const void* wt16,
         return SX8_E_WORKSPACE;
     }
     return gemv_launch(x, M, K, ldx, wt16, bases, scales, N, n_cb, y, workspace, flags, (cudaStream_t)stream);
+}
+
+extern "C" int sx8_gemv_allreduce(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
+                                  const float* scales, int N, int n_cb, float* y, void* workspace,
+                                  size_t workspace_bytes, unsigned flags, const sx8_peers_t* peers, void* stream) {
+    int rc = gemv_check("sx8_gemv_allreduce", x, M, SX8_GEMV_MAX_BATCH, K, ldx, wt16, bases, scales, N, n_cb, y);
+    if (rc != SX8_OK) return rc;
+    SX8_REQUIRE(peers, "sx8_gemv_allreduce: null peer descriptor");
+    SX8_REQUIRE(peers->world >= 1 && peers->world <= SX8_MAX_PEERS && peers->rank >= 0 && peers->rank < peers->world,
+                "sx8_gemv_allreduce: bad rank/world (%d/%d, at most %d ranks)", peers->rank, peers->world, SX8_MAX_PEERS);
+    SX8_REQUIRE(peers->slot_elems >= (long)M * N, "sx8_gemv_allreduce: slot_elems (%ld) < M*N (%ld)", peers->slot_elems,
+                (long)M * N);
+    for (int q = 0; q < peers->world; q++)
+        SX8_REQUIRE(peers->data[q] && peers->flags[q] && (reinterpret_cast<uintptr_t>(peers->data[q]) % 16) == 0 &&
+                        (reinterpret_cast<uintptr_t>(peers->flags[q]) % 4) == 0,
+                    "sx8_gemv_allreduce: null or misaligned peer pointer for rank %d", q);
+    if (!workspace || workspace_bytes < sx8_gemv_workspace_bytes(n_cb, M) ||
+        (reinterpret_cast<uintptr_t>(workspace) % 256) != 0) {
+        set_error("sx8_gemv_allreduce: workspace must be 256-byte aligned and hold %zu bytes (got %zu)",
+                  sx8_gemv_workspace_bytes(n_cb, M), workspace_bytes);
+        return SX8_E_WORKSPACE;
+    }
+    return gemv_launch_ex(x, M, K, ldx, wt16, bases, scales, N, n_cb, y, workspace, flags, peers,
+                          (cudaStream_t)stream);
 }

@@ -71,6 +71,31 @@ def gemv(x, wt16, bases, scales, N, K, n_cb, out=None, flags=0, workspace=None):
     return out
 
 
+def gemv_allreduce(x, wt16, bases, scales, N, K, n_cb, peers, out=None, flags=0, workspace=None):
+    """Row-parallel partial GEMV fused with its all-reduce over peer memory: y (M,N) f32 on
+    every rank = sum over ranks of x_r @ W_r^T.  `peers` is a _lib.Peers descriptor."""
+    if x.dim() == 1:
+        x = x.unsqueeze(0)
+    if not x.is_cuda or x.dtype != torch.float16:
+        raise SX8Error("x must be a CUDA float16 tensor")
+    if x.stride(1) != 1 or x.stride(0) < x.shape[1]:
+        x = x.contiguous()
+    M = x.shape[0]
+    _wt(wt16, N, n_cb)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    L = _lib.lib()
+    need = L.sx8_gemv_workspace_bytes(n_cb, M)
+    ws = workspace if workspace is not None else Workspace.get(x.device, need)
+    import ctypes
+    with torch.cuda.device(x.device):
+        rc = L.sx8_gemv_allreduce(x.data_ptr(), M, K, x.stride(0), wt16.data_ptr(), bases.data_ptr(),
+                                  scales.data_ptr(), N, n_cb, out.data_ptr(), ws.data_ptr(), ws.numel(), flags,
+                                  ctypes.addressof(peers), _stream(x))
+    _lib.check(rc, "sx8_gemv_allreduce")
+    return out
+
+
 def gemm(x, wt16, bases, scales, N, K, n_cb, out_dtype=torch.float32, out=None):
     """Y (M,N) = X (M,K) f16 times the packed matrix, any M >= 1; fp32 accumulate."""
     x = _need(x.contiguous(), torch.float16, "x")

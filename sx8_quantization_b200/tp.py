@@ -51,17 +51,69 @@ def shard_tensor(t, style, rank, world):
     raise ops.SX8Error("unknown tensor-parallel style %r" % (style,))
 
 
-def linear(x, t, out=None, flags=0, group=None, reduce=True):
+class PeerExchange:
+    """Symmetric receive buffers for the fused GEMV + all-reduce (sx8_gemv_allreduce): every
+    rank maps every other rank's buffer (torch symmetric memory over NVLink peer access) and
+    the GEMV epilogue stores its partial tiles straight into them.  NVLink multicast is not
+    used (plain peer stores only).
+
+    Calls alternate between two halves of the buffers ("parity"); all ranks must make the same
+    calls in the same order.  A CUDA graph that captures exchange calls must contain an even
+    number of them, so that a replay starts with the parity it was captured with."""
+
+    def __init__(self, max_elems, device, group=None):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _lib
+        self.group = group if group is not None else torch.distributed.group.WORLD
+        self.world = torch.distributed.get_world_size(self.group)
+        self.rank = torch.distributed.get_rank(self.group)
+        if self.world > 8:
+            raise ops.SX8Error("at most 8 ranks")
+        self.slot_elems = int(max_elems)
+        self.data = symm_mem.empty(2 * self.world * self.slot_elems, dtype=torch.float32, device=device)
+        self.flags = symm_mem.empty(64, dtype=torch.int32, device=device)
+        self.data.zero_()
+        self.flags.zero_()
+        torch.cuda.synchronize(device)
+        self._hd = symm_mem.rendezvous(self.data, group=self.group)
+        self._hf = symm_mem.rendezvous(self.flags, group=self.group)
+        torch.distributed.barrier(self.group)
+        self._desc = []
+        for par in (0, 1):
+            d = _lib.Peers()
+            for q in range(self.world):
+                d.data[q] = int(self._hd.buffer_ptrs[q])
+                d.flags[q] = int(self._hf.buffer_ptrs[q])
+            d.slot_elems = self.slot_elems
+            d.rank, d.world, d.parity = self.rank, self.world, par
+            self._desc.append(d)
+        self.calls = 0
+
+    def next(self):
+        d = self._desc[self.calls & 1]
+        self.calls += 1
+        return d
+
+
+def linear(x, t, out=None, flags=0, group=None, reduce=True, exchange=None):
     """y = x @ W^T for a (possibly sharded) S-X8 tensor.  x: (M, K_local) f16.  For a
-    row-parallel shard the fp32 partial is all-reduced in place (sum) unless
-    reduce=False.  M <= 8 runs the decode GEMV, larger M the GEMM."""
+    row-parallel shard the fp32 partial is summed over ranks: through `exchange` (a
+    PeerExchange: the GEMV stores into peer memory and a small kernel reduces) when given and
+    M <= 8, else with an NCCL all-reduce in place; reduce=False skips it.  M <= 8 runs the
+    decode GEMV, larger M the GEMM."""
     M = x.shape[0]
+    row = reduce and t.get("style") == "row" and torch.distributed.is_initialized() \
+        and torch.distributed.get_world_size(group) > 1
+    if row and exchange is not None and M <= 8 and M * t["N"] <= exchange.slot_elems:
+        return ops.gemv_allreduce(x, t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"],
+                                  exchange.next(), out=out, flags=flags)
     if M <= 8:
         y = ops.gemv(x, t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"], out=out, flags=flags)
     else:
         y = ops.gemm(x, t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"], out_dtype=torch.float32,
                      out=out)
-    if reduce and t.get("style") == "row" and torch.distributed.is_initialized() \
-            and torch.distributed.get_world_size(group) > 1:
+    if row:
         torch.distributed.all_reduce(y, group=group)
     return y
