@@ -429,7 +429,9 @@ def run_tp(args, rank, world, local_rank):
     if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=dev)
     n_layers = args.layers if args.layers > 0 else 4
-    layers = build_model(fam, n_layers, dev, with_pca=True, shard=(rank, world))
+    # --emulate-world W on one GPU: time rank 0's shard of a W-way split without any exchange
+    shard_world = args.emulate_world if (world == 1 and args.emulate_world > 1) else world
+    layers = build_model(fam, n_layers, dev, with_pca=True, shard=(rank, shard_world))
     batches = (1, 8)
     g = torch.Generator(device=dev).manual_seed(5 + rank)
     bytes_rank = sum(tensor_bytes(t) for L in layers for t in L.values())
@@ -569,7 +571,7 @@ def run_tp(args, rank, world, local_rank):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16 x u6 -> f32 accumulate", "data": "synthetic (random-init, quantised on the device)",
             "config": {"workload": "tp_decode_llama70b", "layers": n_layers, "batches": list(batches),
-                       "parallelism": "tp%d" % world,
+                       "parallelism": "tp%d" % world if shard_world == world else "rank 0 of tp%d, no exchange" % shard_world,
                        "allreduce": ("fused into the GEMV epilogue over peer memory (fp32, rank-ordered sum)"
                                      if exchange is not None else "nccl fp32 sum") + " after o and down",
                        "packed_bytes_per_layer": full_layer,
@@ -628,6 +630,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMM / quantizer / embed / dequant extras")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--emulate-world", type=int, default=0,
+                    help="single GPU: run rank 0's shard of a W-way tensor-parallel split, no exchange")
     ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
                     help="row-parallel reduction: fused peer-memory exchange or NCCL")
     ap.add_argument("--max-seconds", type=int, default=900, help="watchdog for the whole run")

@@ -578,6 +578,7 @@ Choice choose(int N, int n_cb) {
                 long waves = (ctas + 3 * kSMs - 1) / (3 * kSMs);
                 double per_wave = (double)ctas / (double)waves;
                 double dev = per_wave > 384.0 ? (per_wave - 384.0) / 384.0 : (384.0 - per_wave) / 384.0;
+                if (ctas < kSMs) dev = 2.0 - (double)ctas / kSMs;   // fewer CTAs than SMs: parallelism first
                 score = -(dev + 0.03 * (double)(waves - 1) + nt_pen[a] + 0.005 * split);
             }
             if (score > best_score) {
