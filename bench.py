@@ -236,6 +236,44 @@ def run_single(args):
                                "GBps": round(tensor_bytes(group[0]) / us / 1e3, 1),
                                "resident_copies": len(group)}
 
+    # ---- the same pass with the projections that share their input fused into one launch
+    #      (q|k|v and gate|up: 4 launches per layer instead of 7), batch 1
+    fused = None
+    if not args.no_extras:
+        mq = [ops.MultiGemv([L["q"], L["k"], L["v"]], 1, dev) for L in layers]
+        mg = [ops.MultiGemv([L["gate"], L["up"]], 1, dev) for L in layers]
+
+        def fused_pass():
+            for L, a, b in zip(layers, mq, mg):
+                a(xs[(1, L["q"]["K"])], flags=flags, workspace=ws)
+                t = L["o"]
+                ops.gemv(xs[(1, t["K"])], t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"],
+                         out=ys[(1, t["N"])], flags=flags, workspace=ws)
+                b(xs[(1, L["gate"]["K"])], flags=flags, workspace=ws)
+                t = L["down"]
+                ops.gemv(xs[(1, t["K"])], t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"],
+                         out=ys[(1, t["N"])], flags=flags, workspace=ws)
+            t = head
+            ops.gemv(xs[(1, t["K"])], t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"],
+                     out=ys[(1, t["N"])], flags=flags, workspace=ws)
+
+        with torch.cuda.stream(st):
+            fused_pass(); st.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=st):
+                fused_pass()
+            for _ in range(3):
+                gr.replay()
+            st.synchronize()
+            a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+            a.record(st)
+            for _ in range(20):
+                gr.replay()
+            b.record(st); st.synchronize()
+        fms = a.elapsed_time(b) / 20
+        fused = {"ms_per_pass": round(fms, 4), "GBps": round(bytes_pass / (fms * 1e-3) / 1e9, 1),
+                 "launches_per_layer": 4, "frac_of_hbm": round(bytes_pass / (fms * 1e-3) / 1e9 / peaks()[0], 4)}
+
     # ---- the other rows of the hot path (BASELINE configs 2 and 4): prefill GEMM, quantizer,
     #      embedding rows, full-tensor decode -- short device-timed loops, reported as extras
     extras = {} if args.no_extras else other_kernels(dev, layers[0], head, fam)
@@ -295,6 +333,7 @@ def run_single(args):
                 "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps,
                 "api": "sx8_decode1_v3.decode1_v44 with pinned host x and y"},
         "clocks": clocks,
+        "fused_projections_batch1": fused,
         "other_kernels": extras,
     }
     if not args.no_cpu:

@@ -72,6 +72,17 @@ int sx8_gemv(const void* x_f16, int M, int K, long ldx, const void* wt16, const 
              const float* scales, int N, int n_cb, float* y, void* workspace,
              size_t workspace_bytes, unsigned flags, void* stream);
 
+/* ---- several decode GEMVs on the same activations, one launch ----------------------
+ * No counterpart in the reference (it launches every projection separately; fused
+ * multi-projection launches are its stated next step, ref: CHANGELOG.md:21-23).  y[i] =
+ * x * W_i^T for count <= 4 matrices with the same K (q|k|v, gate|up): one kernel, one pass
+ * over x, tile groups of all matrices scheduled together.  Arrays are host arrays of device
+ * pointers / sizes.                                                                      */
+int sx8_gemv_multi(const void* x_f16, int M, int K, long ldx, int count, const void* const* wt16,
+                   const float* const* bases, const float* const* scales, const int* N,
+                   float* const* y, int n_cb, void* workspace, size_t workspace_bytes,
+                   unsigned flags, void* stream);
+
 /* ---- row-parallel decode GEMV fused with its all-reduce ---------------------------
  * No counterpart in the reference (it has no multi-GPU code).  One rank of a tensor-parallel
  * group computes its partial y over its K range; the GEMV's epilogue stores every finished

@@ -16,6 +16,7 @@ SIGNATURES = {
     "sx8_last_error": (ctypes.c_char_p, []),
     "sx8_gemv_workspace_bytes": (_sz, [_i, _i]),
     "sx8_gemv": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _i, _i, _vp, _vp, _sz, _u, _vp]),
+    "sx8_gemv_multi": (_i, [_vp, _i, _i, _l, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _sz, _u, _vp]),
     "sx8_gemv_allreduce": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _i, _i, _vp, _vp, _sz, _u, _vp, _vp]),
     "sx8_gemv_tune": (None, [_i, _i, _i]),
     "sx8_gemm_workspace_bytes": (_sz, [_i, _i, _i]),

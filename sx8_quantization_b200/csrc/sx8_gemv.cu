@@ -156,14 +156,23 @@ xpad_kernel(const __half* __restrict__ x, int M, int K, long ldx, int Kp, __half
 }
 
 // ------------------------------------------------------------------ main kernel
-struct GemvParams {
+// One packed matrix of a launch.  A launch may carry up to four matrices that share the
+// activations (q|k|v, gate|up): tile groups are numbered through all of them, matrix i owning
+// groups [group0, group0 + ceil(n_tiles / NT)).
+struct SegDesc {
     const uint8_t* blob;   // T16
-    const __half* x;       // (M, >= 32*n_cb), rows 16-byte aligned
     const float* bases;
     const float* scales;
     float* y;
+    int N, n_tiles, group0;
+};
+constexpr int kMaxSeg = 4;
+
+struct GemvParams {
+    SegDesc seg[kMaxSeg];
+    const __half* x;       // (M, >= 32*n_cb), rows 16-byte aligned
     long ldx;
-    int N, n_cb, M, split, n_tiles, groups;
+    int nseg, n_cb, M, split, groups;
     int debug;   // bit 0: consumers skip the math (pipeline-only timing experiments)
     // Row-parallel exchange (world > 1): instead of y, every finished tile is stored into slot
     // `rank` of each peer's receive buffer (peer memory, plain stores over NVLink), then a
@@ -175,9 +184,9 @@ struct GemvParams {
 };
 
 // Stores one finished value, locally or into every peer's slot.
-__device__ __forceinline__ void put_out(const GemvParams& p, long idx, float v) {
+__device__ __forceinline__ void put_out(const GemvParams& p, float* y, long idx, float v) {
     if (p.world <= 1) {
-        p.y[idx] = v;
+        y[idx] = v;
     } else {
 #pragma unroll 1
         for (int q = 0; q < p.world; q++) p.peer_data[q][(long)p.rank * p.slot_elems + idx] = v;
@@ -224,6 +233,11 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
     const int my_groups = ((int)blockIdx.x < p.groups) ? (p.groups - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
     const int total_iters = my_groups * n_iter;
     constexpr bool kDirectStore = (C::KS == 1);   // with split == 1 a warp owns its tile for all of K
+    // the matrix this CTA works on (launches with several matrices give each CTA one tile group)
+    int si = 0;
+    for (int i = 1; i < p.nseg; i++)
+        if ((int)blockIdx.x >= p.seg[i].group0) si = i;
+    const SegDesc sg = p.seg[si];
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -241,14 +255,14 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
         // the slab of tile i, lane 8+m the slice of activation row m.
         auto coords = [&](int it, int& grp, int& kb0, int& rows) {
             int gi = it / n_iter, j = it - gi * n_iter;
-            grp = (int)blockIdx.x + gi * (int)gridDim.x;
+            grp = (int)blockIdx.x + gi * (int)gridDim.x - sg.group0;
             kb0 = kb_begin + j * KB_S;
             rows = min(KB_S, kb_end - kb0);
         };
         auto arm = [&](int it) {   // lane 0: announce the bytes of stage `it`
             int grp, kb0, rows;
             coords(it, grp, kb0, rows);
-            int tiles = min(NT, p.n_tiles - grp * NT);
+            int tiles = min(NT, sg.n_tiles - grp * NT);
             mbar_expect_tx(bar_full + 8 * (it % STAGES),
                            (uint32_t)rows * ((uint32_t)tiles * T16_UNIT + (uint32_t)p.M * 64u));
         };
@@ -257,9 +271,9 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
             coords(it, grp, kb0, rows);
             int s = it % STAGES;
             long T = (long)grp * NT + lane;
-            if (lane < NT && T < p.n_tiles)
+            if (lane < NT && T < sg.n_tiles)
                 bulk_g2s(sbase + s * C::STAGE + lane * (KB_S * T16_UNIT),
-                         p.blob + (T * p.n_cb + kb0) * T16_UNIT, (uint32_t)rows * T16_UNIT, bar_full + 8 * s);
+                         sg.blob + (T * p.n_cb + kb0) * T16_UNIT, (uint32_t)rows * T16_UNIT, bar_full + 8 * s);
         };
         auto issue_x = [&](int it) {
             int grp, kb0, rows;
@@ -311,11 +325,11 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
                 int kb = min(kb0 + u, kb_end - 1);
                 raw[u] = make_uint4(0u, 0u, 0u, 0u);
                 if (row_ok) raw[u] = *reinterpret_cast<const uint4*>(p.x + (long)g * p.ldx + (long)kb * 32 + t * 8);
-                const float4* b0p = reinterpret_cast<const float4*>(p.bases + (long)kb * 64 + t * 8);
-                const float4* b1p = reinterpret_cast<const float4*>(p.bases + (long)kb * 64 + 32 + t * 8);
+                const float4* b0p = reinterpret_cast<const float4*>(sg.bases + (long)kb * 64 + t * 8);
+                const float4* b1p = reinterpret_cast<const float4*>(sg.bases + (long)kb * 64 + 32 + t * 8);
                 bq[u][0] = b0p[0]; bq[u][1] = b0p[1]; bq[u][2] = b1p[0]; bq[u][3] = b1p[1];
-                sc[u][0] = p.scales[kb * 2 + 0];
-                sc[u][1] = p.scales[kb * 2 + 1];
+                sc[u][0] = sg.scales[kb * 2 + 0];
+                sc[u][1] = sg.scales[kb * 2 + 1];
             }
 #pragma unroll
             for (int u = 0; u < 2; u++) {
@@ -358,7 +372,7 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
         bool ok = true;
         int it = 0;
         for (int gi = 0; gi < my_groups; gi++) {
-            const int grp = (int)blockIdx.x + gi * (int)gridDim.x;
+            const int grp = (int)blockIdx.x + gi * (int)gridDim.x - sg.group0;
             for (int j = 0; j < n_iter; j++, it++) {
                 int s = it % STAGES;
                 if (ok) ok = mbar_wait(bar_full + 8 * s, (it / STAGES) & 1, 2u);
@@ -424,15 +438,15 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
             if (kDirectStore && p.split == 1) {
                 int nA = (grp * NT + ti) * 16 + g, nB = nA + 8, m0 = 2 * t, m1 = m0 + 1;
                 float v0 = accF[0] + accD[0], v1 = accF[1] + accD[1], v2 = accF[2] + accD[2], v3 = accF[3] + accD[3];
-                if (nA < p.N) {
-                    if (m0 < p.M) put_out(p, (long)m0 * p.N + nA, v0);
-                    if (m1 < p.M) put_out(p, (long)m1 * p.N + nA, v1);
+                if (nA < sg.N) {
+                    if (m0 < p.M) put_out(p, sg.y, (long)m0 * sg.N + nA, v0);
+                    if (m1 < p.M) put_out(p, sg.y, (long)m1 * sg.N + nA, v1);
                 }
-                if (nB < p.N) {
-                    if (m0 < p.M) put_out(p, (long)m0 * p.N + nB, v2);
-                    if (m1 < p.M) put_out(p, (long)m1 * p.N + nB, v3);
+                if (nB < sg.N) {
+                    if (m0 < p.M) put_out(p, sg.y, (long)m0 * sg.N + nB, v2);
+                    if (m1 < p.M) put_out(p, sg.y, (long)m1 * sg.N + nB, v3);
                 }
-                if (grp * NT + ti < p.n_tiles) signal_tile(p, lane);
+                if (grp * NT + ti < sg.n_tiles) signal_tile(p, lane);
 #pragma unroll
                 for (int i = 0; i < 4; i++) accF[i] = accD[i] = 0.f;
             }
@@ -476,17 +490,18 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
     }
     if (rank == 0 && warp < NT && (int)blockIdx.x < p.groups) {
         const int g = lane >> 2, t = lane & 3;
-        int nA = ((int)blockIdx.x * NT + warp) * 16 + g, nB = nA + 8;
+        const int tl = ((int)blockIdx.x - sg.group0) * NT + warp;   // tile within this CTA's matrix
+        int nA = tl * 16 + g, nB = nA + 8;
         int m0 = 2 * t, m1 = 2 * t + 1;
-        if (nA < p.N) {
-            if (m0 < p.M) put_out(p, (long)m0 * p.N + nA, accF[0]);
-            if (m1 < p.M) put_out(p, (long)m1 * p.N + nA, accF[1]);
+        if (nA < sg.N) {
+            if (m0 < p.M) put_out(p, sg.y, (long)m0 * sg.N + nA, accF[0]);
+            if (m1 < p.M) put_out(p, sg.y, (long)m1 * sg.N + nA, accF[1]);
         }
-        if (nB < p.N) {
-            if (m0 < p.M) put_out(p, (long)m0 * p.N + nB, accF[2]);
-            if (m1 < p.M) put_out(p, (long)m1 * p.N + nB, accF[3]);
+        if (nB < sg.N) {
+            if (m0 < p.M) put_out(p, sg.y, (long)m0 * sg.N + nB, accF[2]);
+            if (m1 < p.M) put_out(p, sg.y, (long)m1 * sg.N + nB, accF[3]);
         }
-        if ((int)blockIdx.x * NT + warp < p.n_tiles) signal_tile(p, lane);
+        if (tl < sg.n_tiles) signal_tile(p, lane);
     }
 }
 
@@ -690,8 +705,10 @@ int gemv_launch_ex(const void* x, int M, int K, long ldx, const void* wt16, cons
     const int n_tiles = (int)t16_tiles(N);
     static const int dbg = env_int("SX8_GEMV_DEBUG");
     GemvParams p{};
-    p.blob = (const uint8_t*)wt16; p.x = xp; p.bases = bases; p.scales = scales; p.y = y; p.ldx = ld;
-    p.N = N; p.n_cb = n_cb; p.M = M; p.split = c.split; p.n_tiles = n_tiles;
+    p.nseg = 1;
+    p.seg[0] = SegDesc{(const uint8_t*)wt16, bases, scales, y, N, n_tiles, 0};
+    p.x = xp; p.ldx = ld;
+    p.n_cb = n_cb; p.M = M; p.split = c.split;
     p.groups = (n_tiles + c.nt - 1) / c.nt; p.debug = dbg;
     p.rank = 0; p.world = 1; p.slot_elems = 0;
     if (peers && peers->world > 1) {
@@ -727,6 +744,48 @@ int gemv_launch_ex(const void* x, int M, int K, long ldx, const void* wt16, cons
                                        (unsigned)(peers->world * n_tiles));
     if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(reduce_peers_kernel)");
     return SX8_OK;
+}
+
+// Several matrices that share the activations, one launch (q|k|v, gate|up).  Each CTA owns one
+// tile group of one matrix; groups never straddle matrices.
+int gemv_launch_multi(const void* x, int M, int K, long ldx, int count, const void* const* wt16,
+                      const float* const* bases, const float* const* scales, const int* N, float* const* y,
+                      int n_cb, void* workspace, unsigned flags, cudaStream_t stream) {
+    const __half* xp = (const __half*)x;
+    long ld = ldx;
+    const int Kp = n_cb * 32;
+    if (K != Kp || (ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x) % 16) != 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(((long)M * Kp + 255) / 256), 1, 1);
+        cfg.blockDim = dim3(256, 1, 1);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = (flags & SX8_F_PDL) ? 1 : 0;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, xpad_kernel, (const __half*)x, M, K, ldx, Kp, (__half*)workspace);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(xpad_kernel)");
+        xp = (const __half*)workspace;
+        ld = Kp;
+    }
+    long n_total = 0;
+    for (int i = 0; i < count; i++) n_total += (long)t16_tiles(N[i]) * 16;
+    Choice c = choose((int)n_total, n_cb);
+    static const int dbg = env_int("SX8_GEMV_DEBUG");
+    GemvParams p{};
+    p.nseg = count;
+    int g0 = 0;
+    for (int i = 0; i < count; i++) {
+        int nt_i = (int)t16_tiles(N[i]);
+        p.seg[i] = SegDesc{(const uint8_t*)wt16[i], bases[i], scales[i], y[i], N[i], nt_i, g0};
+        g0 += (nt_i + c.nt - 1) / c.nt;
+    }
+    p.x = xp; p.ldx = ld; p.n_cb = n_cb; p.M = M; p.split = c.split; p.groups = g0; p.debug = dbg;
+    p.rank = 0; p.world = 1; p.slot_elems = 0;
+    if (c.nt == 8) return launch_gemv<8, 4, 3>(p, g0, flags, stream);   // one group per CTA: grid = groups
+    if (c.nt == 4) return launch_gemv<4, 8, 3>(p, g0, flags, stream);
+    return launch_gemv<2, 8, 4>(p, g0, flags, stream);
 }
 
 int gemv_check(const char* who, const void* x, int M, int Mmax, int K, long ldx, const void* wt16,
@@ -781,4 +840,25 @@ extern "C" int sx8_gemv_allreduce(const void* x, int M, int K, long ldx, const v
     }
     return gemv_launch_ex(x, M, K, ldx, wt16, bases, scales, N, n_cb, y, workspace, flags, peers,
                           (cudaStream_t)stream);
+}
+
+extern "C" int sx8_gemv_multi(const void* x, int M, int K, long ldx, int count, const void* const* wt16,
+                              const float* const* bases, const float* const* scales, const int* N,
+                              float* const* y, int n_cb, void* workspace, size_t workspace_bytes,
+                              unsigned flags, void* stream) {
+    SX8_REQUIRE(count >= 1 && count <= kMaxSeg, "sx8_gemv_multi: count must be in 1..%d (got %d)", kMaxSeg, count);
+    SX8_REQUIRE(wt16 && bases && scales && N && y, "sx8_gemv_multi: null array");
+    for (int i = 0; i < count; i++) {
+        int rc = gemv_check("sx8_gemv_multi", x, M, SX8_GEMV_MAX_BATCH, K, ldx, wt16[i], bases[i], scales[i], N[i],
+                            n_cb, y[i]);
+        if (rc != SX8_OK) return rc;
+    }
+    if (!workspace || workspace_bytes < sx8_gemv_workspace_bytes(n_cb, M) ||
+        (reinterpret_cast<uintptr_t>(workspace) % 256) != 0) {
+        set_error("sx8_gemv_multi: workspace must be 256-byte aligned and hold %zu bytes (got %zu)",
+                  sx8_gemv_workspace_bytes(n_cb, M), workspace_bytes);
+        return SX8_E_WORKSPACE;
+    }
+    return gemv_launch_multi(x, M, K, ldx, count, wt16, bases, scales, N, y, n_cb, workspace, flags,
+                             (cudaStream_t)stream);
 }

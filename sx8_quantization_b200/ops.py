@@ -71,6 +71,42 @@ def gemv(x, wt16, bases, scales, N, K, n_cb, out=None, flags=0, workspace=None):
     return out
 
 
+class MultiGemv:
+    """Prepared argument block for sx8_gemv_multi: up to four matrices that share x (q|k|v,
+    gate|up) run in one launch.  Build once per group of tensors, call per step."""
+
+    def __init__(self, tensors, M, device):
+        import ctypes
+        if not 1 <= len(tensors) <= 4:
+            raise SX8Error("1..4 matrices per launch")
+        self.n_cb = tensors[0]["n_cb"]
+        self.K = tensors[0]["K"]
+        if any(t["n_cb"] != self.n_cb or t["K"] != self.K for t in tensors):
+            raise SX8Error("all matrices of a launch must have the same K")
+        n = len(tensors)
+        self.tensors = tensors
+        self.M = M
+        self.outs = [torch.empty((M, t["N"]), dtype=torch.float32, device=device) for t in tensors]
+        VP, I = ctypes.c_void_p * n, ctypes.c_int * n
+        self._wt = VP(*[t["wt16"].data_ptr() for t in tensors])
+        self._ba = VP(*[t["bases"].data_ptr() for t in tensors])
+        self._sc = VP(*[t["scales"].data_ptr() for t in tensors])
+        self._y = VP(*[o.data_ptr() for o in self.outs])
+        self._N = I(*[t["N"] for t in tensors])
+        self.count = n
+
+    def __call__(self, x, flags=0, workspace=None):
+        if x.dtype != torch.float16 or not x.is_cuda or x.shape[0] != self.M or x.stride(1) != 1:
+            raise SX8Error("x must be CUDA float16 (M, K) with unit inner stride")
+        L = _lib.lib()
+        ws = workspace if workspace is not None else Workspace.get(x.device, L.sx8_gemv_workspace_bytes(self.n_cb, self.M))
+        with torch.cuda.device(x.device):
+            rc = L.sx8_gemv_multi(x.data_ptr(), self.M, self.K, x.stride(0), self.count, self._wt, self._ba, self._sc,
+                                  self._N, self._y, self.n_cb, ws.data_ptr(), ws.numel(), flags, _stream(x))
+        _lib.check(rc, "sx8_gemv_multi")
+        return self.outs
+
+
 def gemv_allreduce(x, wt16, bases, scales, N, K, n_cb, peers, out=None, flags=0, workspace=None):
     """Row-parallel partial GEMV fused with its all-reduce over peer memory: y (M,N) f32 on
     every rank = sum over ranks of x_r @ W_r^T.  `peers` is a _lib.Peers descriptor."""

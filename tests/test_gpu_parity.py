@@ -282,6 +282,36 @@ def test_gemv_pdl_flag_and_graph(ops):
     assert torch.equal(out, y0)
 
 
+@pytest.mark.parametrize("M", [1, 8])
+def test_gemv_multi_equals_separate_launches(ops, M):
+    """q|k|v-style grouped launch: bit-identical to three separate GEMVs when the launch shape
+    (tile-group width, split) is pinned to the same values for both."""
+    from sx8_quantization_b200 import _lib
+    shapes = [(512, 2560), (136, 2560), (128, 2560)]
+    ts = []
+    for i, (N, K) in enumerate(shapes):
+        w, qt, bi, v44 = case(N, K, 70 + i)
+        wt, b, s = t16_dev(qt, v44)
+        ts.append({"wt16": wt, "bases": b, "scales": s, "N": N, "K": K, "n_cb": qt["n_cb"]})
+    x = dev(orc.synth_x(M, 2560, 13))
+    L = _lib.lib()
+    try:
+        L.sx8_gemv_tune(4, 4, 0)
+        multi = ops.MultiGemv(ts, M, x.device)
+        ys = [y.clone() for y in multi(x)]
+        sep = [ops.gemv(x, t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"]).clone() for t in ts]
+    finally:
+        L.sx8_gemv_tune(-1, -1, -1)
+    for a, b2 in zip(ys, sep):
+        assert torch.equal(a, b2)
+    # and with the automatic launch shape, against the oracle
+    ys = multi(x)
+    for (N, K), y, i in zip(shapes, ys, range(3)):
+        w, qt, bi, v44 = case(N, K, 70 + i)
+        ref = orc.matmul_ref(x.cpu().numpy(), orc.dequant_d64(qt, bi))
+        assert np.abs(y.cpu().numpy() - ref).max() <= TOL_VS_COMPARATOR * np.abs(ref).max()
+
+
 def test_gemv_matches_reference_kernel_build(ops):
     from oracle import build
     ref_mod = build.load_ref("ref_sx8_decode1_v3")
