@@ -3,8 +3,9 @@
 //   Y (M, N) = X (M, K) * W^T,  W decoded on the fly from the T16 blob, fp32 accumulate.
 //
 // CTA tile: 128*MT rows x 256 columns (MT = 1 or 2), K step 64 (two block rows).  Warp roles:
-//   warp 0      producer : X tiles by 2-D TMA (128-byte swizzle), packed 16-column slabs of
-//                          the blob and the fp16 PCA table by TMA bulk copies
+//   warp 0      producer : X tiles by 2-D TMA (128-byte swizzle)
+//   warp 18     producer : packed 16-column slabs of the blob and the fp16 PCA table by TMA
+//                          bulk copies, running up to 8 stages ahead
 //   warp 1      issuer   : one thread issues tcgen05.mma (M=128, N=256, K=16, kind::f16) on
 //                          shared-memory descriptors; accumulators live in TMEM (256 columns
 //                          per 128-row tile); tcgen05.commit releases the stages
@@ -24,23 +25,35 @@ namespace sx8 {
 
 namespace tc {
 
-constexpr int BN = 256, BK = 64, KB_STAGE = 2;
-constexpr int kDecodeWarps = 16, kWarps = kDecodeWarps + 2, kThreads = kWarps * 32;
+constexpr int BK = 64, KB_STAGE = 2;
+constexpr int kDecodeWarps = 16, kWarps = kDecodeWarps + 3, kThreads = kWarps * 32;
+constexpr int kSmemMax = 232448;                 // opt-in shared memory per CTA on sm_100
 constexpr int A_TILE = 128 * 128;                 // 128 rows x 64 fp16, bytes
-constexpr int B_TILE = BN * 128;                  // 256 rows x 64 fp16
-constexpr int P_SLAB = 16 * KB_STAGE * T16_UNIT;  // 16 tiles x 2 kb
 constexpr int P_TAB = KB_STAGE * 128;             // PCA table: per kb 2 x 32 fp16
-constexpr int P_STAGE = P_SLAB + P_TAB;
 constexpr uint32_t kSpin = 1u << 22;
 
-template <int MT>
+// MT = accumulators per CTA (1 or 2), BN = columns a CTA decodes per stage (64, 128 or 256),
+// PAIR = CTAs that share one MMA (1, or 2 = a cluster of two CTAs issuing cta_group::2 MMAs of
+// 256 rows: each CTA supplies its own 128 rows of X and half of the decoded columns, so every
+// decoded weight feeds twice as many rows).  An accumulator is 128 rows x BN*PAIR columns.
+template <int MT, int BN, int PAIR>
 struct Cfg {
-    static constexpr int SA = 3, SB = 2, SP = 3;
+    static constexpr int TILES = BN / 16;
+    static constexpr int BNU = BN * PAIR;                       // MMA N = accumulator columns
+    static constexpr int B_TILE = BN * 128;                     // BN rows x 64 fp16
+    static constexpr int P_SLAB = TILES * KB_STAGE * T16_UNIT;  // TILES tiles x 2 kb
+    static constexpr int P_STAGE = P_SLAB + P_TAB;
+    static constexpr int SA = 3, SB = (BN >= 256) ? 2 : (PAIR == 2 ? 4 : 3);
+    // packed-slab stages: as deep as shared memory allows (at most 8) -- these loads come from
+    // HBM with the longest latency of the pipeline and run ahead of everything else
+    static constexpr int SP_FIT = (kSmemMax - 2048 - SA * MT * A_TILE - SB * B_TILE) / P_STAGE;
+    static constexpr int SP = SP_FIT > 8 ? 8 : SP_FIT;
+    static_assert(SP >= 3, "too few packed-slab stages");
     static constexpr int OFF_A = 0;
     static constexpr int OFF_B = OFF_A + SA * MT * A_TILE;
     static constexpr int OFF_P = OFF_B + SB * B_TILE;
     static constexpr int OFF_BAR = OFF_P + SP * P_STAGE;
-    static constexpr int N_BAR = 2 * SA + 2 * SB + 2 * SP + 1;
+    static constexpr int N_BAR = 3 * SA + 2 * SB + 2 * SP + 1;
     static constexpr int OFF_TMEM = OFF_BAR + N_BAR * 8;
     static constexpr int SMEM = OFF_TMEM + 16 + 1024;   // + slack to align the base to 1024 B
 };
@@ -69,6 +82,32 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
         if (mbar_try_wait(bar, parity)) return true;
     atomicOr(&g_sx8_error_flag, code);
     return false;
+}
+// Cluster-scope variants for the two-CTA mode: barriers of the leader CTA are arrived on by
+// the peer CTA (and by tcgen05.commit), so waits acquire at cluster scope.
+__device__ __forceinline__ bool mbar_wait_cl(uint32_t bar, uint32_t parity, unsigned code) {
+    for (uint32_t i = 0; i < kSpin; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    atomicOr(&g_sx8_error_flag, code);
+    return false;
+}
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t cta_rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta_rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cl(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -112,14 +151,31 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
     d |= (uint64_t)2 << 61;
     return d;
 }
-// kind::f16 instruction descriptor: D = f32, A = B = f16, both K-major, N = 256, M = 128.
-constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+// kind::f16 instruction descriptor: D = f32, A = B = f16, both K-major, N = bn, M = m.
+__host__ __device__ constexpr uint32_t idesc_for(int bn, int m) {
+    return (1u << 4) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
 
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate) : "memory");
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Two-CTA forms: one thread of the leader CTA issues the MMA for both CTAs; the commit arrives
+// on the barrier at the same shared-memory offset in both CTAs of the pair.
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -163,10 +219,12 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
 }
 
 
-template <int MT>
+template <int MT, int BN, int PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap, Params p) {
-    using C = Cfg<MT>;
+    using C = Cfg<MT, BN, PAIR>;
+    constexpr int B_TILE = C::B_TILE, P_SLAB = C::P_SLAB, P_STAGE = C::P_STAGE, TILES = C::TILES, BNU = C::BNU;
+    static_assert(MT * BNU <= 512, "accumulators exceed tensor memory");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sA = sbase + C::OFF_A, sB = sbase + C::OFF_B, sP = sbase + C::OFF_P;
@@ -175,61 +233,88 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     const uint32_t b_full = a_empty + 8 * C::SA, b_empty = b_full + 8 * C::SB;
     const uint32_t p_full = b_empty + 8 * C::SB, p_empty = p_full + 8 * C::SP;
     const uint32_t acc_full = p_empty + 8 * C::SP;
+    const uint32_t a_peer = acc_full + 8;        // leader only: the peer CTA's X tiles have landed
     const uint32_t tmem_slot = sbase + C::OFF_TMEM;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BN;
-    const int m0 = blockIdx.y * (128 * MT);
-    const int tile0 = n0 >> 4;
+    // PAIR == 2: the cluster is two consecutive CTAs along x; rank 0 leads (issues the MMAs).
+    const int rank = (PAIR == 2) ? (int)(blockIdx.x & 1) : 0;
+    const int n0 = (int)(blockIdx.x / PAIR) * BNU;           // first accumulator column
+    const int m0 = blockIdx.y * (128 * MT * PAIR);
+    const int tile0 = (n0 + rank * BN) >> 4;                 // first 16-column tile this CTA decodes
     const int n_ks = (p.n_cb + KB_STAGE - 1) / KB_STAGE;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::SA; s++) { mbar_init(a_full + 8 * s, 1); mbar_init(a_empty + 8 * s, 1); }
-        for (int s = 0; s < C::SB; s++) { mbar_init(b_full + 8 * s, kDecodeWarps); mbar_init(b_empty + 8 * s, 1); }
+        for (int s = 0; s < C::SA; s++) mbar_init(a_peer + 8 * s, 1);
+        for (int s = 0; s < C::SB; s++) { mbar_init(b_full + 8 * s, kDecodeWarps * PAIR); mbar_init(b_empty + 8 * s, 1); }
         for (int s = 0; s < C::SP; s++) { mbar_init(p_full + 8 * s, 1); mbar_init(p_empty + 8 * s, kDecodeWarps); }
         mbar_init(acc_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {   // TMEM: all 512 columns (two 128 x 256 fp32 accumulators)
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512u) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (PAIR == 2) {   // one warp of each CTA of the pair takes part
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512u) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512u) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if constexpr (PAIR == 2) cluster_sync_all();   // the peer's barriers exist before anyone arrives on them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = lds32(tmem_slot);
 
-    if (warp == 0) {
-        // ------------------------------------------------------------ producer
+    if (warp == kWarps - 1) {
+        // ------------------------------------------------------------ producer of packed slabs
         bool ok = true;
         for (int ks = 0; ks < n_ks; ks++) {
             const int kb0 = ks * KB_STAGE;
             const int rows = min(KB_STAGE, p.n_cb - kb0);
-            {   // packed slabs + PCA table: lane i < 16 copies tile i, lane 16 the table
+            {   // packed slabs + PCA table: lane i < TILES copies tile i, lane 16 the table
                 const int s = ks % C::SP;
                 if (ks >= C::SP && ok) ok = mbar_wait(p_empty + 8 * s, ((ks / C::SP) - 1) & 1, 0x10u);
-                const int tiles = min(16, p.n_tiles - tile0);
+                const int tiles = max(0, min(TILES, p.n_tiles - tile0));
                 if (lane == 0)
                     mbar_expect_tx(p_full + 8 * s, (uint32_t)rows * ((uint32_t)tiles * T16_UNIT + 128u));
                 __syncwarp();
                 const uint32_t dst = sP + s * P_STAGE;
-                if (lane < 16 && tile0 + lane < p.n_tiles)
+                if (lane < TILES && tile0 + lane < p.n_tiles)
                     bulk_g2s(dst + lane * (KB_STAGE * T16_UNIT),
                              p.blob + ((long)(tile0 + lane) * p.n_cb + kb0) * T16_UNIT, (uint32_t)rows * T16_UNIT,
                              p_full + 8 * s);
                 if (lane == 16)
                     bulk_g2s(dst + P_SLAB, p.pb + (long)kb0 * 64, (uint32_t)rows * 128u, p_full + 8 * s);
             }
-            {   // X tiles: MT boxes of 64 (K) x 128 (rows); columns/rows out of range read as zero
+        }
+    } else if (warp == 0) {
+        // ------------------------------------------------------------ producer of X tiles
+        bool ok = true;
+        for (int ks = 0; ks < n_ks; ks++) {
+            {   // MT boxes of 64 (K) x 128 (rows); columns/rows out of range read as zero
                 const int s = ks % C::SA;
                 if (ks >= C::SA && ok) ok = mbar_wait(a_empty + 8 * s, ((ks / C::SA) - 1) & 1, 0x20u);
                 if (lane == 0) {
                     mbar_expect_tx(a_full + 8 * s, (uint32_t)(MT * A_TILE));
                     for (int mt = 0; mt < MT; mt++)
-                        tma_load_2d(sA + (s * MT + mt) * A_TILE, &xmap, ks * BK, m0 + mt * 128, a_full + 8 * s);
+                        tma_load_2d(sA + (s * MT + mt) * A_TILE, &xmap, ks * BK, m0 + (mt * PAIR + rank) * 128,
+                                    a_full + 8 * s);
                 }
                 __syncwarp();
             }
+        }
+    } else if (warp == 1 && rank != 0) {
+        // ------------------------------------------------------------ relay (peer CTA of a pair)
+        // tells the leader that this CTA's X tiles of a stage have landed
+        bool ok = true;
+        const uint32_t remote = mapa_u32(a_peer, 0u);
+        for (int ks = 0; ks < n_ks; ks++) {
+            const int sa = ks % C::SA;
+            if (ok) ok = mbar_wait(a_full + 8 * sa, (ks / C::SA) & 1, 0x800u);
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cl(remote + 8 * sa);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
@@ -237,7 +322,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         for (int ks = 0; ks < n_ks; ks++) {
             const int sa = ks % C::SA, sb = ks % C::SB;
             if (ok) ok = mbar_wait(a_full + 8 * sa, (ks / C::SA) & 1, 0x40u);
-            if (ok) ok = mbar_wait(b_full + 8 * sb, (ks / C::SB) & 1, 0x80u);
+            if constexpr (PAIR == 2) {
+                if (ok) ok = mbar_wait_cl(a_peer + 8 * sa, (ks / C::SA) & 1, 0x1000u);
+                if (ok) ok = mbar_wait_cl(b_full + 8 * sb, (ks / C::SB) & 1, 0x80u);
+            } else {
+                if (ok) ok = mbar_wait(b_full + 8 * sb, (ks / C::SB) & 1, 0x80u);
+            }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (lane == 0) {
                 const uint64_t bdesc = umma_desc(sB + sb * B_TILE);
@@ -245,13 +335,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 for (int mt = 0; mt < MT; mt++) {
                     const uint64_t adesc = umma_desc(sA + (sa * MT + mt) * A_TILE);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; k++)   // +32 bytes along K inside the swizzle atom
-                        umma_f16(tmem_base + mt * BN, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2),
-                                 (ks > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / 16; k++) {   // +32 bytes along K inside the swizzle atom
+                        if constexpr (PAIR == 2)
+                            umma_f16_pair(tmem_base + mt * BNU, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2),
+                                          idesc_for(BNU, 256), (ks > 0 || k > 0) ? 1u : 0u);
+                        else
+                            umma_f16(tmem_base + mt * BNU, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2),
+                                     idesc_for(BNU, 128), (ks > 0 || k > 0) ? 1u : 0u);
+                    }
                 }
-                umma_commit(a_empty + 8 * sa);
-                umma_commit(b_empty + 8 * sb);
-                if (ks == n_ks - 1) umma_commit(acc_full);
+                if constexpr (PAIR == 2) {
+                    umma_commit_pair(a_empty + 8 * sa);
+                    umma_commit_pair(b_empty + 8 * sb);
+                    if (ks == n_ks - 1) umma_commit_pair(acc_full);
+                } else {
+                    umma_commit(a_empty + 8 * sa);
+                    umma_commit(b_empty + 8 * sb);
+                    if (ks == n_ks - 1) umma_commit(acc_full);
+                }
             }
             __syncwarp();
         }
@@ -262,21 +363,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         const uint32_t sh2 = 8u + 2u * (uint32_t)t;
         const float kBase = 0.25f * 0.015873f * 512.0f;   // levels are formed scaled by 2^-9
         bool ok = true;
+        const uint32_t b_full_leader = (PAIR == 2) ? mapa_u32(b_full, 0u) : b_full;
         for (int ks = 0; ks < n_ks; ks++) {
             const int sp = ks % C::SP, sb = ks % C::SB;
             const int rows = min(KB_STAGE, p.n_cb - ks * KB_STAGE);
             if (ok) ok = mbar_wait(p_full + 8 * sp, (ks / C::SP) & 1, 0x100u);
-            if (ks >= C::SB && ok) ok = mbar_wait(b_empty + 8 * sb, ((ks / C::SB) - 1) & 1, 0x200u);
+            if (ks >= C::SB && ok) {
+                if constexpr (PAIR == 2) ok = mbar_wait_cl(b_empty + 8 * sb, ((ks / C::SB) - 1) & 1, 0x200u);
+                else ok = mbar_wait(b_empty + 8 * sb, ((ks / C::SB) - 1) & 1, 0x200u);
+            }
             const uint32_t pst = sP + sp * P_STAGE, bst = sB + sb * B_TILE;
-            {
-                const int tl = dw;
+            // work items (tile, block row) are dealt round-robin to the 16 decode warps
+#pragma unroll
+            for (int item = dw; item < TILES * KB_STAGE; item += kDecodeWarps) {
+                const int tl = item % TILES, r = item / TILES;
                 const bool tile_ok = tile0 + tl < p.n_tiles;
                 // Column 16*tl + g sits in operand row 16*tl + rho(g), rho(g) = 4*(g&1) + (g>>1): the
                 // eight lanes of a quarter-warp then store to eight different 16-byte bank groups.
                 // The epilogue undoes the permutation when it reads the accumulator columns.
                 const uint32_t rowA = (uint32_t)(tl * 16 + (((g & 1) << 2) | (g >> 1))), rowB = rowA + 8;
-#pragma unroll
-                for (int r = 0; r < KB_STAGE; r++) {
+                {
                     uint4 wa = make_uint4(0u, 0u, 0u, 0u), wb = wa;
                     if (r < rows && tile_ok) {
                         const uint32_t unit = pst + (tl * KB_STAGE + r) * T16_UNIT;
@@ -336,28 +442,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic stores -> tensor-core reads
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(b_full + 8 * sb);
+                if constexpr (PAIR == 2) mbar_arrive_cl(b_full_leader + 8 * sb);
+                else mbar_arrive(b_full + 8 * sb);
                 mbar_arrive(p_empty + 8 * sp);
             }
         }
         // ------------------------------------------------------------ epilogue
-        if (ok) ok = mbar_wait(acc_full, 0u, 0x400u);
+        if constexpr (PAIR == 2) { if (ok) ok = mbar_wait_cl(acc_full, 0u, 0x400u); }
+        else { if (ok) ok = mbar_wait(acc_full, 0u, 0x400u); }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int quarter = warp & 3;            // TMEM lanes 32*quarter .. +31 are this warp's
-        const int part = dw >> 2;                // the four warps of a quarter split the 256 columns
-        // Staging for the TMA store: 4 KB per warp in the (now idle) B stages; rows of 128 bytes,
-        // 16-byte chunks XOR-swizzled with the row index (the Y tensor map uses the same swizzle).
-        const uint32_t stg = sB + (uint32_t)dw * 4096u;
+        const int part = dw >> 2;                // the four warps of a quarter share the BN columns
+        // Staging for the TMA store: 4 KB per warp in the (now idle) A and B stages; rows of 128
+        // bytes, 16-byte chunks XOR-swizzled with the row index (the Y tensor map's swizzle).
+        static_assert(C::SA * MT * A_TILE + C::SB * B_TILE >= kDecodeWarps * 4096, "staging does not fit");
+        const uint32_t stg = sA + (uint32_t)dw * 4096u;
 #pragma unroll 1
         for (int mt = 0; mt < MT; mt++) {
-            const int mrow0 = m0 + mt * 128 + quarter * 32;
+            const int mrow0 = m0 + (mt * PAIR + rank) * 128 + quarter * 32;
             const long m = (long)mrow0 + lane;
             if (p.tma_store && p.out_f16) {
-                // one 64-column x 32-row box of fp16 per accumulator
+              // 64-column x 32-row boxes of fp16
+#pragma unroll 1
+              for (int c64 = part; c64 < BNU / 64; c64 += 4) {
                 uint32_t v[32], w[32];
-                const int col = part * 64;
-                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BN + col), v);
-                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BN + col + 32), w);
+                const int col = c64 * 64;
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BNU + col), v);
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BNU + col + 32), w);
                 asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                 __syncwarp();
                 uint32_t h[32];
@@ -378,12 +489,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) tma_store_2d(&ymap, stg, n0 + col, mrow0);
+              }
             } else {
 #pragma unroll 1
-                for (int cc = 0; cc < 2; cc++) {
-                    const int col = part * 64 + cc * 32;
+                for (int c32 = part; c32 < BNU / 32; c32 += 4) {
+                    const int col = c32 * 32;
                     uint32_t v[32];
-                    tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BN + col), v);
+                    tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BNU + col), v);
                     if (p.tma_store) {
                         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // staging free again
                         __syncwarp();
@@ -421,9 +533,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     __syncthreads();
+    // PAIR == 2: neither CTA may free its tensor memory or leave (its shared memory is read by
+    // the pair's MMAs and its barriers are arrived on remotely) before both are done.
+    if constexpr (PAIR == 2) cluster_sync_all();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+        if constexpr (PAIR == 2)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
 }
 
@@ -475,25 +593,63 @@ bool make_ymap(CUtensorMap* map, void* y, int M, int N, int out_f16) {
     return r == CUDA_SUCCESS;
 }
 
-template <int MT>
-int launch_tc(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
+template <int MT, int BN, int PAIR>
+int launch_tc_bn(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
     CUtensorMap ymap;
     memset(&ymap, 0, sizeof(ymap));
     p.tma_store = make_ymap(&ymap, p.y, p.M, p.N, p.out_f16) ? 1 : 0;
-    using C = tc::Cfg<MT>;
+    using C = tc::Cfg<MT, BN, PAIR>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        e = cudaFuncSetAttribute(tc::gemm_tc_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        e = cudaFuncSetAttribute(tc::gemm_tc_kernel<MT, BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemm_tc smem)");
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    dim3 grid((unsigned)((p.N + tc::BN - 1) / tc::BN), (unsigned)((p.M + 128 * MT - 1) / (128 * MT)), 1);
-    tc::gemm_tc_kernel<MT><<<grid, tc::kThreads, C::SMEM, stream>>>(map, ymap, p);
-    SX8_LAUNCH_CHECK("gemm_tc_kernel");
+    dim3 grid((unsigned)(PAIR * ((p.N + C::BNU - 1) / C::BNU)),
+              (unsigned)((p.M + 128 * MT * PAIR - 1) / (128 * MT * PAIR)), 1);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(tc::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = PAIR;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (PAIR == 2) ? 1 : 0;
+    e = cudaLaunchKernelEx(&cfg, tc::gemm_tc_kernel<MT, BN, PAIR>, map, ymap, p);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(gemm_tc_kernel)");
     return SX8_OK;
+}
+
+// Columns per CTA: the widest tile (most reuse of each decoded weight and each X tile), narrowed
+// only while twice as many CTAs still fit in one wave -- a second wave costs more than it gains.
+template <int MT>
+int launch_tc(const CUtensorMap& map, const tc::Params& p, cudaStream_t stream) {
+    static const int force_bn = getenv("SX8_GEMM_BN") ? atoi(getenv("SX8_GEMM_BN")) : 0;
+    const long mtiles = (p.M + 128 * MT - 1) / (128 * MT);
+    int bn = 256;
+    if (((p.N + 127) / 128) * mtiles <= 148) bn = 128;
+    if (bn == 128 && ((p.N + 63) / 64) * mtiles <= 148 && ((p.N + 127) / 128) * mtiles <= 37) bn = 64;
+    if (force_bn == 64 || force_bn == 128 || force_bn == 256) bn = force_bn;
+    if (bn == 256) return launch_tc_bn<MT, 256, 1>(map, p, stream);
+    if (bn == 128) return launch_tc_bn<MT, 128, 1>(map, p, stream);
+    return launch_tc_bn<MT, 64, 1>(map, p, stream);
+}
+
+// Shape rule.  Two-CTA tiles (256*MT rows x 256 columns per pair) halve the decode work per
+// MMA and win once there are enough rows to fill them; below that the one-CTA tiles.
+int launch_auto(const CUtensorMap& map, const tc::Params& p, cudaStream_t stream) {
+    static const int pair_mode = getenv("SX8_GEMM_PAIR") ? atoi(getenv("SX8_GEMM_PAIR")) : 0;
+    if (pair_mode == 2 || (pair_mode == 1 && p.M > 256)) return launch_tc_bn<2, 128, 2>(map, p, stream);
+    if (pair_mode == 1 && p.M > 128) return launch_tc_bn<1, 128, 2>(map, p, stream);
+    if (p.M > 128) return launch_tc<2>(map, p, stream);
+    return launch_tc<1>(map, p, stream);
 }
 
 }  // namespace
@@ -539,8 +695,7 @@ int gemm_tc_launch(const void* x, int M, int K, long ldx, const void* wt16, cons
         return SX8_E_CUDA;
     }
     tc::Params p{(const uint8_t*)wt16, pb, y, M, N, n_cb, (int)t16_tiles(N), out_f16, 0};
-    if (M > 128) return launch_tc<2>(map, p, stream);
-    return launch_tc<1>(map, p, stream);
+    return launch_auto(map, p, stream);
 }
 
 }  // namespace sx8
@@ -631,6 +786,5 @@ extern "C" int sx8_gemm_static(const void* x, int M, int K, long ldx, const void
         return SX8_E_CUDA;
     }
     tc::Params p{(const uint8_t*)wt16, pb, y, M, N, n_cb, (int)t16_tiles(N), out_f16, 0};
-    if (M > 128) return launch_tc<2>(map, p, stream);
-    return launch_tc<1>(map, p, stream);
+    return launch_auto(map, p, stream);
 }

@@ -212,8 +212,8 @@ struct GemvCfg {
     static int smem_bytes(int kb_per_cta) { return FIXED + kb_per_cta * DT_KB; }
 };
 
-template <int NT, int KB_S, int STAGES>
-__global__ void __launch_bounds__(kThreads, 3) gemv_kernel(GemvParams p) {
+template <int NT, int KB_S, int STAGES, int MINB = 3>
+__global__ void __launch_bounds__(kThreads, MINB) gemv_kernel(GemvParams p) {
     using C = GemvCfg<NT, KB_S, STAGES>;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
@@ -614,7 +614,7 @@ Choice choose(int N, int n_cb) {
     return best;
 }
 
-template <int NT, int KB_S, int STAGES>
+template <int NT, int KB_S, int STAGES, int MINB = 3>
 int launch_gemv(const GemvParams& p, int grid_x, unsigned flags, cudaStream_t stream) {
     using C = GemvCfg<NT, KB_S, STAGES>;
     static bool attr_set[64] = {};
@@ -622,7 +622,7 @@ int launch_gemv(const GemvParams& p, int grid_x, unsigned flags, cudaStream_t st
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        e = cudaFuncSetAttribute(gemv_kernel<NT, KB_S, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(gemv_kernel<NT, KB_S, STAGES, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  C::smem_bytes(kMaxKbPerCta));
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemv smem)");
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
@@ -649,7 +649,7 @@ int launch_gemv(const GemvParams& p, int grid_x, unsigned flags, cudaStream_t st
     }
     cfg.attrs = attrs;
     cfg.numAttrs = na;
-    e = cudaLaunchKernelEx(&cfg, gemv_kernel<NT, KB_S, STAGES>, p);
+    e = cudaLaunchKernelEx(&cfg, gemv_kernel<NT, KB_S, STAGES, MINB>, p);
     if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(gemv_kernel)");
     return SX8_OK;
 }
