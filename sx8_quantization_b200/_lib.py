@@ -6,7 +6,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libsx8b200.so")
+# SX8_LIB_PATH selects another build of the same library (e.g. one compiled with extra flags)
+LIB_PATH = os.environ.get("SX8_LIB_PATH") or os.path.join(_HERE, "libsx8b200.so")
 
 _vp, _i, _l, _sz, _u = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_size_t, ctypes.c_uint
 

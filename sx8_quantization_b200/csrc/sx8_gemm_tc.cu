@@ -27,6 +27,7 @@ namespace tc {
 
 constexpr int BK = 64, KB_STAGE = 2;
 constexpr int kDecodeWarps = 16, kWarps = kDecodeWarps + 3, kThreads = kWarps * 32;
+constexpr int kGroupWarps = kDecodeWarps / 2;      // decode warps working on one stage
 constexpr int kSmemMax = 232448;                 // opt-in shared memory per CTA on sm_100
 constexpr int A_TILE = 128 * 128;                 // 128 rows x 64 fp16, bytes
 constexpr int P_TAB = KB_STAGE * 128;             // PCA table: per kb 2 x 32 fp16
@@ -43,19 +44,13 @@ struct Cfg {
     static constexpr int B_TILE = BN * 128;                     // BN rows x 64 fp16
     static constexpr int P_SLAB = TILES * KB_STAGE * T16_UNIT;  // TILES tiles x 2 kb
     static constexpr int P_STAGE = P_SLAB + P_TAB;
-    static constexpr int SA = 3, SB = (BN >= 256) ? 2 : (PAIR == 2 ? 4 : 3);
-    // packed-slab stages: as deep as shared memory allows (at most 8) -- these loads come from
-    // HBM with the longest latency of the pipeline and run ahead of everything else
-    static constexpr int SP_FIT = (kSmemMax - 2048 - SA * MT * A_TILE - SB * B_TILE) / P_STAGE;
-    static constexpr int SP = SP_FIT > 8 ? 8 : SP_FIT;
-    static_assert(SP >= 3, "too few packed-slab stages");
-    static constexpr int OFF_A = 0;
-    static constexpr int OFF_B = OFF_A + SA * MT * A_TILE;
-    static constexpr int OFF_P = OFF_B + SB * B_TILE;
-    static constexpr int OFF_BAR = OFF_P + SP * P_STAGE;
-    static constexpr int N_BAR = 3 * SA + 2 * SB + 2 * SP + 1;
-    static constexpr int OFF_TMEM = OFF_BAR + N_BAR * 8;
-    static constexpr int SMEM = OFF_TMEM + 16 + 1024;   // + slack to align the base to 1024 B
+    // Stage counts are launch parameters (Params::sa/sb/sp): X-tile stages, decoded-operand
+    // stages, packed-slab stages.  Shared memory, in order: X tiles, operand tiles, slabs,
+    // barriers, the tensor-memory address.
+    static constexpr int smem_bytes(int sa, int sb, int sp) {
+        return sa * MT * A_TILE + sb * B_TILE + sp * P_STAGE + (3 * sa + 2 * sb + 2 * sp + 1) * 8 + 16 +
+               1024;   // + slack to align the base to 1024 B
+    }
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -68,36 +63,71 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// CL = true: acquire at cluster scope (the barrier is arrived on by the peer CTA of a pair or
+// by a two-CTA tcgen05.commit).
+template <bool CL>
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned code) {
-    for (uint32_t i = 0; i < kSpin; i++)
-        if (mbar_try_wait(bar, parity)) return true;
-    atomicOr(&g_sx8_error_flag, code);
-    return false;
-}
-// Cluster-scope variants for the two-CTA mode: barriers of the leader CTA are arrived on by
-// the peer CTA (and by tcgen05.commit), so waits acquire at cluster scope.
-__device__ __forceinline__ bool mbar_wait_cl(uint32_t bar, uint32_t parity, unsigned code) {
-    for (uint32_t i = 0; i < kSpin; i++) {
-        uint32_t ok;
+    if constexpr (CL)
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
             "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-    }
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Non-blocking probe.  A wait costs a shared-memory round trip (a few hundred cycles) even
+// when the phase has long completed, and a warp that waits on two barriers per stage pays it
+// twice, serially, before its real work.  So every role probes the barriers of its NEXT
+// stage before it starts on the current one and looks at the answer afterwards.
+template <bool CL>
+__device__ __forceinline__ uint32_t mbar_probe(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    if constexpr (CL)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+template <bool CL>
+__device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, unsigned code) {
+    for (uint32_t i = 0; i < kSpin; i++)
+        if (mbar_try_wait<CL>(bar, parity)) return true;
     atomicOr(&g_sx8_error_flag, code);
     return false;
 }
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned code) {
+    return mbar_wait_t<false>(bar, parity, code);
+}
+__device__ __forceinline__ bool mbar_wait_cl(uint32_t bar, uint32_t parity, unsigned code) {
+    return mbar_wait_t<true>(bar, parity, code);
+}
+// Position in a ring of n stages: slot s, round r (the phase parity of a "full" barrier is
+// r & 1; an "empty" barrier is waited on from round 1 with parity (r - 1) & 1).
+struct Ring {
+    int s, n;
+    uint32_t r;
+    __device__ __forceinline__ Ring(int n_) : s(0), n(n_), r(0) {}
+    __device__ __forceinline__ Ring next() const {
+        Ring q = *this;
+        if (++q.s == q.n) { q.s = 0; q.r++; }
+        return q;
+    }
+};
 __device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t cta_rank) {
     uint32_t r;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta_rank));
@@ -210,6 +240,9 @@ struct Params {
     void* y;
     int M, N, n_cb, n_tiles, out_f16;
     int tma_store;   // Y rows are 16-byte multiples: the epilogue stores through the Y tensor map
+    int sa, sb, sp;  // pipeline depths: X-tile, decoded-operand and packed-slab stages
+    int debug;       // timing experiments only (results are wrong): 1 = skip the decode math, 2 = skip the
+                     // MMAs, 4 = skip the packed-slab copies, 8 = skip the X-tile copies
 };
 
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
@@ -221,20 +254,22 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
 
 template <int MT, int BN, int PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap, Params p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap,
+               const __grid_constant__ CUtensorMap wmap, Params p) {
     using C = Cfg<MT, BN, PAIR>;
     constexpr int B_TILE = C::B_TILE, P_SLAB = C::P_SLAB, P_STAGE = C::P_STAGE, TILES = C::TILES, BNU = C::BNU;
     static_assert(MT * BNU <= 512, "accumulators exceed tensor memory");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t sA = sbase + C::OFF_A, sB = sbase + C::OFF_B, sP = sbase + C::OFF_P;
-    const uint32_t bar0 = sbase + C::OFF_BAR;
-    const uint32_t a_full = bar0, a_empty = a_full + 8 * C::SA;
-    const uint32_t b_full = a_empty + 8 * C::SA, b_empty = b_full + 8 * C::SB;
-    const uint32_t p_full = b_empty + 8 * C::SB, p_empty = p_full + 8 * C::SP;
-    const uint32_t acc_full = p_empty + 8 * C::SP;
+    const int SA = p.sa, SB = p.sb, SP = p.sp;
+    const uint32_t sA = sbase, sB = sA + SA * MT * A_TILE, sP = sB + SB * B_TILE;
+    const uint32_t bar0 = sP + SP * P_STAGE;
+    const uint32_t a_full = bar0, a_empty = a_full + 8 * SA;
+    const uint32_t b_full = a_empty + 8 * SA, b_empty = b_full + 8 * SB;
+    const uint32_t p_full = b_empty + 8 * SB, p_empty = p_full + 8 * SP;
+    const uint32_t acc_full = p_empty + 8 * SP;
     const uint32_t a_peer = acc_full + 8;        // leader only: the peer CTA's X tiles have landed
-    const uint32_t tmem_slot = sbase + C::OFF_TMEM;
+    const uint32_t tmem_slot = a_peer + 8 * SA;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // PAIR == 2: the cluster is two consecutive CTAs along x; rank 0 leads (issues the MMAs).
@@ -245,10 +280,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     const int n_ks = (p.n_cb + KB_STAGE - 1) / KB_STAGE;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::SA; s++) { mbar_init(a_full + 8 * s, 1); mbar_init(a_empty + 8 * s, 1); }
-        for (int s = 0; s < C::SA; s++) mbar_init(a_peer + 8 * s, 1);
-        for (int s = 0; s < C::SB; s++) { mbar_init(b_full + 8 * s, kDecodeWarps * PAIR); mbar_init(b_empty + 8 * s, 1); }
-        for (int s = 0; s < C::SP; s++) { mbar_init(p_full + 8 * s, 1); mbar_init(p_empty + 8 * s, kDecodeWarps); }
+        for (int s = 0; s < SA; s++) { mbar_init(a_full + 8 * s, 1); mbar_init(a_empty + 8 * s, 1); }
+        for (int s = 0; s < SA; s++) mbar_init(a_peer + 8 * s, 1);
+        for (int s = 0; s < SB; s++) { mbar_init(b_full + 8 * s, kGroupWarps * PAIR); mbar_init(b_empty + 8 * s, 1); }
+        for (int s = 0; s < SP; s++) { mbar_init(p_full + 8 * s, 1); mbar_init(p_empty + 8 * s, kGroupWarps); }
         mbar_init(acc_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -270,32 +305,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     if (warp == kWarps - 1) {
         // ------------------------------------------------------------ producer of packed slabs
         bool ok = true;
+        Ring rp(SP);
         for (int ks = 0; ks < n_ks; ks++) {
             const int kb0 = ks * KB_STAGE;
             const int rows = min(KB_STAGE, p.n_cb - kb0);
             {   // packed slabs + PCA table: lane i < TILES copies tile i, lane 16 the table
-                const int s = ks % C::SP;
-                if (ks >= C::SP && ok) ok = mbar_wait(p_empty + 8 * s, ((ks / C::SP) - 1) & 1, 0x10u);
-                const int tiles = max(0, min(TILES, p.n_tiles - tile0));
-                if (lane == 0)
-                    mbar_expect_tx(p_full + 8 * s, (uint32_t)rows * ((uint32_t)tiles * T16_UNIT + 128u));
-                __syncwarp();
+                const int s = rp.s;
+                if (rp.r > 0 && ok) ok = mbar_wait(p_empty + 8 * s, (rp.r - 1) & 1, 0x10u);
+                rp = rp.next();
+                if (p.debug & 4) {
+                    if (lane == 0) mbar_arrive(p_full + 8 * s);
+                    continue;
+                }
+                // One tensor copy brings the slabs of all TILES tiles: the blob is a 2-D array of
+                // 32-bit words, one row of n_cb * 120 words per 16-column tile; the box is
+                // TILES rows x 240 words (two block rows).  Tiles or block rows past the end
+                // arrive as zeros (and count as bytes).
                 const uint32_t dst = sP + s * P_STAGE;
-                if (lane < TILES && tile0 + lane < p.n_tiles)
-                    bulk_g2s(dst + lane * (KB_STAGE * T16_UNIT),
-                             p.blob + ((long)(tile0 + lane) * p.n_cb + kb0) * T16_UNIT, (uint32_t)rows * T16_UNIT,
-                             p_full + 8 * s);
-                if (lane == 16)
+                if (lane == 0) {
+                    mbar_expect_tx(p_full + 8 * s, (uint32_t)P_SLAB + (uint32_t)rows * 128u);
+                    tma_load_2d(dst, &wmap, kb0 * (T16_UNIT / 4), tile0, p_full + 8 * s);
                     bulk_g2s(dst + P_SLAB, p.pb + (long)kb0 * 64, (uint32_t)rows * 128u, p_full + 8 * s);
+                }
+                __syncwarp();
             }
         }
     } else if (warp == 0) {
         // ------------------------------------------------------------ producer of X tiles
         bool ok = true;
+        Ring ra(SA);
         for (int ks = 0; ks < n_ks; ks++) {
             {   // MT boxes of 64 (K) x 128 (rows); columns/rows out of range read as zero
-                const int s = ks % C::SA;
-                if (ks >= C::SA && ok) ok = mbar_wait(a_empty + 8 * s, ((ks / C::SA) - 1) & 1, 0x20u);
+                const int s = ra.s;
+                if (ra.r > 0 && ok) ok = mbar_wait(a_empty + 8 * s, (ra.r - 1) & 1, 0x20u);
+                ra = ra.next();
+                if (p.debug & 8) {
+                    if (lane == 0) mbar_arrive(a_full + 8 * s);
+                    continue;
+                }
                 if (lane == 0) {
                     mbar_expect_tx(a_full + 8 * s, (uint32_t)(MT * A_TILE));
                     for (int mt = 0; mt < MT; mt++)
@@ -310,29 +357,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         // tells the leader that this CTA's X tiles of a stage have landed
         bool ok = true;
         const uint32_t remote = mapa_u32(a_peer, 0u);
+        Ring ra(SA);
         for (int ks = 0; ks < n_ks; ks++) {
-            const int sa = ks % C::SA;
-            if (ok) ok = mbar_wait(a_full + 8 * sa, (ks / C::SA) & 1, 0x800u);
+            if (ok) ok = mbar_wait(a_full + 8 * ra.s, ra.r & 1, 0x800u);
             __syncwarp();
-            if (lane == 0) mbar_arrive_cl(remote + 8 * sa);
+            if (lane == 0) mbar_arrive_cl(remote + 8 * ra.s);
+            ra = ra.next();
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         bool ok = true;
+        Ring ra(SA), rb(SB);
+        uint32_t pre_a = 0, pre_b = 0, pre_c = (PAIR == 2) ? 0u : 1u;   // answers of the early probes
         for (int ks = 0; ks < n_ks; ks++) {
-            const int sa = ks % C::SA, sb = ks % C::SB;
-            if (ok) ok = mbar_wait(a_full + 8 * sa, (ks / C::SA) & 1, 0x40u);
-            if constexpr (PAIR == 2) {
-                if (ok) ok = mbar_wait_cl(a_peer + 8 * sa, (ks / C::SA) & 1, 0x1000u);
-                if (ok) ok = mbar_wait_cl(b_full + 8 * sb, (ks / C::SB) & 1, 0x80u);
-            } else {
-                if (ok) ok = mbar_wait(b_full + 8 * sb, (ks / C::SB) & 1, 0x80u);
+            const int sa = ra.s, sb = rb.s;
+            if (!pre_a && ok) ok = mbar_wait(a_full + 8 * sa, ra.r & 1, 0x40u);
+            if (!pre_c && ok) ok = mbar_wait_cl(a_peer + 8 * sa, ra.r & 1, 0x1000u);
+            if (!pre_b && ok) ok = mbar_wait_t<PAIR == 2>(b_full + 8 * sb, rb.r & 1, 0x80u);
+            ra = ra.next();
+            rb = rb.next();
+            if (ks + 1 < n_ks) {   // probe the next stage now, read the answers next iteration
+                pre_a = mbar_probe<false>(a_full + 8 * ra.s, ra.r & 1);
+                if constexpr (PAIR == 2) pre_c = mbar_probe<true>(a_peer + 8 * ra.s, ra.r & 1);
+                pre_b = mbar_probe<PAIR == 2>(b_full + 8 * rb.s, rb.r & 1);
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (lane == 0) {
                 const uint64_t bdesc = umma_desc(sB + sb * B_TILE);
 #pragma unroll
-                for (int mt = 0; mt < MT; mt++) {
+                for (int mt = 0; mt < MT && !(p.debug & 2); mt++) {
                     const uint64_t adesc = umma_desc(sA + (sa * MT + mt) * A_TILE);
 #pragma unroll
                     for (int k = 0; k < BK / 16; k++) {   // +32 bytes along K inside the swizzle atom
@@ -344,7 +397,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                                      idesc_for(BNU, 128), (ks > 0 || k > 0) ? 1u : 0u);
                     }
                 }
-                if constexpr (PAIR == 2) {
+                if (p.debug & 32) {   // handshake experiment: plain arrivals instead of commits
+                    mbar_arrive(a_empty + 8 * sa);
+                    mbar_arrive(b_empty + 8 * sb);
+                    if (ks == n_ks - 1) mbar_arrive(acc_full);
+                } else if constexpr (PAIR == 2) {
                     umma_commit_pair(a_empty + 8 * sa);
                     umma_commit_pair(b_empty + 8 * sb);
                     if (ks == n_ks - 1) umma_commit_pair(acc_full);
@@ -364,18 +421,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         const float kBase = 0.25f * 0.015873f * 512.0f;   // levels are formed scaled by 2^-9
         bool ok = true;
         const uint32_t b_full_leader = (PAIR == 2) ? mapa_u32(b_full, 0u) : b_full;
-        for (int ks = 0; ks < n_ks; ks++) {
-            const int sp = ks % C::SP, sb = ks % C::SB;
+        // The warps form two groups that take alternate stages: the fixed cost a warp pays per
+        // stage (barrier round trips, the proxy fence) is then spread over twice the items, and
+        // one group's waits overlap the other group's arithmetic.
+        const int grp = dw / kGroupWarps, gw = dw % kGroupWarps;
+        Ring rp(SP), rb(SB);
+        if (grp == 1) { rp = rp.next(); rb = rb.next(); }
+        uint32_t pre_p = 0, pre_b = (rb.r == 0) ? 1u : 0u;   // answers of the early probes
+        for (int ks = grp; ks < n_ks; ks += 2) {
+            const int sp = rp.s, sb = rb.s;
             const int rows = min(KB_STAGE, p.n_cb - ks * KB_STAGE);
-            if (ok) ok = mbar_wait(p_full + 8 * sp, (ks / C::SP) & 1, 0x100u);
-            if (ks >= C::SB && ok) {
-                if constexpr (PAIR == 2) ok = mbar_wait_cl(b_empty + 8 * sb, ((ks / C::SB) - 1) & 1, 0x200u);
-                else ok = mbar_wait(b_empty + 8 * sb, ((ks / C::SB) - 1) & 1, 0x200u);
+            if (!pre_p && ok) ok = mbar_wait(p_full + 8 * sp, rp.r & 1, 0x100u);
+            if (!pre_b && ok) ok = mbar_wait_t<PAIR == 2>(b_empty + 8 * sb, (rb.r - 1) & 1, 0x200u);
+            rp = rp.next().next();
+            rb = rb.next().next();
+            if (ks + 2 < n_ks) {   // probe this group's next stage now, read the answers next iteration
+                pre_p = mbar_probe<false>(p_full + 8 * rp.s, rp.r & 1);
+                pre_b = (rb.r == 0) ? 1u : mbar_probe<PAIR == 2>(b_empty + 8 * rb.s, (rb.r - 1) & 1);
             }
             const uint32_t pst = sP + sp * P_STAGE, bst = sB + sb * B_TILE;
-            // work items (tile, block row) are dealt round-robin to the 16 decode warps
+            // work items (tile, block row) are dealt round-robin to the group's warps
 #pragma unroll
-            for (int item = dw; item < TILES * KB_STAGE; item += kDecodeWarps) {
+            for (int item = gw; item < TILES * KB_STAGE && !(p.debug & 1); item += kGroupWarps) {
                 const int tl = item % TILES, r = item / TILES;
                 const bool tile_ok = tile0 + tl < p.n_tiles;
                 // Column 16*tl + g sits in operand row 16*tl + rho(g), rho(g) = 4*(g&1) + (g>>1): the
@@ -439,7 +506,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                     sts128(bst + rowB * 128 + ((c ^ (rowB & 7u)) << 4), wb);
                 }
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic stores -> tensor-core reads
+            if (!(p.debug & 64))
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic stores -> tensor-core reads
             __syncwarp();
             if (lane == 0) {
                 if constexpr (PAIR == 2) mbar_arrive_cl(b_full_leader + 8 * sb);
@@ -455,7 +523,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         const int part = dw >> 2;                // the four warps of a quarter share the BN columns
         // Staging for the TMA store: 4 KB per warp in the (now idle) A and B stages; rows of 128
         // bytes, 16-byte chunks XOR-swizzled with the row index (the Y tensor map's swizzle).
-        static_assert(C::SA * MT * A_TILE + C::SB * B_TILE >= kDecodeWarps * 4096, "staging does not fit");
+        // (the host checks that the X and operand stages together hold the 64 KB of staging)
         const uint32_t stg = sA + (uint32_t)dw * 4096u;
 #pragma unroll 1
         for (int mt = 0; mt < MT; mt++) {
@@ -599,21 +667,57 @@ int launch_tc_bn(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
     memset(&ymap, 0, sizeof(ymap));
     p.tma_store = make_ymap(&ymap, p.y, p.M, p.N, p.out_f16) ? 1 : 0;
     using C = tc::Cfg<MT, BN, PAIR>;
+    // Pipeline depths.  The packed slabs come from HBM with the longest latency and get every
+    // stage that is left (at most 8); X tiles come from L2.
+    static const int env_sa = getenv("SX8_GEMM_SA") ? atoi(getenv("SX8_GEMM_SA")) : 0;
+    static const int env_sb = getenv("SX8_GEMM_SB") ? atoi(getenv("SX8_GEMM_SB")) : 0;
+    static const int env_sp = getenv("SX8_GEMM_SP") ? atoi(getenv("SX8_GEMM_SP")) : 0;
+    static const int env_debug = getenv("SX8_GEMM_DEBUG") ? atoi(getenv("SX8_GEMM_DEBUG")) : 0;
+    p.debug = env_debug;
+    p.sa = env_sa > 0 ? env_sa : 3;
+    p.sb = env_sb > 0 ? env_sb : ((BN >= 256) ? 2 : (PAIR == 2 ? 4 : 3));
+    if (env_sp > 0) {
+        p.sp = env_sp;
+    } else {
+        p.sp = 8;
+        while (p.sp > 2 && C::smem_bytes(p.sa, p.sb, p.sp) > tc::kSmemMax) p.sp--;
+    }
+    const int smem = C::smem_bytes(p.sa, p.sb, p.sp);
+    if (p.sa < 2 || p.sb < 2 || p.sp < 2 || smem > tc::kSmemMax ||
+        p.sa * MT * tc::A_TILE + p.sb * C::B_TILE < tc::kDecodeWarps * 4096) {
+        set_error("sx8_gemm: pipeline depths (%d, %d, %d) do not fit shared memory", p.sa, p.sb, p.sp);
+        return SX8_E_UNSUPPORTED;
+    }
     static bool attr_set[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        e = cudaFuncSetAttribute(tc::gemm_tc_kernel<MT, BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        e = cudaFuncSetAttribute(tc::gemm_tc_kernel<MT, BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 tc::kSmemMax);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemm_tc smem)");
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    CUtensorMap wmap;
+    {
+        cuuint64_t gdim[2] = {(cuuint64_t)p.n_cb * (T16_UNIT / 4), (cuuint64_t)p.n_tiles};
+        cuuint64_t gstr[1] = {(cuuint64_t)p.n_cb * T16_UNIT};
+        cuuint32_t box[2] = {(cuuint32_t)(tc::KB_STAGE * T16_UNIT / 4), (cuuint32_t)C::TILES};
+        cuuint32_t estr[2] = {1u, 1u};
+        CUresult r = encode_fn()(&wmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, (void*)p.blob, gdim, gstr, box, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            set_error("sx8_gemm: cuTensorMapEncodeTiled(blob) failed (%d)", (int)r);
+            return SX8_E_CUDA;
+        }
     }
     dim3 grid((unsigned)(PAIR * ((p.N + C::BNU - 1) / C::BNU)),
               (unsigned)((p.M + 128 * MT * PAIR - 1) / (128 * MT * PAIR)), 1);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(tc::kThreads, 1, 1);
-    cfg.dynamicSmemBytes = C::SMEM;
+    cfg.dynamicSmemBytes = (size_t)smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -622,7 +726,7 @@ int launch_tc_bn(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (PAIR == 2) ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, tc::gemm_tc_kernel<MT, BN, PAIR>, map, ymap, p);
+    e = cudaLaunchKernelEx(&cfg, tc::gemm_tc_kernel<MT, BN, PAIR>, map, ymap, wmap, p);
     if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(gemm_tc_kernel)");
     return SX8_OK;
 }
@@ -642,12 +746,16 @@ int launch_tc(const CUtensorMap& map, const tc::Params& p, cudaStream_t stream) 
     return launch_tc_bn<MT, 64, 1>(map, p, stream);
 }
 
-// Shape rule.  Two-CTA tiles (256*MT rows x 256 columns per pair) halve the decode work per
-// MMA and win once there are enough rows to fill them; below that the one-CTA tiles.
+// Shape rule.  Two-CTA tiles (512 rows x 256 columns per pair) halve the decode work and the
+// operand reads per MMA and win as soon as M fills them; up to 256 rows the one-CTA tiles.
+// SX8_GEMM_PAIR overrides for experiments: 0 = never pair, 2 = always 512-row pairs,
+// 3 = always 256-row pairs.
 int launch_auto(const CUtensorMap& map, const tc::Params& p, cudaStream_t stream) {
-    static const int pair_mode = getenv("SX8_GEMM_PAIR") ? atoi(getenv("SX8_GEMM_PAIR")) : 0;
+    static const int pair_mode = getenv("SX8_GEMM_PAIR") ? atoi(getenv("SX8_GEMM_PAIR")) : 1;
+    static const int force_mt = getenv("SX8_GEMM_MT") ? atoi(getenv("SX8_GEMM_MT")) : 0;
+    if (pair_mode == 3) return launch_tc_bn<1, 128, 2>(map, p, stream);
     if (pair_mode == 2 || (pair_mode == 1 && p.M > 256)) return launch_tc_bn<2, 128, 2>(map, p, stream);
-    if (pair_mode == 1 && p.M > 128) return launch_tc_bn<1, 128, 2>(map, p, stream);
+    if (force_mt == 1) return launch_tc<1>(map, p, stream);
     if (p.M > 128) return launch_tc<2>(map, p, stream);
     return launch_tc<1>(map, p, stream);
 }
@@ -694,7 +802,7 @@ int gemm_tc_launch(const void* x, int M, int K, long ldx, const void* wt16, cons
         set_error("sx8_gemm: cuTensorMapEncodeTiled failed (%d)", (int)r);
         return SX8_E_CUDA;
     }
-    tc::Params p{(const uint8_t*)wt16, pb, y, M, N, n_cb, (int)t16_tiles(N), out_f16, 0};
+    tc::Params p{(const uint8_t*)wt16, pb, y, M, N, n_cb, (int)t16_tiles(N), out_f16, 0, 0, 0, 0, 0};
     return launch_auto(map, p, stream);
 }
 
@@ -785,6 +893,6 @@ extern "C" int sx8_gemm_static(const void* x, int M, int K, long ldx, const void
         set_error("sx8_gemm_static: cuTensorMapEncodeTiled failed (%d)", (int)r);
         return SX8_E_CUDA;
     }
-    tc::Params p{(const uint8_t*)wt16, pb, y, M, N, n_cb, (int)t16_tiles(N), out_f16, 0};
+    tc::Params p{(const uint8_t*)wt16, pb, y, M, N, n_cb, (int)t16_tiles(N), out_f16, 0, 0, 0, 0, 0};
     return launch_auto(map, p, stream);
 }

@@ -65,6 +65,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking probe of a phase.  A wait costs a shared-memory round trip even when the
+// phase completed long ago, so the consumers probe the NEXT stage's barrier before they start
+// on the current stage and read the answer afterwards.
+__device__ __forceinline__ uint32_t mbar_probe(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
 // Bounded wait: gives up after kSpinLimit polls, records the failure in the device
 // error word and returns false; the caller then stops waiting for the rest of the kernel.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned code) {
@@ -371,11 +385,13 @@ __global__ void __launch_bounds__(kThreads, MINB) gemv_kernel(GemvParams p) {
         const uint32_t sh2 = 8u + 2u * (uint32_t)t;
         bool ok = true;
         int it = 0;
+        uint32_t pre = 0;   // answer of the early probe of this iteration's barrier
         for (int gi = 0; gi < my_groups; gi++) {
             const int grp = (int)blockIdx.x + gi * (int)gridDim.x - sg.group0;
             for (int j = 0; j < n_iter; j++, it++) {
                 int s = it % STAGES;
-                if (ok) ok = mbar_wait(bar_full + 8 * s, (it / STAGES) & 1, 2u);
+                if (!pre && ok) ok = mbar_wait(bar_full + 8 * s, (it / STAGES) & 1, 2u);
+                pre = mbar_probe(bar_full + 8 * ((it + 1) % STAGES), ((it + 1) / STAGES) & 1);
                 int rows = min(KB_S, kb_end - (kb_begin + j * KB_S));
                 uint32_t st = sbase + s * C::STAGE;
 #pragma unroll
