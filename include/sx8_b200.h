@@ -182,6 +182,22 @@ int sx8_repack_v44(const void* dmin_f16, const void* dmax_f16, const uint8_t* co
                    long out_f, int n_cb, int hdr_bytes, void* hdr_out, void* levels_out,
                    void* stream);
 
+/* ---- interleaved 30-byte blocks (GGUF tensor data) -----------------------------------
+ * A block_sx8 record is {dmin f16 @0, dmax f16 @2, config @4, qh[16] @5, ql[8] @21,
+ * coeff @29}, n-major (bid = n*n_cb + kb): the layout of the llama.cpp fork's GGUF files
+ * (ref: scripts/convert_pkl_to_gguf_sx8.py:20-38 blockify_vec; patches/llama-cpp-sx8.patch
+ * :136-144 struct block_sx8) and of docs/SX8_FLASH_V4_3_SPEC.md:13-25.
+ * sx8_repack_t16_blocks: records -> device layout in one pass (GGUF tensor -> GEMV-ready).
+ * sx8_blocks_from_planes / sx8_planes_from_blocks: the container's planes <-> records,
+ * byte-exact both ways.  `blocks` must be 2-byte aligned.                              */
+int sx8_repack_t16_blocks(const void* blocks, long out_f, int n_cb, void* wt16_out, void* stream);
+int sx8_blocks_from_planes(const void* dmin_f16, const void* dmax_f16, const uint8_t* config,
+                           const uint8_t* coeff, const uint8_t* levels_hi, const uint8_t* levels_lo,
+                           long n_blk, void* blocks_out, void* stream);
+int sx8_planes_from_blocks(const void* blocks, long n_blk, void* dmin_f16, void* dmax_f16,
+                           uint8_t* config, uint8_t* coeff, uint8_t* levels_hi, uint8_t* levels_lo,
+                           void* stream);
+
 /* Device-side error word of the bounded waits inside the pipelined kernels: 0 when no
  * wait ever ran out.  Reads back synchronously (cudaMemcpy) -- for tests and health
  * checks, not for the hot path.                                                      */

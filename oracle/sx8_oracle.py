@@ -323,3 +323,31 @@ def to_t16(qt):
     blob[:, :, :96] = lev.reshape(nt, n_cb, 96)
     blob[:, :, 96:] = hdr.reshape(nt, n_cb, 24)
     return np.ascontiguousarray(blob).view(np.uint8).reshape(-1)
+
+
+# ---------------------------------------------------------------- interleaved 30-byte blocks
+def blocks_from_planes(qt):
+    """(n_blk, 30) u8 block_sx8 records {dmin, dmax, config, qh[16], ql[8], coeff}: the layout
+    ref scripts/convert_pkl_to_gguf_sx8.py:20-38 (blockify_vec) writes into GGUF tensors and
+    docs/SX8_FLASH_V4_3_SPEC.md:13-25 specifies."""
+    nb = int(qt["n_blocks"])
+    out = np.empty((nb, 30), np.uint8)
+    out[:, 0:2] = np.ascontiguousarray(qt["dmin"], dtype=np.float16).reshape(-1).view(np.uint8).reshape(nb, 2)
+    out[:, 2:4] = np.ascontiguousarray(qt["dmax"], dtype=np.float16).reshape(-1).view(np.uint8).reshape(nb, 2)
+    out[:, 4] = np.asarray(qt["config"], dtype=np.uint8).reshape(-1)
+    out[:, 5:21] = np.asarray(qt["levels_hi"], dtype=np.uint8).reshape(nb, 16)
+    out[:, 21:29] = np.asarray(qt["levels_lo"], dtype=np.uint8).reshape(nb, 8)
+    out[:, 29] = np.asarray(qt["coeff"], dtype=np.uint8).reshape(-1)
+    return out
+
+
+def planes_from_blocks(blocks, shape):
+    """Inverse of blocks_from_planes: the container's plane dict for a tensor of `shape`."""
+    b = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1, 30)
+    nb = b.shape[0]
+    out_f, in_f = shape
+    return {"shape": (out_f, in_f), "n_blocks": nb, "n_cb": nb // out_f,
+            "dmin": np.ascontiguousarray(b[:, 0:2]).view(np.float16).reshape(-1),
+            "dmax": np.ascontiguousarray(b[:, 2:4]).view(np.float16).reshape(-1),
+            "config": b[:, 4].copy(), "levels_hi": np.ascontiguousarray(b[:, 5:21]).reshape(-1),
+            "levels_lo": np.ascontiguousarray(b[:, 21:29]).reshape(-1), "coeff": b[:, 29].copy()}

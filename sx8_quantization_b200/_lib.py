@@ -31,6 +31,9 @@ SIGNATURES = {
     "sx8_t16_bytes": (_sz, [_l, _i]),
     "sx8_repack_t16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _l, _i, _vp, _vp]),
     "sx8_repack_v44": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _l, _i, _i, _vp, _vp, _vp]),
+    "sx8_repack_t16_blocks": (_i, [_vp, _l, _i, _vp, _vp]),
+    "sx8_blocks_from_planes": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _l, _vp, _vp]),
+    "sx8_planes_from_blocks": (_i, [_vp, _l, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "sx8_device_error_flag": (_i, [ctypes.POINTER(ctypes.c_uint)]),
 }
 

@@ -280,11 +280,40 @@ repack_v44_kernel(const uint16_t* __restrict__ dmin, const uint16_t* __restrict_
 // ------------------------------------------------------------------ repack to T16
 // One thread per (tile, kb, lane): gathers the two sub-blocks it owns from the n-major
 // file planes and writes its three level words; lanes t = 0,1,2 also write H0,H1,H2.
+// Where the repack reads a block from: the container's separate planes, or interleaved
+// 30-byte block_sx8 records {dmin f16, dmax f16, config, qh[16], ql[8], coeff} (the GGUF
+// tensor data, ref scripts/convert_pkl_to_gguf_sx8.py:20-38).
+struct PlaneSrc {
+    const uint16_t *dmin, *dmax;
+    const uint8_t *config, *coeff, *hi, *lo;
+    __device__ __forceinline__ uint32_t hi4(long bid, int t) const { return *reinterpret_cast<const uint32_t*>(hi + bid * 16 + t * 4); }
+    __device__ __forceinline__ uint32_t lo2(long bid, int t) const { return *reinterpret_cast<const uint16_t*>(lo + bid * 8 + t * 2); }
+    __device__ __forceinline__ uint32_t ends(long bid) const { return (uint32_t)dmin[bid] | ((uint32_t)dmax[bid] << 16); }
+    __device__ __forceinline__ uint32_t cc(long bid) const { return (uint32_t)config[bid] | ((uint32_t)coeff[bid] << 8); }
+};
+struct BlockSrc {
+    const uint8_t* blk;   // records are 2-byte aligned (30 is even); qh/ql sit at odd offsets
+    __device__ __forceinline__ uint32_t hi4(long bid, int t) const {
+        const uint8_t* q = blk + bid * SX8_BLOCK_BYTES + 5 + t * 4;
+        return (uint32_t)q[0] | ((uint32_t)q[1] << 8) | ((uint32_t)q[2] << 16) | ((uint32_t)q[3] << 24);
+    }
+    __device__ __forceinline__ uint32_t lo2(long bid, int t) const {
+        const uint8_t* q = blk + bid * SX8_BLOCK_BYTES + 21 + t * 2;
+        return (uint32_t)q[0] | ((uint32_t)q[1] << 8);
+    }
+    __device__ __forceinline__ uint32_t ends(long bid) const {
+        const uint16_t* h = reinterpret_cast<const uint16_t*>(blk + bid * SX8_BLOCK_BYTES);
+        return (uint32_t)h[0] | ((uint32_t)h[1] << 16);
+    }
+    __device__ __forceinline__ uint32_t cc(long bid) const {
+        const uint8_t* q = blk + bid * SX8_BLOCK_BYTES;
+        return (uint32_t)q[4] | ((uint32_t)q[29] << 8);
+    }
+};
+
+template <class SRC>
 __global__ void __launch_bounds__(256)
-repack_t16_kernel(const uint16_t* __restrict__ dmin, const uint16_t* __restrict__ dmax,
-                  const uint8_t* __restrict__ config, const uint8_t* __restrict__ coeff,
-                  const uint8_t* __restrict__ hi, const uint8_t* __restrict__ lo, long N, int n_cb,
-                  uint8_t* __restrict__ blob) {
+repack_t16_kernel(SRC src, long N, int n_cb, uint8_t* __restrict__ blob) {
     long gid = (long)blockIdx.x * 256 + threadIdx.x;
     long n_units = t16_tiles(N) * n_cb;
     long unit = gid >> 5;
@@ -298,21 +327,19 @@ repack_t16_kernel(const uint16_t* __restrict__ dmin, const uint16_t* __restrict_
     for (int i = 0; i < 8; i++) { a[i] = 0; b[i] = 0; }
     if (colA < N) {
         long bid = colA * n_cb + kb;
-        uint32_t hi4 = *reinterpret_cast<const uint32_t*>(hi + bid * 16 + t * 4);
-        uint32_t lo2 = *reinterpret_cast<const uint16_t*>(lo + bid * 8 + t * 2);
+        uint32_t hi4 = src.hi4(bid, t), lo2 = src.lo2(bid, t);
 #pragma unroll
         for (int i = 0; i < 8; i++) a[i] = (uint32_t)level_of(hi4, lo2, i);
-        hA = (uint32_t)dmin[bid] | ((uint32_t)dmax[bid] << 16);
-        ccA = (uint32_t)config[bid] | ((uint32_t)coeff[bid] << 8);
+        hA = src.ends(bid);
+        ccA = src.cc(bid);
     }
     if (colB < N) {
         long bid = colB * n_cb + kb;
-        uint32_t hi4 = *reinterpret_cast<const uint32_t*>(hi + bid * 16 + t * 4);
-        uint32_t lo2 = *reinterpret_cast<const uint16_t*>(lo + bid * 8 + t * 2);
+        uint32_t hi4 = src.hi4(bid, t), lo2 = src.lo2(bid, t);
 #pragma unroll
         for (int i = 0; i < 8; i++) b[i] = (uint32_t)level_of(hi4, lo2, i);
-        hB = (uint32_t)dmin[bid] | ((uint32_t)dmax[bid] << 16);
-        ccB = (uint32_t)config[bid] | ((uint32_t)coeff[bid] << 8);
+        hB = src.ends(bid);
+        ccB = src.cc(bid);
     }
     const int ord[4] = {0, 2, 1, 3};
     uint32_t W0 = 0, W1 = 0, W2 = 0;
@@ -332,6 +359,50 @@ repack_t16_kernel(const uint16_t* __restrict__ dmin, const uint16_t* __restrict_
     if (t == 2) {
         uint32_t cfA = ccA & 0xFF, coA = ccA >> 8, cfB = ccB & 0xFF, coB = ccB >> 8;
         u[112 + g] = (coA & 15) | ((coB & 15) << 4) | (cfA << 8) | ((coA >> 4) << 16) | ((coB >> 4) << 20) | (cfB << 24);
+    }
+}
+
+// planes <-> interleaved 30-byte records, one thread per block (15 two-byte moves)
+template <bool TO_BLOCKS>
+__global__ void __launch_bounds__(256)
+blocks_kernel(uint16_t* dmin, uint16_t* dmax, uint8_t* config, uint8_t* coeff, uint8_t* hi, uint8_t* lo, long n_blk,
+              uint8_t* blk) {
+    long bid = (long)blockIdx.x * 256 + threadIdx.x;
+    if (bid >= n_blk) return;
+    uint8_t* r = blk + bid * SX8_BLOCK_BYTES;
+    uint16_t* r16 = reinterpret_cast<uint16_t*>(r);
+    if (TO_BLOCKS) {
+        uint8_t h[16], l[8];
+        *reinterpret_cast<uint4*>(h) = *reinterpret_cast<const uint4*>(hi + bid * 16);
+        *reinterpret_cast<uint2*>(l) = *reinterpret_cast<const uint2*>(lo + bid * 8);
+        r16[0] = dmin[bid];
+        r16[1] = dmax[bid];
+        r16[2] = (uint16_t)config[bid] | ((uint16_t)h[0] << 8);
+#pragma unroll
+        for (int i = 0; i < 7; i++) r16[3 + i] = (uint16_t)h[2 * i + 1] | ((uint16_t)h[2 * i + 2] << 8);
+        r16[10] = (uint16_t)h[15] | ((uint16_t)l[0] << 8);
+#pragma unroll
+        for (int i = 0; i < 3; i++) r16[11 + i] = (uint16_t)l[2 * i + 1] | ((uint16_t)l[2 * i + 2] << 8);
+        r16[14] = (uint16_t)l[7] | ((uint16_t)coeff[bid] << 8);
+    } else {
+        uint16_t w[15];
+#pragma unroll
+        for (int i = 0; i < 15; i++) w[i] = r16[i];
+        dmin[bid] = w[0];
+        dmax[bid] = w[1];
+        config[bid] = (uint8_t)w[2];
+        uint8_t h[16], l[8];
+        h[0] = (uint8_t)(w[2] >> 8);
+#pragma unroll
+        for (int i = 0; i < 7; i++) { h[2 * i + 1] = (uint8_t)w[3 + i]; h[2 * i + 2] = (uint8_t)(w[3 + i] >> 8); }
+        h[15] = (uint8_t)w[10];
+        l[0] = (uint8_t)(w[10] >> 8);
+#pragma unroll
+        for (int i = 0; i < 3; i++) { l[2 * i + 1] = (uint8_t)w[11 + i]; l[2 * i + 2] = (uint8_t)(w[11 + i] >> 8); }
+        l[7] = (uint8_t)w[14];
+        coeff[bid] = (uint8_t)(w[14] >> 8);
+        *reinterpret_cast<uint4*>(hi + bid * 16) = *reinterpret_cast<const uint4*>(h);
+        *reinterpret_cast<uint2*>(lo + bid * 8) = *reinterpret_cast<const uint2*>(l);
     }
 }
 
@@ -400,9 +471,49 @@ extern "C" int sx8_repack_t16(const void* dmin, const void* dmax, const uint8_t*
                 "sx8_repack_t16: misaligned pointer");
     long threads = t16_tiles(out_f) * n_cb * 32;
     SX8_REQUIRE((threads + 255) / 256 <= 0x7FFFFFFFL, "sx8_repack_t16: tensor too large for one launch");
-    repack_t16_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        (const uint16_t*)dmin, (const uint16_t*)dmax, config, coeff, hi, lo, out_f, n_cb, (uint8_t*)wt16_out);
+    PlaneSrc src{(const uint16_t*)dmin, (const uint16_t*)dmax, config, coeff, hi, lo};
+    repack_t16_kernel<PlaneSrc><<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        src, out_f, n_cb, (uint8_t*)wt16_out);
     SX8_LAUNCH_CHECK("repack_t16_kernel");
+    return SX8_OK;
+}
+
+extern "C" int sx8_repack_t16_blocks(const void* blocks, long out_f, int n_cb, void* wt16_out, void* stream) {
+    SX8_REQUIRE(blocks && wt16_out, "sx8_repack_t16_blocks: null pointer");
+    SX8_REQUIRE(out_f > 0 && n_cb > 0, "sx8_repack_t16_blocks: need out_f>0, n_cb>0");
+    SX8_REQUIRE(aligned(blocks, 2) && aligned(wt16_out, 16), "sx8_repack_t16_blocks: misaligned pointer");
+    long threads = t16_tiles(out_f) * n_cb * 32;
+    SX8_REQUIRE((threads + 255) / 256 <= 0x7FFFFFFFL, "sx8_repack_t16_blocks: tensor too large for one launch");
+    BlockSrc src{(const uint8_t*)blocks};
+    repack_t16_kernel<BlockSrc><<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        src, out_f, n_cb, (uint8_t*)wt16_out);
+    SX8_LAUNCH_CHECK("repack_t16_kernel<blocks>");
+    return SX8_OK;
+}
+
+extern "C" int sx8_blocks_from_planes(const void* dmin, const void* dmax, const uint8_t* config, const uint8_t* coeff,
+                                      const uint8_t* hi, const uint8_t* lo, long n_blk, void* blocks_out,
+                                      void* stream) {
+    SX8_REQUIRE(dmin && dmax && config && coeff && hi && lo && blocks_out, "sx8_blocks_from_planes: null pointer");
+    SX8_REQUIRE(n_blk > 0 && (n_blk + 255) / 256 <= 0x7FFFFFFFL, "sx8_blocks_from_planes: bad block count %ld", n_blk);
+    SX8_REQUIRE(aligned(dmin, 2) && aligned(dmax, 2) && aligned(hi, 16) && aligned(lo, 8) && aligned(blocks_out, 2),
+                "sx8_blocks_from_planes: misaligned pointer");
+    blocks_kernel<true><<<(unsigned)((n_blk + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        (uint16_t*)dmin, (uint16_t*)dmax, (uint8_t*)config, (uint8_t*)coeff, (uint8_t*)hi, (uint8_t*)lo, n_blk,
+        (uint8_t*)blocks_out);
+    SX8_LAUNCH_CHECK("blocks_kernel<to>");
+    return SX8_OK;
+}
+
+extern "C" int sx8_planes_from_blocks(const void* blocks, long n_blk, void* dmin, void* dmax, uint8_t* config,
+                                      uint8_t* coeff, uint8_t* hi, uint8_t* lo, void* stream) {
+    SX8_REQUIRE(dmin && dmax && config && coeff && hi && lo && blocks, "sx8_planes_from_blocks: null pointer");
+    SX8_REQUIRE(n_blk > 0 && (n_blk + 255) / 256 <= 0x7FFFFFFFL, "sx8_planes_from_blocks: bad block count %ld", n_blk);
+    SX8_REQUIRE(aligned(dmin, 2) && aligned(dmax, 2) && aligned(hi, 16) && aligned(lo, 8) && aligned(blocks, 2),
+                "sx8_planes_from_blocks: misaligned pointer");
+    blocks_kernel<false><<<(unsigned)((n_blk + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        (uint16_t*)dmin, (uint16_t*)dmax, config, coeff, hi, lo, n_blk, (uint8_t*)blocks);
+    SX8_LAUNCH_CHECK("blocks_kernel<from>");
     return SX8_OK;
 }
 

@@ -23,6 +23,7 @@
 namespace sx8 {
 
 constexpr int T16_UNIT = 480;
+constexpr int SX8_BLOCK_BYTES = 30;   // one interleaved block_sx8 record
 constexpr int T16_LEV = 384;
 
 __host__ __device__ inline long t16_tiles(long N) { return (N + 15) / 16; }

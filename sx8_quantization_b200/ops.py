@@ -250,3 +250,49 @@ def repack_v44(dmin, dmax, config, coeff, hi, lo, out_f, n_cb, hdr_bytes=6):
                                        lev.data_ptr(), _stream(hi))
     _lib.check(rc, "sx8_repack_v44")
     return hdr, lev
+
+
+def repack_t16_blocks(blocks, out_f, n_cb):
+    """Interleaved 30-byte block_sx8 records (out_f*n_cb, 30) u8, n-major -- a GGUF tensor's
+    data -- -> T16 device blob."""
+    blocks = _need(blocks, torch.uint8, "blocks")
+    if blocks.numel() != out_f * n_cb * 30:
+        raise SX8Error("blocks has %d bytes, need %d" % (blocks.numel(), out_f * n_cb * 30))
+    nbytes = _lib.lib().sx8_t16_bytes(out_f, n_cb)
+    blob = torch.empty((nbytes // 480, 480), dtype=torch.uint8, device=blocks.device)
+    with torch.cuda.device(blocks.device):
+        rc = _lib.lib().sx8_repack_t16_blocks(blocks.data_ptr(), out_f, n_cb, blob.data_ptr(), _stream(blocks))
+    _lib.check(rc, "sx8_repack_t16_blocks")
+    return blob
+
+
+def blocks_from_planes(dmin, dmax, config, coeff, hi, lo):
+    """n-major planes -> (n_blk, 30) u8 interleaved records, byte-identical to the reference's
+    blockify_vec (ref scripts/convert_pkl_to_gguf_sx8.py:20-38)."""
+    n_blk = config.numel()
+    out = torch.empty((n_blk, 30), dtype=torch.uint8, device=config.device)
+    with torch.cuda.device(config.device):
+        rc = _lib.lib().sx8_blocks_from_planes(dmin.data_ptr(), dmax.data_ptr(), config.data_ptr(), coeff.data_ptr(),
+                                               hi.data_ptr(), lo.data_ptr(), n_blk, out.data_ptr(), _stream(config))
+    _lib.check(rc, "sx8_blocks_from_planes")
+    return out
+
+
+def planes_from_blocks(blocks):
+    """(n_blk, 30) u8 records -> dict of n-major planes (dmin, dmax f16; config, coeff, levels_hi,
+    levels_lo u8)."""
+    blocks = _need(blocks, torch.uint8, "blocks")
+    n_blk = blocks.numel() // 30
+    if n_blk * 30 != blocks.numel():
+        raise SX8Error("blocks is not a whole number of 30-byte records")
+    dev = blocks.device
+    q = {"dmin": torch.empty(n_blk, dtype=torch.float16, device=dev), "dmax": torch.empty(n_blk, dtype=torch.float16, device=dev),
+         "config": torch.empty(n_blk, dtype=torch.uint8, device=dev), "coeff": torch.empty(n_blk, dtype=torch.uint8, device=dev),
+         "levels_hi": torch.empty(n_blk * 16, dtype=torch.uint8, device=dev),
+         "levels_lo": torch.empty(n_blk * 8, dtype=torch.uint8, device=dev)}
+    with torch.cuda.device(dev):
+        rc = _lib.lib().sx8_planes_from_blocks(blocks.data_ptr(), n_blk, q["dmin"].data_ptr(), q["dmax"].data_ptr(),
+                                               q["config"].data_ptr(), q["coeff"].data_ptr(), q["levels_hi"].data_ptr(),
+                                               q["levels_lo"].data_ptr(), _stream(blocks))
+    _lib.check(rc, "sx8_planes_from_blocks")
+    return q
