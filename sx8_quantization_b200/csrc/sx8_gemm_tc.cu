@@ -2,18 +2,26 @@
 //
 //   Y (M, N) = X (M, K) * W^T,  W decoded on the fly from the T16 blob, fp32 accumulate.
 //
-// CTA tile: 128*MT rows x 256 columns (MT = 1 or 2), K step 64 (two block rows).  Warp roles:
+// Tiles.  M > 256: a cluster of two CTAs computes 512 rows x 256 columns with two-CTA MMAs
+// (tcgen05.mma.cta_group::2, M=256, N=256, K=16, two accumulators): each CTA loads its own
+// 256 rows of X and decodes 128 of the 256 columns.  M <= 256: one CTA computes 128*MT rows x
+// BN columns (cta_group::1).  K step 64 (two block rows).  Warp roles:
 //   warp 0      producer : X tiles by 2-D TMA (128-byte swizzle)
-//   warp 18     producer : packed 16-column slabs of the blob and the fp16 PCA table by TMA
-//                          bulk copies, running up to 8 stages ahead
-//   warp 1      issuer   : one thread issues tcgen05.mma (M=128, N=256, K=16, kind::f16) on
-//                          shared-memory descriptors; accumulators live in TMEM (256 columns
-//                          per 128-row tile); tcgen05.commit releases the stages
+//   warp 18     producer : packed slabs of the blob (one 2-D tensor copy per stage) and the
+//                          fp16 PCA table, running up to 8 stages ahead
+//   warp 1      issuer   : in the leader CTA one thread issues the MMAs on shared-memory
+//                          descriptors; accumulators live in TMEM (all 512 columns);
+//                          tcgen05.commit releases the stages (in both CTAs of a pair).  In the
+//                          peer CTA this warp tells the leader when the peer's X tiles landed.
 //   warps 2..17 decoders : bit-extract 6-bit levels from the packed slab, form fp16 weights
 //                          w = dmin + base*(mult*level + 63*off) + c0*s0*b0[t] + c1*s1*b1[t]
 //                          (the arithmetic of ref cuda/sx8_fused_wmma.cu:83-96, in fp16 pairs)
 //                          and store them as the K-major, 128-byte-swizzled B operand tile;
-//                          afterwards the same warps read TMEM back (tcgen05.ld) and write Y.
+//                          afterwards the same warps read TMEM back (tcgen05.ld) and write Y
+//                          through swizzled staging and TMA stores.
+// Every role probes the barriers of its next stage early (mbarrier.test_wait) and reads the
+// answer one iteration later: a blocking wait costs a shared-memory round trip even when the
+// phase completed long ago.
 // Every wait on an mbarrier is bounded; a wait that runs out sets the device error word and
 // the kernel drains and frees its TMEM.
 #include <cuda.h>
@@ -27,7 +35,6 @@ namespace tc {
 
 constexpr int BK = 64, KB_STAGE = 2;
 constexpr int kDecodeWarps = 16, kWarps = kDecodeWarps + 3, kThreads = kWarps * 32;
-constexpr int kGroupWarps = kDecodeWarps / 2;      // decode warps working on one stage
 constexpr int kSmemMax = 232448;                 // opt-in shared memory per CTA on sm_100
 constexpr int A_TILE = 128 * 128;                 // 128 rows x 64 fp16, bytes
 constexpr int P_TAB = KB_STAGE * 128;             // PCA table: per kb 2 x 32 fp16
@@ -252,11 +259,13 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
 }
 
 
-template <int MT, int BN, int PAIR>
+// G = decode groups: the 16 decode warps form G groups of 16/G warps that take every G-th stage.
+template <int MT, int BN, int PAIR, int G>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap,
                const __grid_constant__ CUtensorMap wmap, Params p) {
     using C = Cfg<MT, BN, PAIR>;
+    constexpr int kGroupWarps = kDecodeWarps / G;
     constexpr int B_TILE = C::B_TILE, P_SLAB = C::P_SLAB, P_STAGE = C::P_STAGE, TILES = C::TILES, BNU = C::BNU;
     static_assert(MT * BNU <= 512, "accumulators exceed tensor memory");
     extern __shared__ uint8_t smem_raw[];
@@ -421,21 +430,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         const float kBase = 0.25f * 0.015873f * 512.0f;   // levels are formed scaled by 2^-9
         bool ok = true;
         const uint32_t b_full_leader = (PAIR == 2) ? mapa_u32(b_full, 0u) : b_full;
-        // The warps form two groups that take alternate stages: the fixed cost a warp pays per
-        // stage (barrier round trips, the proxy fence) is then spread over twice the items, and
-        // one group's waits overlap the other group's arithmetic.
+        // The warps form G groups that take every G-th stage: the fixed cost a warp pays per
+        // stage (barrier round trips, the proxy fence -- the largest stall of this kernel) is
+        // spread over G times the items, and one group's waits overlap the others' arithmetic.
         const int grp = dw / kGroupWarps, gw = dw % kGroupWarps;
         Ring rp(SP), rb(SB);
-        if (grp == 1) { rp = rp.next(); rb = rb.next(); }
+        for (int i = 0; i < grp; i++) { rp = rp.next(); rb = rb.next(); }
         uint32_t pre_p = 0, pre_b = (rb.r == 0) ? 1u : 0u;   // answers of the early probes
-        for (int ks = grp; ks < n_ks; ks += 2) {
+        for (int ks = grp; ks < n_ks; ks += G) {
             const int sp = rp.s, sb = rb.s;
             const int rows = min(KB_STAGE, p.n_cb - ks * KB_STAGE);
             if (!pre_p && ok) ok = mbar_wait(p_full + 8 * sp, rp.r & 1, 0x100u);
             if (!pre_b && ok) ok = mbar_wait_t<PAIR == 2>(b_empty + 8 * sb, (rb.r - 1) & 1, 0x200u);
-            rp = rp.next().next();
-            rb = rb.next().next();
-            if (ks + 2 < n_ks) {   // probe this group's next stage now, read the answers next iteration
+#pragma unroll
+            for (int i = 0; i < G; i++) { rp = rp.next(); rb = rb.next(); }
+            if (ks + G < n_ks) {   // probe this group's next stage now, read the answers next iteration
                 pre_p = mbar_probe<false>(p_full + 8 * rp.s, rp.r & 1);
                 pre_b = (rb.r == 0) ? 1u : mbar_probe<PAIR == 2>(b_empty + 8 * rb.s, (rb.r - 1) & 1);
             }
@@ -661,7 +670,7 @@ bool make_ymap(CUtensorMap* map, void* y, int M, int N, int out_f16) {
     return r == CUDA_SUCCESS;
 }
 
-template <int MT, int BN, int PAIR>
+template <int MT, int BN, int PAIR, int G = 2>
 int launch_tc_bn(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
     CUtensorMap ymap;
     memset(&ymap, 0, sizeof(ymap));
@@ -693,7 +702,7 @@ int launch_tc_bn(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        e = cudaFuncSetAttribute(tc::gemm_tc_kernel<MT, BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(tc::gemm_tc_kernel<MT, BN, PAIR, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  tc::kSmemMax);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemm_tc smem)");
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
@@ -726,7 +735,7 @@ int launch_tc_bn(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (PAIR == 2) ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, tc::gemm_tc_kernel<MT, BN, PAIR>, map, ymap, wmap, p);
+    e = cudaLaunchKernelEx(&cfg, tc::gemm_tc_kernel<MT, BN, PAIR, G>, map, ymap, wmap, p);
     if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(gemm_tc_kernel)");
     return SX8_OK;
 }
@@ -754,7 +763,11 @@ int launch_auto(const CUtensorMap& map, const tc::Params& p, cudaStream_t stream
     static const int pair_mode = getenv("SX8_GEMM_PAIR") ? atoi(getenv("SX8_GEMM_PAIR")) : 1;
     static const int force_mt = getenv("SX8_GEMM_MT") ? atoi(getenv("SX8_GEMM_MT")) : 0;
     if (pair_mode == 3) return launch_tc_bn<1, 128, 2>(map, p, stream);
-    if (pair_mode == 2 || (pair_mode == 1 && p.M > 256)) return launch_tc_bn<2, 128, 2>(map, p, stream);
+    static const int groups = getenv("SX8_GEMM_GROUPS") ? atoi(getenv("SX8_GEMM_GROUPS")) : 4;
+    if (pair_mode == 2 || (pair_mode == 1 && p.M > 256)) {
+        if (groups == 2) return launch_tc_bn<2, 128, 2, 2>(map, p, stream);
+        return launch_tc_bn<2, 128, 2, 4>(map, p, stream);
+    }
     if (force_mt == 1) return launch_tc<1>(map, p, stream);
     if (p.M > 128) return launch_tc<2>(map, p, stream);
     return launch_tc<1>(map, p, stream);
