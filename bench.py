@@ -30,6 +30,8 @@ sys.path.insert(0, ROOT)
 
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only without MEASURED_PEAKS.json
 BATCHES = (1, 2, 4, 8)
+# dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes for one gemv launch (ncu, lm_head)
+NCU_TRAFFIC_RATIO = 1.012
 
 
 def peaks():
@@ -326,9 +328,13 @@ def run_single(args):
         "gpu_launches": n_gemv * args.steps,
         "device_error_flag": flag,
         "roofline": {"bound": "hbm", "achieved": round(value, 1), "peak": peak, "unit": "GB/s",
-                     "frac": round(value / peak, 4), "traffic": None,
+                     "frac": round(value / peak, 4),
+                     "traffic": int(NCU_TRAFFIC_RATIO * bytes_pass / len(mats)),
                      "note": "achieved = packed weight bytes / wall time of the whole graph-replayed step "
-                             "(every gemv kernel and the launch gaps between them included), of %s peak" % peak_kind},
+                             "(every gemv kernel and the launch gaps between them included), of %s peak; traffic = "
+                             "DRAM bytes per average launch: the ncu capture of the lm_head launch read+wrote "
+                             "%.3f x its algorithmic bytes, scaled by bytes to the average launch of the step"
+                             % (peak_kind, NCU_TRAFFIC_RATIO)},
         "e2e": {"value": round(e2e_val, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps,
                 "api": "sx8_decode1_v3.decode1_v44 with pinned host x and y"},

@@ -12,7 +12,8 @@ import importlib
 import runpy
 import sys
 
-DROP_IN = ("sx8_decode1_v3", "sx8_gemm_compact", "sx8_fused_wmma", "sx8_embed_v44", "kernel_sx8_v43")
+DROP_IN = ("sx8_decode1_v3", "sx8_gemm_compact", "sx8_fused_wmma", "sx8_embed_v44", "kernel_sx8_v43",
+           "sx8_container_v43")
 
 
 def register():
