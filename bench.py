@@ -341,6 +341,7 @@ def run_single(args):
         "clocks": clocks,
         "fused_projections_batch1": fused,
         "other_kernels": extras,
+        "e2e_decoder_qwen3_4b": None if (args.no_extras or args.no_decoder) else decoder_e2e(dev),
     }
     if not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(budget_s=args.cpu_seconds)
@@ -358,6 +359,30 @@ def _time_us(fn, iters=10, warm=3):
         fn()
     b.record(); torch.cuda.synchronize()
     return a.elapsed_time(b) * 1e3 / iters
+
+
+def decoder_e2e(dev, prompt=512, new=256):
+    """BASELINE config 3: random-init Qwen3-4B-shaped decoder, every linear and the embedding
+    in S-X8; a prompt of uniform random ids, then greedy decode with the step in one CUDA
+    graph, at batch 1 (GEMV path) and batch 32 (tensor-core GEMM path)."""
+    import torch
+    from sx8_quantization_b200.decoder import SX8Decoder, QWEN3_4B_DECODER
+    out = {"prompt_tokens": prompt, "new_tokens": new, "glue": "RMSNorm/RoPE/attention/SwiGLU in PyTorch"}
+    for batch in (1, 32):
+        dec = SX8Decoder(QWEN3_4B_DECODER, device=dev, seed=9, max_seq=prompt + new, batch=batch)
+        g = torch.Generator(device=dev).manual_seed(1234)
+        ids = torch.randint(0, QWEN3_4B_DECODER["vocab"], (batch, prompt), generator=g, device=dev)
+        dec.generate(ids, 8)                       # warm-up: allocations, graph capture
+        toks, t = dec.generate(ids, new)
+        out["batch%d" % batch] = {
+            "prefill_ms": round(t["prefill_ms"], 2), "prefill_tok_per_s": round(batch * prompt / t["prefill_ms"] * 1e3, 1),
+            "decode_ms_per_step": round(t["decode_ms_per_token"], 4),
+            "decode_tok_per_s": round(batch / t["decode_ms_per_token"] * 1e3, 1),
+            "weight_GBps_decode": round(dec.packed_bytes / (t["decode_ms_per_token"] * 1e-3) / 1e9, 1),
+            "distinct_tokens": int(toks.unique().numel())}
+        del dec
+        torch.cuda.empty_cache()
+    return out
 
 
 def other_kernels(dev, layer0, head, fam):
@@ -673,6 +698,7 @@ def main():
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMM / quantizer / embed / dequant extras")
+    ap.add_argument("--no-decoder", action="store_true", help="skip the end-to-end decoder leg")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--emulate-world", type=int, default=0,

@@ -322,6 +322,22 @@ __global__ void __launch_bounds__(kThreads, MINB) gemv_kernel(GemvParams p) {
         const int ti = warp % NT, kpart = warp / NT;
         const int g = lane >> 2, t = lane & 3;
         const bool row_ok = g < p.M;
+        // PCA bases and scales are weights: the first pair of block rows is fetched before
+        // waiting for the preceding kernel, like the producer's weight copies.
+        float4 bq[2][4];
+        float sc[2][2];
+        auto load_bases = [&](int kb0) {
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                int kb = min(kb0 + u, kb_end - 1);
+                const float4* b0p = reinterpret_cast<const float4*>(sg.bases + (long)kb * 64 + t * 8);
+                const float4* b1p = reinterpret_cast<const float4*>(sg.bases + (long)kb * 64 + 32 + t * 8);
+                bq[u][0] = b0p[0]; bq[u][1] = b0p[1]; bq[u][2] = b1p[0]; bq[u][3] = b1p[1];
+                sc[u][0] = sg.scales[kb * 2 + 0];
+                sc[u][1] = sg.scales[kb * 2 + 1];
+            }
+        };
+        if (kb_begin + 2 * warp < kb_end) load_bases(kb_begin + 2 * warp);
         asm volatile("griddepcontrol.wait;" ::: "memory");
 
         // ---- activation-side table for kb_begin..kb_end: one warp per kb, lane = (m = g, t).
@@ -332,18 +348,12 @@ __global__ void __launch_bounds__(kThreads, MINB) gemv_kernel(GemvParams p) {
         // is pre-multiplied by 1024.  Loads of two kb are issued together to hide their latency.
         for (int kb0 = kb_begin + 2 * warp; kb0 < kb_end; kb0 += 2 * kConsumerWarps) {
             uint4 raw[2];
-            float4 bq[2][4];
-            float sc[2][2];
+            if (kb0 != kb_begin + 2 * warp) load_bases(kb0);
 #pragma unroll
             for (int u = 0; u < 2; u++) {
                 int kb = min(kb0 + u, kb_end - 1);
                 raw[u] = make_uint4(0u, 0u, 0u, 0u);
                 if (row_ok) raw[u] = *reinterpret_cast<const uint4*>(p.x + (long)g * p.ldx + (long)kb * 32 + t * 8);
-                const float4* b0p = reinterpret_cast<const float4*>(sg.bases + (long)kb * 64 + t * 8);
-                const float4* b1p = reinterpret_cast<const float4*>(sg.bases + (long)kb * 64 + 32 + t * 8);
-                bq[u][0] = b0p[0]; bq[u][1] = b0p[1]; bq[u][2] = b1p[0]; bq[u][3] = b1p[1];
-                sc[u][0] = sg.scales[kb * 2 + 0];
-                sc[u][1] = sg.scales[kb * 2 + 1];
             }
 #pragma unroll
             for (int u = 0; u < 2; u++) {
