@@ -198,6 +198,29 @@ int sx8_planes_from_blocks(const void* blocks, long n_blk, void* dmin_f16, void*
                            uint8_t* config, uint8_t* coeff, uint8_t* levels_hi, uint8_t* levels_lo,
                            void* stream);
 
+/* ---- decoder glue -----------------------------------------------------------------------
+ * The small kernels between the S-X8 linears of one decode step, so that a captured step is
+ * nine launches per layer.  No counterpart among the reference's kernels: the reference
+ * leaves this work to the host framework's model code (it swaps only the Linear / Embedding
+ * modules, ref: scripts/integrate_fused_v44.py:85-116).  f32 residual stream and GEMV
+ * outputs, f16 activations and KV cache (B, hkv, S, D); `pos` points to one int64 in device
+ * memory (the position being written), so a captured graph serves every step.
+ *   add_rmsnorm : h += y (y may be NULL); x_out = f16(rmsnorm(h) * gamma)
+ *   rope_cache  : rotary embedding (half-split) of q, k at *pos; q_out f16 (B, hq, D); k, v
+ *                 written to the caches at *pos; cos_t / sin_t are (S, D/2) f32 tables
+ *   attn_decode : softmax(q K^T * scale) V over cache positions 0..*pos; out f16 (B, hq*D);
+ *                 D in {64, 128}, hq/hkv in {1, 2, 4, 8}
+ *   silu_mul    : act_out = f16(silu(g) * u), n elements                                   */
+int sx8_glue_add_rmsnorm(void* h_f32, const void* y_f32, const void* gamma_f32, int B, int H, float eps,
+                         void* x_out_f16, void* stream);
+int sx8_glue_rope_cache(const void* q_f32, const void* k_f32, const void* v_f32, const void* pos,
+                        const void* cos_t, const void* sin_t, int B, int hq, int hkv, int D, int S,
+                        void* q_out_f16, void* k_cache_f16, void* v_cache_f16, void* stream);
+int sx8_glue_attn_decode(const void* q_f16, const void* k_cache_f16, const void* v_cache_f16,
+                         const void* pos, int B, int hq, int hkv, int D, int S, float scale,
+                         void* out_f16, void* stream);
+int sx8_glue_silu_mul(const void* g_f32, const void* u_f32, long n, void* act_out_f16, void* stream);
+
 /* Device-side error word of the bounded waits inside the pipelined kernels: 0 when no
  * wait ever ran out.  Reads back synchronously (cudaMemcpy) -- for tests and health
  * checks, not for the hot path.                                                      */

@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libsx8b200.so")
-SOURCES = ["sx8_api.cu", "sx8_codec.cu", "sx8_gemv.cu", "sx8_gemm.cu", "sx8_gemm_tc.cu"]
+SOURCES = ["sx8_api.cu", "sx8_codec.cu", "sx8_gemv.cu", "sx8_gemm.cu", "sx8_gemm_tc.cu", "sx8_glue.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-rdc=true"]
 

@@ -6,9 +6,10 @@ Every linear (q, k, v, o, gate, up, down, lm_head) and the embedding table are S
 tensors in the T16 device layout, quantised on the device from seeded random weights
 (N(0, 0.02) + 0.1 % outliers); projections that share their input run as one multi-matrix
 GEMV launch (q|k|v, gate|up).  The glue between the linears -- RMSNorm, RoPE, attention
-over the cache, SwiGLU, argmax -- is plain PyTorch: it is not part of the S-X8 path, and the
-reference takes it from the host framework as well (ref scripts/integrate_fused_v44.py:
-85-116 swaps only the nn.Linear / nn.Embedding modules of a transformers model).
+over the cache, SwiGLU -- is not part of the S-X8 path (the reference takes it from the host
+framework, ref scripts/integrate_fused_v44.py:85-116 swaps only the nn.Linear / nn.Embedding
+modules of a transformers model).  Prefill uses PyTorch for it; a decode step uses the four
+sx8_glue_* kernels (nine launches per layer) or, with fused_glue=False, plain PyTorch.
 
 Default shapes follow Qwen3-4B (36 layers, hidden 2560, 32 query / 8 key-value heads of
 128, SwiGLU 9728, vocabulary 151936); the per-head q/k norms of that family are left out."""
@@ -32,7 +33,7 @@ def _rope(x, cos, sin):
 
 
 class SX8Decoder:
-    def __init__(self, cfg=None, device="cuda:0", seed=0, max_seq=768, batch=1, with_pca=True):
+    def __init__(self, cfg=None, device="cuda:0", seed=0, max_seq=768, batch=1, with_pca=True, fused_glue=True):
         self.cfg = dict(QWEN3_4B_DECODER if cfg is None else cfg)
         c = self.cfg
         self.dev = torch.device(device)
@@ -72,6 +73,15 @@ class SX8Decoder:
             self.multi = [(ops.MultiGemv([L["q"], L["k"], L["v"]], self.B, self.dev),
                            ops.MultiGemv([L["gate"], L["up"]], self.B, self.dev)) for L in self.layers]
         self.graph = None
+        self.fused_glue = bool(fused_glue)
+        f16, f32 = dict(dtype=torch.float16, device=self.dev), dict(dtype=torch.float32, device=self.dev)
+        B = self.B
+        self.buf = {"h": torch.empty(B, H, **f32), "x": torch.empty(B, H, **f16), "q16": torch.empty(B, self.nq, **f16),
+                    "a": torch.empty(B, self.nq, **f16), "act": torch.empty(B, c["ffn"], **f16),
+                    "o": torch.empty(B, H, **f32), "d": torch.empty(B, H, **f32),
+                    "q": torch.empty(B, self.nq, **f32), "k": torch.empty(B, self.nkv, **f32),
+                    "v": torch.empty(B, self.nkv, **f32), "g": torch.empty(B, c["ffn"], **f32),
+                    "u": torch.empty(B, c["ffn"], **f32), "logits": torch.empty(B, c["vocab"], **f32)}
         self.packed_bytes = sum(t["wt16"].numel() for L in self.layers for t in L.values()) + self.lm_head["wt16"].numel()
 
     # ------------------------------------------------------------------ pieces
@@ -124,8 +134,44 @@ class SX8Decoder:
         return logits
 
     # ------------------------------------------------------------------ one decode step
+    def _lin_into(self, x, t, out):
+        """x (B, K) f16 -> out (B, N) f32, preallocated."""
+        if x.shape[0] <= 8:
+            return ops.gemv(x, t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"], out=out, flags=SX8_F_PDL)
+        return ops.gemm(x, t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"], out_dtype=torch.float32, out=out)
+
+    def _step_fused(self):
+        """One decode step with the sx8_glue_* kernels between the linears."""
+        c, b = self.cfg, self.buf
+        D, hq, hkv = c["head_dim"], c["n_q"], c["n_kv"]
+        b["h"].copy_(self._embed(self.tok))
+        y = None
+        for l, L in enumerate(self.layers):
+            ops.glue_add_rmsnorm(b["h"], y, self.gamma, c["eps"], b["x"])
+            if self.multi is not None:
+                q, k, v = self.multi[l][0](b["x"], flags=SX8_F_PDL)
+            else:
+                q, k, v = (self._lin_into(b["x"], L[n], b[n]) for n in ("q", "k", "v"))
+            ops.glue_rope_cache(q, k, v, self.pos, self.cos, self.sin, hq, hkv, D, b["q16"], self.k_cache[l], self.v_cache[l])
+            ops.glue_attn_decode(b["q16"], self.k_cache[l], self.v_cache[l], self.pos, hq, hkv, D, self.scale, b["a"])
+            self._lin_into(b["a"], L["o"], b["o"])
+            ops.glue_add_rmsnorm(b["h"], b["o"], self.gamma, c["eps"], b["x"])
+            if self.multi is not None:
+                g, u = self.multi[l][1](b["x"], flags=SX8_F_PDL)
+            else:
+                g, u = self._lin_into(b["x"], L["gate"], b["g"]), self._lin_into(b["x"], L["up"], b["u"])
+            ops.glue_silu_mul(g, u, b["act"])
+            y = self._lin_into(b["act"], L["down"], b["d"])
+        ops.glue_add_rmsnorm(b["h"], y, self.gamma, c["eps"], b["x"])
+        logits = self._lin_into(b["x"], self.lm_head, b["logits"])
+        self.tok.copy_(logits.argmax(-1))
+        self.pos.add_(1)
+        return logits
+
     def _step(self):
         """Consumes self.tok at position self.pos; writes the next token and advances."""
+        if self.fused_glue:
+            return self._step_fused()
         c = self.cfg
         B, D, hq, hkv = self.B, c["head_dim"], c["n_q"], c["n_kv"]
         grp = hq // hkv

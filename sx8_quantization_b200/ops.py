@@ -296,3 +296,41 @@ def planes_from_blocks(blocks):
                                                q["levels_lo"].data_ptr(), _stream(blocks))
     _lib.check(rc, "sx8_planes_from_blocks")
     return q
+
+
+# ---- decoder glue (sx8_glue_*): thin wrappers, all tensors preallocated by the caller
+def glue_add_rmsnorm(h, y, gamma, eps, x_out):
+    """h (B,H) f32 += y (or None); x_out (B,H) f16 = rmsnorm(h) * gamma."""
+    B, H = h.shape
+    with torch.cuda.device(h.device):
+        rc = _lib.lib().sx8_glue_add_rmsnorm(h.data_ptr(), 0 if y is None else y.data_ptr(), gamma.data_ptr(), B, H,
+                                             float(eps), x_out.data_ptr(), _stream(h))
+    _lib.check(rc, "sx8_glue_add_rmsnorm")
+    return x_out
+
+
+def glue_rope_cache(q, k, v, pos, cos_t, sin_t, hq, hkv, D, q_out, k_cache, v_cache):
+    """q (B,hq*D), k, v (B,hkv*D) f32; caches (B,hkv,S,D) f16 written at position pos[0]."""
+    B, S = q.shape[0], k_cache.shape[2]
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().sx8_glue_rope_cache(q.data_ptr(), k.data_ptr(), v.data_ptr(), pos.data_ptr(), cos_t.data_ptr(),
+                                            sin_t.data_ptr(), B, hq, hkv, D, S, q_out.data_ptr(), k_cache.data_ptr(),
+                                            v_cache.data_ptr(), _stream(q))
+    _lib.check(rc, "sx8_glue_rope_cache")
+    return q_out
+
+
+def glue_attn_decode(q16, k_cache, v_cache, pos, hq, hkv, D, scale, out):
+    B, S = q16.shape[0], k_cache.shape[2]
+    with torch.cuda.device(q16.device):
+        rc = _lib.lib().sx8_glue_attn_decode(q16.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), pos.data_ptr(), B, hq,
+                                             hkv, D, S, float(scale), out.data_ptr(), _stream(q16))
+    _lib.check(rc, "sx8_glue_attn_decode")
+    return out
+
+
+def glue_silu_mul(g, u, act_out):
+    with torch.cuda.device(g.device):
+        rc = _lib.lib().sx8_glue_silu_mul(g.data_ptr(), u.data_ptr(), g.numel(), act_out.data_ptr(), _stream(g))
+    _lib.check(rc, "sx8_glue_silu_mul")
+    return act_out

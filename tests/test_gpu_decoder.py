@@ -75,3 +75,71 @@ def test_batch_above_eight_uses_the_gemm_path():
     assert (got - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
     toks, _ = dec.generate(ids, 4, use_graph=True)
     assert toks.shape == (12, 4)
+
+
+@pytest.mark.parametrize("batch", [1, 3, 12])
+def test_fused_glue_step_matches_pytorch_glue(batch):
+    import torch
+    from sx8_quantization_b200.decoder import SX8Decoder
+    dec = SX8Decoder(SMALL, seed=6, max_seq=40, batch=batch)
+    g = torch.Generator(device="cuda").manual_seed(8)
+    ids = torch.randint(0, SMALL["vocab"], (batch, 20), generator=g, device="cuda")
+    outs = {}
+    for fused in (False, True):
+        dec.fused_glue = fused
+        dec.prefill(ids)
+        logits = [dec._step().clone() for _ in range(3)]
+        outs[fused] = torch.stack(logits)
+    ref, got = outs[False], outs[True]
+    assert torch.isfinite(got).all()
+    assert (got - ref).abs().max().item() <= 1e-2 * ref.abs().max().item()
+
+
+def test_glue_kernels_against_pytorch():
+    import torch
+    import torch.nn.functional as F
+    from sx8_quantization_b200 import ops
+    from sx8_quantization_b200.decoder import _rope
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(9)
+    B, H, hq, hkv, D, S = 3, 320, 8, 2, 128, 96
+    h = torch.randn(B, H, generator=g, device=dev)
+    y = torch.randn(B, H, generator=g, device=dev)
+    gamma = torch.rand(H, generator=g, device=dev) + 0.5
+    x = torch.empty(B, H, dtype=torch.float16, device=dev)
+    h2 = h.clone()
+    ops.glue_add_rmsnorm(h2, y, gamma, 1e-6, x)
+    assert torch.allclose(h2, h + y)
+    want = F.rms_norm(h + y, (H,), gamma, 1e-6)
+    assert (x.float() - want).abs().max().item() <= 2e-3 * want.abs().max().item()
+    # rope + cache + attention at position 37
+    pos = torch.tensor([37], device=dev)
+    q = torch.randn(B, hq * D, generator=g, device=dev)
+    k = torch.randn(B, hkv * D, generator=g, device=dev)
+    v = torch.randn(B, hkv * D, generator=g, device=dev)
+    kc = torch.randn(B, hkv, S, D, generator=g, device=dev).half()
+    vc = torch.randn(B, hkv, S, D, generator=g, device=dev).half()
+    inv = 1.0 / (1.0e4 ** (torch.arange(0, D, 2, device=dev, dtype=torch.float32) / D))
+    ang = torch.arange(S, device=dev, dtype=torch.float32)[:, None] * inv[None, :]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    q16 = torch.empty(B, hq * D, dtype=torch.float16, device=dev)
+    ops.glue_rope_cache(q, k, v, pos, cos, sin, hq, hkv, D, q16, kc, vc)
+    qr = _rope(q.view(B, hq, D), cos[37][None, None], sin[37][None, None]).half()
+    kr = _rope(k.view(B, hkv, D), cos[37][None, None], sin[37][None, None]).half()
+    kc_ref[:, :, 37] = kr
+    vc_ref[:, :, 37] = v.view(B, hkv, D).half()
+    assert torch.equal(kc, kc_ref) and torch.equal(vc, vc_ref)
+    assert (q16.view(B, hq, D).float() - qr.float()).abs().max().item() <= 2e-3
+    out = torch.empty(B, hq * D, dtype=torch.float16, device=dev)
+    scale = D ** -0.5
+    ops.glue_attn_decode(q16, kc, vc, pos, hq, hkv, D, scale, out)
+    grp = hq // hkv
+    s = torch.matmul(q16.view(B, hkv, grp, D).float(), kc[:, :, :38].float().transpose(-1, -2)) * scale
+    want = torch.matmul(torch.softmax(s, -1), vc[:, :, :38].float()).reshape(B, hq * D)
+    assert (out.float() - want).abs().max().item() <= 3e-3 * max(1.0, want.abs().max().item())
+    # swiglu
+    a, b2 = torch.randn(B, 1000, generator=g, device=dev), torch.randn(B, 1000, generator=g, device=dev)
+    act = torch.empty(B, 1000, dtype=torch.float16, device=dev)
+    ops.glue_silu_mul(a, b2, act)
+    assert (act.float() - F.silu(a) * b2).abs().max().item() <= 2e-3 * 4
