@@ -322,14 +322,35 @@ __global__ void __launch_bounds__(kThreads, MINB) gemv_kernel(GemvParams p) {
         const int ti = warp % NT, kpart = warp / NT;
         const int g = lane >> 2, t = lane & 3;
         const bool row_ok = g < p.M;
-        // PCA bases and scales are weights: the first pair of block rows is fetched before
-        // waiting for the preceding kernel, like the producer's weight copies.
+        // ---- activation-side table for kb_begin..kb_end.  A work item is (block row kb, batch
+        // row m); the four lanes t = 0..3 of a lane group take one item (8 activations each), a
+        // warp takes 2 x 8 items per pass, the CTA 128: at batch 1 that is 128 block rows per
+        // pass, so even a CTA with a long K range builds its table in one round of loads.
+        // Two 8-byte entries per (kb, m), read by lanes t = 0 and t = 1 of the main loop:
+        //   entry t=0: { {SxB_hi, 0}, {Z0_hi, Z1_hi} }    entry t=1: { {SxB_lo, 0}, {Z0_lo, Z1_lo} }
+        // The first word multiplies the {dmin, dmax} pair of a column (the zero half cancels
+        // dmax), the second the {c0, c1} * 2^-10 pair; Zj (ref cuda/sx8_decode1_v3.cu:44-65)
+        // is pre-multiplied by 1024.
+        // PCA bases and scales are weights: those of the first pass are fetched before waiting
+        // for the preceding kernel, like the producer's weight copies.
+        const int n_items = (kb_end - kb_begin) * p.M;
+        constexpr int kPass = 16 * kConsumerWarps;
         float4 bq[2][4];
         float sc[2][2];
-        auto load_bases = [&](int kb0) {
+        int ikb[2], im[2];
+        auto locate = [&](int i0) {
 #pragma unroll
             for (int u = 0; u < 2; u++) {
-                int kb = min(kb0 + u, kb_end - 1);
+                int item = min(i0 + u * (kPass / 2) + warp * 8 + g, max(n_items - 1, 0));
+                int q = item / p.M;
+                ikb[u] = kb_begin + q;
+                im[u] = item - q * p.M;
+            }
+        };
+        auto load_bases = [&]() {
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const int kb = ikb[u];
                 const float4* b0p = reinterpret_cast<const float4*>(sg.bases + (long)kb * 64 + t * 8);
                 const float4* b1p = reinterpret_cast<const float4*>(sg.bases + (long)kb * 64 + 32 + t * 8);
                 bq[u][0] = b0p[0]; bq[u][1] = b0p[1]; bq[u][2] = b1p[0]; bq[u][3] = b1p[1];
@@ -337,27 +358,24 @@ __global__ void __launch_bounds__(kThreads, MINB) gemv_kernel(GemvParams p) {
                 sc[u][1] = sg.scales[kb * 2 + 1];
             }
         };
-        if (kb_begin + 2 * warp < kb_end) load_bases(kb_begin + 2 * warp);
+        if (n_items > 0) {
+            locate(0);
+            load_bases();
+        }
         asm volatile("griddepcontrol.wait;" ::: "memory");
 
-        // ---- activation-side table for kb_begin..kb_end: one warp per kb, lane = (m = g, t).
-        // Two 8-byte entries per row m, read by lanes t = 0 and t = 1 of the main loop:
-        //   entry t=0: { {SxB_hi, 0}, {Z0_hi, Z1_hi} }    entry t=1: { {SxB_lo, 0}, {Z0_lo, Z1_lo} }
-        // The first word multiplies the {dmin, dmax} pair of a column (the zero half cancels
-        // dmax), the second the {c0, c1} * 2^-10 pair; Zj (ref cuda/sx8_decode1_v3.cu:44-65)
-        // is pre-multiplied by 1024.  Loads of two kb are issued together to hide their latency.
-        for (int kb0 = kb_begin + 2 * warp; kb0 < kb_end; kb0 += 2 * kConsumerWarps) {
+        for (int i0 = 0; i0 < n_items; i0 += kPass) {
             uint4 raw[2];
-            if (kb0 != kb_begin + 2 * warp) load_bases(kb0);
-#pragma unroll
-            for (int u = 0; u < 2; u++) {
-                int kb = min(kb0 + u, kb_end - 1);
-                raw[u] = make_uint4(0u, 0u, 0u, 0u);
-                if (row_ok) raw[u] = *reinterpret_cast<const uint4*>(p.x + (long)g * p.ldx + (long)kb * 32 + t * 8);
+            if (i0 > 0) {
+                locate(i0);
+                load_bases();
             }
 #pragma unroll
+            for (int u = 0; u < 2; u++)
+                raw[u] = *reinterpret_cast<const uint4*>(p.x + (long)im[u] * p.ldx + (long)ikb[u] * 32 + t * 8);
+#pragma unroll
             for (int u = 0; u < 2; u++) {
-                int kb = kb0 + u;
+                const bool valid = i0 + u * (kPass / 2) + warp * 8 + g < n_items;
                 const __half* hh = reinterpret_cast<const __half*>(&raw[u]);
                 float bb0[8] = {bq[u][0].x, bq[u][0].y, bq[u][0].z, bq[u][0].w, bq[u][1].x, bq[u][1].y, bq[u][1].z, bq[u][1].w};
                 float bb1[8] = {bq[u][2].x, bq[u][2].y, bq[u][2].z, bq[u][2].w, bq[u][3].x, bq[u][3].y, bq[u][3].z, bq[u][3].w};
@@ -381,10 +399,10 @@ __global__ void __launch_bounds__(kThreads, MINB) gemv_kernel(GemvParams p) {
                 split_hilo(sx, sh, sl);
                 split_hilo(z0, z0h, z0l);
                 split_hilo(z1, z1h, z1l);
-                if (t < 2 && kb < kb_end) {
+                if (t < 2 && valid) {
                     uint32_t w0 = (t == 0) ? sh : sl;
                     uint32_t w1 = (t == 0) ? (z0h | (z1h << 16)) : (z0l | (z1l << 16));
-                    uint32_t a = dtab + (kb - kb_begin) * DT_KB + g * 16 + t * 8;
+                    uint32_t a = dtab + (ikb[u] - kb_begin) * DT_KB + im[u] * 16 + t * 8;
                     sts32(a, w0);
                     sts32(a + 4, w1);
                 }
@@ -593,7 +611,7 @@ int env_int(const char* name) {
 // configurations put about 384 CTAs in flight per wave (3 CTAs per SM hold 444; ~2.6 per SM
 // leaves room for the next launch's prefetching CTAs), prefer wide tile groups, and use as
 // little split-K as that allows.  Very large N runs a persistent grid without split-K.
-Choice choose(int N, int n_cb) {
+Choice choose(int N, int n_cb, int M) {
     static const int e_nt = env_int("SX8_GEMV_NT"), e_split = env_int("SX8_GEMV_SPLIT"),
                      e_grid = env_int("SX8_GEMV_GRID");
     const int f_nt = g_tune_nt >= 0 ? g_tune_nt : e_nt, f_split = g_tune_split >= 0 ? g_tune_split : e_split,
@@ -613,8 +631,11 @@ Choice choose(int N, int n_cb) {
             if (split > min_split && n_cb / split < 4) break;
             long ctas = (long)groups * split;
             double score;
-            if (nt == 8 && split == 1 && groups >= 6 * kSMs) {
-                score = 1.0;   // persistent grid, balanced by construction
+            if (split == 1 && (n_tiles + 7) / 8 >= 6 * kSMs) {
+                // very large N (lm_head): no split-K, many waves; four-tile groups measured best
+                // (117 us against 130 us for eight-tile groups on a persistent grid, 151936 x 2560)
+                // at batch 1-4; at batch 8 the activation table costs more per CTA and eight win
+                score = (nt == (M <= 4 ? 4 : 8)) ? 1.0 : (nt == 2 ? 0.8 : 0.9);
             } else {
                 long waves = (ctas + 3 * kSMs - 1) / (3 * kSMs);
                 double per_wave = (double)ctas / (double)waves;
@@ -630,9 +651,9 @@ Choice choose(int N, int n_cb) {
     }
     int groups = (n_tiles + best.nt - 1) / best.nt;
     best.grid_x = groups;
-    if (best.nt == 8 && best.split == 1) {
-        int cap = f_grid > 0 ? f_grid : 3 * kSMs;
-        if (groups > cap) {   // equal number of tile groups per CTA
+    if (best.split == 1) {   // persistent grid: eight-tile groups by default, others on request
+        int cap = f_grid > 0 ? f_grid : (best.nt == 8 ? 3 * kSMs : 0);
+        if (cap > 0 && groups > cap) {   // equal number of tile groups per CTA
             int per = (groups + cap - 1) / cap;
             best.grid_x = (groups + per - 1) / per;
         }
@@ -727,7 +748,7 @@ int gemv_launch_ex(const void* x, int M, int K, long ldx, const void* wt16, cons
         xp = (const __half*)workspace;
         ld = Kp;
     }
-    Choice c = choose(N, n_cb);
+    Choice c = choose(N, n_cb, M);
     const int n_tiles = (int)t16_tiles(N);
     static const int dbg = env_int("SX8_GEMV_DEBUG");
     GemvParams p{};
@@ -797,7 +818,7 @@ int gemv_launch_multi(const void* x, int M, int K, long ldx, int count, const vo
     }
     long n_total = 0;
     for (int i = 0; i < count; i++) n_total += (long)t16_tiles(N[i]) * 16;
-    Choice c = choose((int)n_total, n_cb);
+    Choice c = choose((int)n_total, n_cb, M);
     static const int dbg = env_int("SX8_GEMV_DEBUG");
     GemvParams p{};
     p.nseg = count;
