@@ -367,7 +367,7 @@ def decoder_e2e(dev, prompt=512, new=256):
     graph, at batch 1 (GEMV path) and batch 32 (tensor-core GEMM path)."""
     import torch
     from sx8_quantization_b200.decoder import SX8Decoder, QWEN3_4B_DECODER
-    out = {"prompt_tokens": prompt, "new_tokens": new, "glue": "RMSNorm/RoPE/attention/SwiGLU in PyTorch"}
+    out = {"prompt_tokens": prompt, "new_tokens": new, "glue": "decode step: sx8_glue kernels (nine launches per layer); prefill: PyTorch"}
     for batch in (1, 32):
         dec = SX8Decoder(QWEN3_4B_DECODER, device=dev, seed=9, max_seq=prompt + new, batch=batch)
         g = torch.Generator(device=dev).manual_seed(1234)
