@@ -475,7 +475,9 @@ def run_reference(args):
     n = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
     print(json.dumps({
         "impl": "reference", "metric": "sx8_decode_gemv_weight_GBps", "value": round(v, 4), "unit": "GB/s",
-        "n_gpus": n, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
+        "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(30 * 9728 * 80 / (v * 1e9) * 1e3, 3),   # one call of the sample (gate projection)
+        "higher_is_better": True,
         "scaling": "weak" if n == 1 else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "gemv_sweep_qwen3_4b" if n == 1 else "tp_decode_llama70b",
                    "sample": c["sample"]},
