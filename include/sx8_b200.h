@@ -209,16 +209,21 @@ int sx8_planes_from_blocks(const void* blocks, long n_blk, void* dmin_f16, void*
  *   rope_cache  : rotary embedding (half-split) of q, k at *pos; q_out f16 (B, hq, D); k, v
  *                 written to the caches at *pos; cos_t / sin_t are (S, D/2) f32 tables
  *   attn_decode : softmax(q K^T * scale) V over cache positions 0..*pos; out f16 (B, hq*D);
- *                 D in {64, 128}, hq/hkv in {1, 2, 4, 8}
+ *                 D in {64, 128}, hq/hkv in {1, 2, 4, 8}, S <= 1024.  The positions are split
+ *                 over 8 CTAs per (sequence, kv head) that merge through `scratch`
+ *                 (sx8_glue_attn_scratch_bytes, 16-byte aligned; its first
+ *                 B*hkv*4 bytes are arrival counters: zero them once, the kernel leaves
+ *                 them zero); calls that share a scratch buffer must be stream-ordered
  *   silu_mul    : act_out = f16(silu(g) * u), n elements                                   */
 int sx8_glue_add_rmsnorm(void* h_f32, const void* y_f32, const void* gamma_f32, int B, int H, float eps,
                          void* x_out_f16, void* stream);
 int sx8_glue_rope_cache(const void* q_f32, const void* k_f32, const void* v_f32, const void* pos,
                         const void* cos_t, const void* sin_t, int B, int hq, int hkv, int D, int S,
                         void* q_out_f16, void* k_cache_f16, void* v_cache_f16, void* stream);
+size_t sx8_glue_attn_scratch_bytes(int B, int hq, int hkv, int D);
 int sx8_glue_attn_decode(const void* q_f16, const void* k_cache_f16, const void* v_cache_f16,
                          const void* pos, int B, int hq, int hkv, int D, int S, float scale,
-                         void* out_f16, void* stream);
+                         void* out_f16, void* scratch, size_t scratch_bytes, void* stream);
 int sx8_glue_silu_mul(const void* g_f32, const void* u_f32, long n, void* act_out_f16, void* stream);
 
 /* Device-side error word of the bounded waits inside the pipelined kernels: 0 when no

@@ -36,7 +36,8 @@ SIGNATURES = {
     "sx8_planes_from_blocks": (_i, [_vp, _l, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "sx8_glue_add_rmsnorm": (_i, [_vp, _vp, _vp, _i, _i, ctypes.c_float, _vp, _vp]),
     "sx8_glue_rope_cache": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
-    "sx8_glue_attn_decode": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, ctypes.c_float, _vp, _vp]),
+    "sx8_glue_attn_scratch_bytes": (_sz, [_i, _i, _i, _i]),
+    "sx8_glue_attn_decode": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, ctypes.c_float, _vp, _vp, _sz, _vp]),
     "sx8_glue_silu_mul": (_i, [_vp, _vp, _l, _vp, _vp]),
     "sx8_device_error_flag": (_i, [ctypes.POINTER(ctypes.c_uint)]),
 }

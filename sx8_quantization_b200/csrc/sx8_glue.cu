@@ -11,6 +11,30 @@
 
 namespace sx8 {
 
+// Programmatic dependent launch: let the next kernel of the stream (a GEMV, which then starts
+// streaming its weights) be scheduled at once, and wait for the preceding kernel before
+// touching any input.  Both are no-ops for a launch without the attribute.
+__device__ __forceinline__ void pdl_prologue() {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// Launch with the programmatic-stream-serialization attribute.
+template <class... KArgs, class... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
@@ -22,30 +46,58 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
-// h[b] += y[b] (when y != null); x[b] = f16( h[b] * rsqrt(mean(h[b]^2) + eps) * gamma )
-__global__ void __launch_bounds__(256)
+// h[b] += y[b] (when y != null); x[b] = f16( h[b] * rsqrt(mean(h[b]^2) + eps) * gamma ).
+// One CTA of 1024 threads per row; a thread keeps its (up to kRmsPer) float4 of the row in
+// registers between the sum and the scaling, so the row is read once (H % 4 == 0,
+// H <= 4096 * kRmsPer).
+constexpr int kRmsThreads = 1024, kRmsPer = 4;
+__global__ void __launch_bounds__(kRmsThreads)
 add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ y, const float* __restrict__ gamma, int H, float eps,
                    __half* __restrict__ x) {
-    __shared__ float red[8];
+    pdl_prologue();
+    __shared__ float red[32];
     const long row = blockIdx.x;
-    float* hr = h + row * H;
+    float4* hr = reinterpret_cast<float4*>(h + row * H);
+    const float4* yr = y ? reinterpret_cast<const float4*>(y + row * H) : nullptr;
+    const int n4 = H >> 2;
+    float4 v[kRmsPer];
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += 256) {
-        float v = hr[i];
-        if (y) {
-            v += y[row * H + i];
-            hr[i] = v;
+#pragma unroll
+    for (int j = 0; j < kRmsPer; j++) {
+        const int i = threadIdx.x + j * kRmsThreads;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < n4) {
+            v[j] = hr[i];
+            if (yr) {
+                float4 w = yr[i];
+                v[j].x += w.x; v[j].y += w.y; v[j].z += w.z; v[j].w += w.w;
+                hr[i] = v[j];
+            }
+            ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
         }
-        ss = fmaf(v, v, ss);
     }
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
     __syncthreads();
     float tot = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; w++) tot += red[w];
+    for (int w = 0; w < 32; w++) tot += red[w];
     const float r = rsqrtf(tot / (float)H + eps);
-    for (int i = threadIdx.x; i < H; i += 256) x[row * H + i] = __float2half_rn(hr[i] * r * gamma[i]);
+    const float4* gr = reinterpret_cast<const float4*>(gamma);
+    uint2* xr = reinterpret_cast<uint2*>(x + row * H);
+#pragma unroll
+    for (int j = 0; j < kRmsPer; j++) {
+        const int i = threadIdx.x + j * kRmsThreads;
+        if (i < n4) {
+            float4 g = gr[i];
+            __half2 lo = __floats2half2_rn(v[j].x * r * g.x, v[j].y * r * g.y);
+            __half2 hi = __floats2half2_rn(v[j].z * r * g.z, v[j].w * r * g.w);
+            uint2 o;
+            o.x = *reinterpret_cast<uint32_t*>(&lo);
+            o.y = *reinterpret_cast<uint32_t*>(&hi);
+            xr[i] = o;
+        }
+    }
 }
 
 // Rotary embedding (half-split convention) of q and k at position *pos; q -> f16 (B, hq, D);
@@ -56,6 +108,7 @@ rope_cache_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
                   const long* __restrict__ pos_p, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                   int hq, int hkv, int D, int S, __half* __restrict__ q_out, __half* __restrict__ k_cache,
                   __half* __restrict__ v_cache) {
+    pdl_prologue();
     const int b = blockIdx.y, head = blockIdx.x;
     const long pos = *pos_p;
     if (pos < 0 || pos >= S) return;
@@ -79,53 +132,74 @@ rope_cache_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     }
 }
 
-// Attention of one new position over the cache: out (B, hq*D) f16.  One CTA per (sequence, kv
-// head); the GRP = hq/hkv query heads of the group share every K and V row read.  Scores of
-// positions 0..*pos are kept in shared memory (S floats per query head).
+// Attention of one new position over the cache: out (B, hq*D) f16.  Grid (kv head, sequence,
+// kAttnSplit): a CTA takes one slice of the cached positions 0..*pos of one kv head; the
+// GRP = hq/hkv query heads of the group share every K and V row it reads.  It writes its
+// running maximum, its sum of exponentials and its unnormalised output to scratch; the CTA
+// that finishes last for a (sequence, kv head) -- decided by a counter in scratch, which it
+// resets -- merges the kAttnSplit partial results.  Everything here is latency: a 768-position
+// cache of one head is 190 KB, so the point of the split is to put 8 times as many loads in
+// flight, not to share bandwidth.
+constexpr int kAttnSplit = 8, kAttnThreads = 256;
 template <int D, int GRP>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kAttnThreads)
 attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_cache, const __half* __restrict__ v_cache,
-                   const long* __restrict__ pos_p, int hkv, int S, float scale, __half* __restrict__ out) {
-    extern __shared__ float sc[];                 // GRP * S scores, then GRP * D query values
-    float* qs = sc + (size_t)GRP * S;
+                   const long* __restrict__ pos_p, int hkv, int S, float scale, float* __restrict__ part,
+                   unsigned* __restrict__ counters, __half* __restrict__ out) {
+    pdl_prologue();
+    constexpr int CH = 128;                       // at most 128 positions per CTA (S <= 1024)
+    __shared__ float sc[GRP][CH];
+    __shared__ float qs[GRP * D];
     __shared__ float red[GRP][8];
-    const int b = blockIdx.y, hv = blockIdx.x;
+    __shared__ float acc_s[(kAttnThreads / (D / 2)) * GRP * D];
+    __shared__ unsigned s_last;
+    const int b = blockIdx.y, hv = blockIdx.x, sp = blockIdx.z;
     const int n = (int)min((long)S, *pos_p + 1);  // positions in the cache, the new one included
+    const int chunk = (n + kAttnSplit - 1) / kAttnSplit;
+    const int t0 = sp * chunk, cnt = max(0, min(chunk, n - t0));
     const __half* qg = q + ((long)b * hkv + hv) * GRP * D;
-    for (int i = threadIdx.x; i < GRP * D; i += 256) qs[i] = __half2float(qg[i]) * scale;
+    for (int i = threadIdx.x; i < GRP * D; i += kAttnThreads) qs[i] = __half2float(qg[i]) * scale;
     __syncthreads();
-    const __half* kb = k_cache + ((long)b * hkv + hv) * (long)S * D;
-    const __half* vb = v_cache + ((long)b * hkv + hv) * (long)S * D;
-    // scores: one thread per position, all GRP heads at once (the K row is read once)
+    const __half* kb = k_cache + (((long)b * hkv + hv) * (long)S + t0) * D;
+    const __half* vb = v_cache + (((long)b * hkv + hv) * (long)S + t0) * D;
+    // scores: two threads per position (each half of the head dimension), all GRP heads at once
     float mx[GRP];
 #pragma unroll
     for (int g = 0; g < GRP; g++) mx[g] = -INFINITY;
-    for (int t = threadIdx.x; t < n; t += 256) {
-        const uint4* kr = reinterpret_cast<const uint4*>(kb + (long)t * D);
+    {
+        const int t = threadIdx.x >> 1, hf = threadIdx.x & 1;
         float acc[GRP];
 #pragma unroll
         for (int g = 0; g < GRP; g++) acc[g] = 0.f;
-#pragma unroll 4
-        for (int c = 0; c < D / 8; c++) {
-            uint4 raw = kr[c];
-            const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+        if (t < cnt) {
+            const uint4* kr = reinterpret_cast<const uint4*>(kb + (long)t * D + hf * (D / 2));
+            uint4 raw[D / 16];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                float2 kv = __half22float2(h2[j]);
+            for (int c = 0; c < D / 16; c++) raw[c] = kr[c];
 #pragma unroll
-                for (int g = 0; g < GRP; g++) {
-                    acc[g] = fmaf(kv.x, qs[g * D + c * 8 + 2 * j], acc[g]);
-                    acc[g] = fmaf(kv.y, qs[g * D + c * 8 + 2 * j + 1], acc[g]);
+            for (int c = 0; c < D / 16; c++) {
+                const __half2* h2 = reinterpret_cast<const __half2*>(&raw[c]);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    float2 kv = __half22float2(h2[j]);
+                    const int d = hf * (D / 2) + c * 8 + 2 * j;
+#pragma unroll
+                    for (int g = 0; g < GRP; g++) {
+                        acc[g] = fmaf(kv.x, qs[g * D + d], acc[g]);
+                        acc[g] = fmaf(kv.y, qs[g * D + d + 1], acc[g]);
+                    }
                 }
             }
         }
 #pragma unroll
         for (int g = 0; g < GRP; g++) {
-            sc[g * S + t] = acc[g];
-            mx[g] = fmaxf(mx[g], acc[g]);
+            acc[g] += __shfl_xor_sync(0xFFFFFFFFu, acc[g], 1);
+            if (t < cnt) {
+                if (hf == 0) sc[g][t] = acc[g];
+                mx[g] = acc[g];
+            }
         }
     }
-    // block-wide max and sum per head
     float m[GRP], den[GRP];
 #pragma unroll
     for (int g = 0; g < GRP; g++) {
@@ -141,20 +215,20 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_ca
         m[g] = w;
     }
     __syncthreads();
-    float part[GRP];
+    float psum[GRP];
 #pragma unroll
-    for (int g = 0; g < GRP; g++) part[g] = 0.f;
-    for (int t = threadIdx.x; t < n; t += 256) {
+    for (int g = 0; g < GRP; g++) psum[g] = 0.f;
+    if (threadIdx.x < cnt) {
 #pragma unroll
         for (int g = 0; g < GRP; g++) {
-            float e = __expf(sc[g * S + t] - m[g]);
-            sc[g * S + t] = e;
-            part[g] += e;
+            float e = __expf(sc[g][threadIdx.x] - m[g]);
+            sc[g][threadIdx.x] = e;
+            psum[g] = e;
         }
     }
 #pragma unroll
     for (int g = 0; g < GRP; g++) {
-        float w = warp_sum(part[g]);
+        float w = warp_sum(psum[g]);
         if ((threadIdx.x & 31) == 0) red[g][threadIdx.x >> 5] = w;
     }
     __syncthreads();
@@ -165,41 +239,83 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_ca
         for (int i = 0; i < 8; i++) w += red[g][i];
         den[g] = w;
     }
-    // out[g][d] = sum_t p[g][t] * V[t][d]: thread = (slice of positions, pair of dims); D/2 threads
-    // cover a V row with 4-byte loads, 256 / (D/2) slices split the positions
-    constexpr int TPR = D / 2, SL = 256 / TPR;
+    // o[g][d] = sum_t p[g][t] * V[t][d]: D/2 threads cover a V row with 4-byte loads, the
+    // 256 / (D/2) slices split the positions; four rows are in flight per thread
+    constexpr int TPR = D / 2, SL = kAttnThreads / TPR;
     const int dp = threadIdx.x % TPR, sl = threadIdx.x / TPR;
     float o0[GRP], o1[GRP];
 #pragma unroll
     for (int g = 0; g < GRP; g++) { o0[g] = 0.f; o1[g] = 0.f; }
-    for (int t = sl; t < n; t += SL) {
-        float2 vv = __half22float2(*reinterpret_cast<const __half2*>(vb + (long)t * D + 2 * dp));
+    for (int tb = sl; tb < cnt; tb += 4 * SL) {
+        __half2 vv[4];
 #pragma unroll
-        for (int g = 0; g < GRP; g++) {
-            float pw = sc[g * S + t];
-            o0[g] = fmaf(pw, vv.x, o0[g]);
-            o1[g] = fmaf(pw, vv.y, o1[g]);
+        for (int u = 0; u < 4; u++) {
+            const int t = tb + u * SL;
+            vv[u] = (t < cnt) ? *reinterpret_cast<const __half2*>(vb + (long)t * D + 2 * dp) : __half2();
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int t = tb + u * SL;
+            if (t < cnt) {
+                float2 f = __half22float2(vv[u]);
+#pragma unroll
+                for (int g = 0; g < GRP; g++) {
+                    float pw = sc[g][t];
+                    o0[g] = fmaf(pw, f.x, o0[g]);
+                    o1[g] = fmaf(pw, f.y, o1[g]);
+                }
+            }
         }
     }
-    __syncthreads();                              // scores are dead: reuse the buffer for the slices
-    float* acc = sc;                              // (SL, GRP, D)
 #pragma unroll
     for (int g = 0; g < GRP; g++) {
-        acc[(sl * GRP + g) * D + 2 * dp] = o0[g];
-        acc[(sl * GRP + g) * D + 2 * dp + 1] = o1[g];
+        acc_s[(sl * GRP + g) * D + 2 * dp] = o0[g];
+        acc_s[(sl * GRP + g) * D + 2 * dp + 1] = o1[g];
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < GRP * D; i += 256) {
-        float s = 0.f;
+    // partial result of this slice: [GRP][D] outputs, then GRP maxima, then GRP sums
+    constexpr int PSZ = GRP * (D + 2);
+    float* mine = part + (((long)b * hkv + hv) * kAttnSplit + sp) * PSZ;
+    for (int i = threadIdx.x; i < GRP * D; i += kAttnThreads) {
+        float sum = 0.f;
 #pragma unroll
-        for (int j = 0; j < SL; j++) s += acc[j * GRP * D + i];
-        out[((long)b * hkv + hv) * GRP * D + i] = __float2half_rn(s / den[i / D]);
+        for (int j = 0; j < SL; j++) sum += acc_s[j * GRP * D + i];
+        mine[i] = sum;
     }
+    if (threadIdx.x < GRP) {
+        mine[GRP * D + threadIdx.x] = m[threadIdx.x];
+        mine[GRP * D + GRP + threadIdx.x] = den[threadIdx.x];
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(&counters[b * hkv + hv], 1u);
+    __syncthreads();
+    if (s_last != kAttnSplit - 1) return;
+    __threadfence();
+    // merge the slices (this CTA arrived last, so all of them are in scratch)
+    const float* all = part + ((long)b * hkv + hv) * kAttnSplit * PSZ;
+    for (int i = threadIdx.x; i < GRP * D; i += kAttnThreads) {
+        const int g = i / D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int s2 = 0; s2 < kAttnSplit; s2++) M = fmaxf(M, __ldcg(all + s2 * PSZ + GRP * D + g));
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int s2 = 0; s2 < kAttnSplit; s2++) {
+            float ms = __ldcg(all + s2 * PSZ + GRP * D + g);
+            float w = (ms == -INFINITY) ? 0.f : __expf(ms - M);
+            L = fmaf(w, __ldcg(all + s2 * PSZ + GRP * D + GRP + g), L);
+            O = fmaf(w, __ldcg(all + s2 * PSZ + i), O);
+        }
+        out[((long)b * hkv + hv) * GRP * D + i] = __float2half_rn(O / L);
+    }
+    if (threadIdx.x == 0) counters[b * hkv + hv] = 0u;   // ready for the next call
 }
 
 // act = f16( silu(g) * u )
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(const float* __restrict__ g, const float* __restrict__ u, long n, __half* __restrict__ act) {
+    pdl_prologue();
     long i = (long)blockIdx.x * 256 + threadIdx.x;
     if (i >= n) return;
     float a = g[i];
@@ -213,10 +329,11 @@ using namespace sx8;
 extern "C" int sx8_glue_add_rmsnorm(void* h, const void* y, const void* gamma, int B, int H, float eps, void* x_out,
                                     void* stream) {
     SX8_REQUIRE(h && gamma && x_out, "sx8_glue_add_rmsnorm: null pointer");
-    SX8_REQUIRE(B > 0 && H > 0, "sx8_glue_add_rmsnorm: need B>0, H>0");
-    add_rmsnorm_kernel<<<(unsigned)B, 256, 0, (cudaStream_t)stream>>>((float*)h, (const float*)y, (const float*)gamma, H, eps,
-                                                                       (__half*)x_out);
-    SX8_LAUNCH_CHECK("add_rmsnorm_kernel");
+    SX8_REQUIRE(B > 0 && H > 0 && (H % 4) == 0 && H <= 4 * kRmsThreads * kRmsPer,
+                "sx8_glue_add_rmsnorm: need B>0 and H a multiple of 4 up to %d (got %d)", 4 * kRmsThreads * kRmsPer, H);
+    cudaError_t e = launch_pdl(add_rmsnorm_kernel, dim3((unsigned)B), dim3(kRmsThreads), 0, (cudaStream_t)stream, (float*)h,
+                               (const float*)y, (const float*)gamma, H, eps, (__half*)x_out);
+    if (e != cudaSuccess) return cuda_fail(e, "launch(add_rmsnorm_kernel)");
     return SX8_OK;
 }
 
@@ -226,38 +343,41 @@ extern "C" int sx8_glue_rope_cache(const void* q, const void* k, const void* v, 
     SX8_REQUIRE(q && k && v && pos && cos_t && sin_t && q_out && k_cache && v_cache, "sx8_glue_rope_cache: null pointer");
     SX8_REQUIRE(B > 0 && hq > 0 && hkv > 0 && D > 0 && (D % 2) == 0 && S > 0, "sx8_glue_rope_cache: bad sizes");
     dim3 grid((unsigned)(hq + 2 * hkv), (unsigned)B, 1);
-    rope_cache_kernel<<<grid, 64, 0, (cudaStream_t)stream>>>((const float*)q, (const float*)k, (const float*)v, (const long*)pos,
-                                                             (const float*)cos_t, (const float*)sin_t, hq, hkv, D, S,
-                                                             (__half*)q_out, (__half*)k_cache, (__half*)v_cache);
-    SX8_LAUNCH_CHECK("rope_cache_kernel");
+    cudaError_t e = launch_pdl(rope_cache_kernel, grid, dim3(64), 0, (cudaStream_t)stream, (const float*)q, (const float*)k,
+                               (const float*)v, (const long*)pos, (const float*)cos_t, (const float*)sin_t, hq, hkv, D, S,
+                               (__half*)q_out, (__half*)k_cache, (__half*)v_cache);
+    if (e != cudaSuccess) return cuda_fail(e, "launch(rope_cache_kernel)");
     return SX8_OK;
 }
 
+extern "C" size_t sx8_glue_attn_scratch_bytes(int B, int hq, int hkv, int D) {
+    if (B <= 0 || hq <= 0 || hkv <= 0 || D <= 0) return 0;
+    // counters (one per sequence and kv head, rounded up to 256 bytes), then the partial results
+    size_t cnt = (((size_t)B * hkv * sizeof(unsigned)) + 255) & ~(size_t)255;
+    return cnt + (size_t)B * hkv * kAttnSplit * (size_t)(hq / hkv) * (D + 2) * sizeof(float);
+}
+
 extern "C" int sx8_glue_attn_decode(const void* q, const void* k_cache, const void* v_cache, const void* pos, int B, int hq,
-                                    int hkv, int D, int S, float scale, void* out, void* stream) {
-    SX8_REQUIRE(q && k_cache && v_cache && pos && out, "sx8_glue_attn_decode: null pointer");
+                                    int hkv, int D, int S, float scale, void* out, void* scratch, size_t scratch_bytes,
+                                    void* stream) {
+    SX8_REQUIRE(q && k_cache && v_cache && pos && out && scratch, "sx8_glue_attn_decode: null pointer");
     SX8_REQUIRE(B > 0 && hkv > 0 && S > 0 && hq % hkv == 0, "sx8_glue_attn_decode: bad sizes");
     const int grp = hq / hkv;
     SX8_REQUIRE((D == 128 || D == 64) && (grp == 4 || grp == 2 || grp == 1 || grp == 8),
                 "sx8_glue_attn_decode: supports head_dim 64 or 128 and 1, 2, 4 or 8 query heads per kv head (got %d, %d)", D, grp);
-    // scores (grp * S floats) + scaled queries (grp * D); the buffer is reused for the
-    // (256 / (D/2)) x grp x D partial outputs
-    size_t smem = sizeof(float) * ((size_t)grp * S + (size_t)grp * D);
-    size_t need2 = sizeof(float) * (size_t)(256 / (D / 2)) * grp * D;
-    if (need2 > smem) smem = need2;
-    SX8_REQUIRE(smem <= 200 * 1024, "sx8_glue_attn_decode: cache length %d needs %zu bytes of shared memory", S, smem);
-    dim3 grid((unsigned)hkv, (unsigned)B, 1);
+    SX8_REQUIRE(S <= 128 * kAttnSplit, "sx8_glue_attn_decode: cache length %d exceeds %d", S, 128 * kAttnSplit);
+    SX8_REQUIRE(scratch_bytes >= sx8_glue_attn_scratch_bytes(B, hq, hkv, D) && (reinterpret_cast<uintptr_t>(scratch) % 16) == 0,
+                "sx8_glue_attn_decode: scratch too small or misaligned (need %zu bytes)", sx8_glue_attn_scratch_bytes(B, hq, hkv, D));
+    unsigned* counters = (unsigned*)scratch;
+    float* part = (float*)((uint8_t*)scratch + ((((size_t)B * hkv * sizeof(unsigned)) + 255) & ~(size_t)255));
+    dim3 grid((unsigned)hkv, (unsigned)B, (unsigned)kAttnSplit);
     cudaStream_t st = (cudaStream_t)stream;
 #define SX8_ATTN(DD, GG)                                                                                              \
     do {                                                                                                              \
-        if (smem > 48 * 1024) {                                                                                       \
-            cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<DD, GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                                 (int)smem);                                                          \
-            if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(attn_decode)");                          \
-        }                                                                                                             \
-        attn_decode_kernel<DD, GG><<<grid, 256, smem, st>>>((const __half*)q, (const __half*)k_cache,                 \
-                                                            (const __half*)v_cache, (const long*)pos, hkv, S, scale,  \
-                                                            (__half*)out);                                            \
+        cudaError_t e2 = launch_pdl(attn_decode_kernel<DD, GG>, grid, dim3(kAttnThreads), 0, st, (const __half*)q,    \
+                                    (const __half*)k_cache, (const __half*)v_cache, (const long*)pos, hkv, S, scale,  \
+                                    part, counters, (__half*)out);                                                    \
+        if (e2 != cudaSuccess) return cuda_fail(e2, "launch(attn_decode_kernel)");                                    \
     } while (0)
     if (D == 128 && grp == 4) SX8_ATTN(128, 4);
     else if (D == 128 && grp == 8) SX8_ATTN(128, 8);
@@ -268,15 +388,14 @@ extern "C" int sx8_glue_attn_decode(const void* q, const void* k_cache, const vo
     else if (D == 64 && grp == 2) SX8_ATTN(64, 2);
     else SX8_ATTN(64, 1);
 #undef SX8_ATTN
-    SX8_LAUNCH_CHECK("attn_decode_kernel");
     return SX8_OK;
 }
 
 extern "C" int sx8_glue_silu_mul(const void* g, const void* u, long n, void* act_out, void* stream) {
     SX8_REQUIRE(g && u && act_out, "sx8_glue_silu_mul: null pointer");
     SX8_REQUIRE(n > 0 && (n + 255) / 256 <= 0x7FFFFFFFL, "sx8_glue_silu_mul: bad size %ld", n);
-    silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const float*)g, (const float*)u, n,
-                                                                                    (__half*)act_out);
-    SX8_LAUNCH_CHECK("silu_mul_kernel");
+    cudaError_t e = launch_pdl(silu_mul_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream,
+                               (const float*)g, (const float*)u, n, (__half*)act_out);
+    if (e != cudaSuccess) return cuda_fail(e, "launch(silu_mul_kernel)");
     return SX8_OK;
 }

@@ -82,6 +82,7 @@ class SX8Decoder:
                     "q": torch.empty(B, self.nq, **f32), "k": torch.empty(B, self.nkv, **f32),
                     "v": torch.empty(B, self.nkv, **f32), "g": torch.empty(B, c["ffn"], **f32),
                     "u": torch.empty(B, c["ffn"], **f32), "logits": torch.empty(B, c["vocab"], **f32)}
+        self.attn_scratch = ops.glue_attn_scratch(B, c["n_q"], c["n_kv"], D, self.dev)
         self.packed_bytes = sum(t["wt16"].numel() for L in self.layers for t in L.values()) + self.lm_head["wt16"].numel()
 
     # ------------------------------------------------------------------ pieces
@@ -153,7 +154,8 @@ class SX8Decoder:
             else:
                 q, k, v = (self._lin_into(b["x"], L[n], b[n]) for n in ("q", "k", "v"))
             ops.glue_rope_cache(q, k, v, self.pos, self.cos, self.sin, hq, hkv, D, b["q16"], self.k_cache[l], self.v_cache[l])
-            ops.glue_attn_decode(b["q16"], self.k_cache[l], self.v_cache[l], self.pos, hq, hkv, D, self.scale, b["a"])
+            ops.glue_attn_decode(b["q16"], self.k_cache[l], self.v_cache[l], self.pos, hq, hkv, D, self.scale, b["a"],
+                                 self.attn_scratch)
             self._lin_into(b["a"], L["o"], b["o"])
             ops.glue_add_rmsnorm(b["h"], b["o"], self.gamma, c["eps"], b["x"])
             if self.multi is not None:

@@ -320,11 +320,17 @@ def glue_rope_cache(q, k, v, pos, cos_t, sin_t, hq, hkv, D, q_out, k_cache, v_ca
     return q_out
 
 
-def glue_attn_decode(q16, k_cache, v_cache, pos, hq, hkv, D, scale, out):
+def glue_attn_scratch(B, hq, hkv, D, device):
+    """Zeroed scratch for glue_attn_decode (arrival counters + partial results)."""
+    return torch.zeros(_lib.lib().sx8_glue_attn_scratch_bytes(B, hq, hkv, D), dtype=torch.uint8, device=device)
+
+
+def glue_attn_decode(q16, k_cache, v_cache, pos, hq, hkv, D, scale, out, scratch):
     B, S = q16.shape[0], k_cache.shape[2]
     with torch.cuda.device(q16.device):
         rc = _lib.lib().sx8_glue_attn_decode(q16.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), pos.data_ptr(), B, hq,
-                                             hkv, D, S, float(scale), out.data_ptr(), _stream(q16))
+                                             hkv, D, S, float(scale), out.data_ptr(), scratch.data_ptr(), scratch.numel(),
+                                             _stream(q16))
     _lib.check(rc, "sx8_glue_attn_decode")
     return out
 

@@ -133,7 +133,10 @@ def test_glue_kernels_against_pytorch():
     assert (q16.view(B, hq, D).float() - qr.float()).abs().max().item() <= 2e-3
     out = torch.empty(B, hq * D, dtype=torch.float16, device=dev)
     scale = D ** -0.5
-    ops.glue_attn_decode(q16, kc, vc, pos, hq, hkv, D, scale, out)
+    scratch = ops.glue_attn_scratch(B, hq, hkv, D, dev)
+    for _ in range(2):   # twice: the arrival counters must come back to zero
+        out.zero_()
+        ops.glue_attn_decode(q16, kc, vc, pos, hq, hkv, D, scale, out, scratch)
     grp = hq // hkv
     s = torch.matmul(q16.view(B, hkv, grp, D).float(), kc[:, :, :38].float().transpose(-1, -2)) * scale
     want = torch.matmul(torch.softmax(s, -1), vc[:, :, :38].float()).reshape(B, hq * D)
