@@ -38,8 +38,17 @@ namespace sx8 {
 constexpr int kConsumerWarps = 8;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr uint32_t kSpinLimit = 1u << 22;
-constexpr int kMaxKbPerCta = 256;   // capacity of the per-CTA activation table
-constexpr int DT_KB = 128;          // table bytes per kb: [m][t = 0,1] x {lo-term word, coefficient-term word}
+// Per-CTA activation table: 16 bytes per (block row, batch row): [t = 0,1] x {lo-term word,
+// coefficient-term word}; a block row takes 16*M bytes.  32 KB of table keep three CTAs per SM,
+// so a CTA can cover 256 block rows at batch 8 and 1024 at batch 1 or 2 (a lane group of the
+// main loop that belongs to a batch row >= M reads past its block row's entries; the table is
+// padded by 128 bytes for the last one, and those lanes' results are never stored).
+constexpr int kTableBytes = 32768;
+__host__ __device__ inline int table_stride(int M) { return 16 * M; }
+inline int max_kb_per_cta(int M) {
+    int v = kTableBytes / table_stride(M);
+    return v > 1024 ? 1024 : v;
+}
 
 // ------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -223,7 +232,7 @@ struct GemvCfg {
     static constexpr int STAGE = OFF_X + 8 * XROW;
     static constexpr int RED_BYTES = kConsumerWarps * 32 * 16;
     static constexpr int FIXED = STAGES * STAGE + RED_BYTES + 2 * STAGES * 8 + 16;
-    static int smem_bytes(int kb_per_cta) { return FIXED + kb_per_cta * DT_KB; }
+    static int smem_bytes(int kb_per_cta, int M) { return FIXED + kb_per_cta * table_stride(M) + 128; }
 };
 
 template <int NT, int KB_S, int STAGES, int MINB = 3>
@@ -235,6 +244,7 @@ __global__ void __launch_bounds__(kThreads, MINB) gemv_kernel(GemvParams p) {
     const uint32_t bar_full = red + C::RED_BYTES;
     const uint32_t bar_empty = bar_full + STAGES * 8;
     const uint32_t dtab = bar_empty + STAGES * 8 + 16;
+    const int dt_kb = table_stride(p.M);
 
     asm volatile("griddepcontrol.launch_dependents;");
 
@@ -402,7 +412,7 @@ __global__ void __launch_bounds__(kThreads, MINB) gemv_kernel(GemvParams p) {
                 if (t < 2 && valid) {
                     uint32_t w0 = (t == 0) ? sh : sl;
                     uint32_t w1 = (t == 0) ? (z0h | (z1h << 16)) : (z0l | (z1l << 16));
-                    uint32_t a = dtab + (ikb[u] - kb_begin) * DT_KB + im[u] * 16 + t * 8;
+                    uint32_t a = dtab + (ikb[u] - kb_begin) * dt_kb + im[u] * 16 + t * 8;
                     sts32(a, w0);
                     sts32(a + 4, w1);
                 }
@@ -435,7 +445,7 @@ __global__ void __launch_bounds__(kThreads, MINB) gemv_kernel(GemvParams p) {
                     if (row_ok) xq = lds128(st + C::OFF_X + g * C::XROW + r * 64 + t * 16);
                     uint32_t dv0 = 0u, dv1 = 0u;
                     if (t < 2) {
-                        uint32_t a = dtab + (j * KB_S + r) * DT_KB + g * 16 + t * 8;
+                        uint32_t a = dtab + (j * KB_S + r) * dt_kb + g * 16 + t * 8;
                         asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(dv0), "=r"(dv1) : "r"(a) : "memory");
                     }
 
@@ -617,7 +627,7 @@ Choice choose(int N, int n_cb, int M) {
     const int f_nt = g_tune_nt >= 0 ? g_tune_nt : e_nt, f_split = g_tune_split >= 0 ? g_tune_split : e_split,
               f_grid = g_tune_grid >= 0 ? g_tune_grid : e_grid;
     const int n_tiles = (int)t16_tiles(N);
-    const int min_split = (n_cb + kMaxKbPerCta - 1) / kMaxKbPerCta;
+    const int min_split = (n_cb + max_kb_per_cta(M) - 1) / max_kb_per_cta(M);
     Choice best{8, min_split, 0};
     double best_score = -1e30;
     const int nts[3] = {8, 4, 2};
@@ -649,8 +659,20 @@ Choice choose(int N, int n_cb, int M) {
             }
         }
     }
+    // Large matrices (>= 48 MB packed; the 70B-class projections): four-tile groups with a
+    // 2- or 3-way split measured best (28672 x 8192: 78 us against 88; 8192 x 28672: 82 against
+    // 85; 8192 x 8192: 27.9 against 29.9 for the rule above) unless N alone gives thousands of
+    // groups (the lm_head rule above).
+    if (!f_nt && !f_split && (long)n_tiles * n_cb * T16_UNIT >= (48L << 20) && (n_tiles + 7) / 8 < 6 * kSMs) {
+        int g4 = (n_tiles + 3) / 4;
+        int nt = 4, sp = g4 <= 256 ? 3 : 2;
+        if (M > 4) { nt = 8; sp = 3; }   // batch 5..8: the activation table costs more per CTA (94 us against 116)
+        best = Choice{nt, sp < min_split ? min_split : sp, 0};
+    }
     int groups = (n_tiles + best.nt - 1) / best.nt;
     best.grid_x = groups;
+    static const int verbose = env_int("SX8_GEMV_VERBOSE");
+    if (verbose) fprintf(stderr, "sx8 gemv launch shape: N=%d n_cb=%d M=%d -> nt=%d split=%d groups=%d\n", N, n_cb, M, best.nt, best.split, groups);
     if (best.split == 1) {   // persistent grid: eight-tile groups by default, others on request
         int cap = f_grid > 0 ? f_grid : (best.nt == 8 ? 3 * kSMs : 0);
         if (cap > 0 && groups > cap) {   // equal number of tile groups per CTA
@@ -670,7 +692,7 @@ int launch_gemv(const GemvParams& p, int grid_x, unsigned flags, cudaStream_t st
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
         e = cudaFuncSetAttribute(gemv_kernel<NT, KB_S, STAGES, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 C::smem_bytes(kMaxKbPerCta));
+                                 C::smem_bytes(kTableBytes / 16, 1));
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemv smem)");
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
@@ -678,7 +700,7 @@ int launch_gemv(const GemvParams& p, int grid_x, unsigned flags, cudaStream_t st
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid_x, (unsigned)p.split, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = (size_t)C::smem_bytes(kb_per);
+    cfg.dynamicSmemBytes = (size_t)C::smem_bytes(kb_per, p.M);
     cfg.stream = stream;
     cudaLaunchAttribute attrs[2];
     unsigned na = 0;
@@ -841,7 +863,8 @@ int gemv_check(const char* who, const void* x, int M, int Mmax, int K, long ldx,
     SX8_REQUIRE(M >= 1 && M <= Mmax, "%s: M must be in 1..%d (got %d)", who, Mmax, M);
     SX8_REQUIRE(N > 0, "%s: N must be positive (got %d)", who, N);
     SX8_REQUIRE(K > 0 && n_cb == (K + 31) / 32, "%s: need K>0 and n_cb == ceil(K/32) (got K=%d n_cb=%d)", who, K, n_cb);
-    SX8_REQUIRE(n_cb <= 8 * kMaxKbPerCta, "%s: K too large (n_cb=%d, limit %d)", who, n_cb, 8 * kMaxKbPerCta);
+    SX8_REQUIRE(n_cb <= 8 * max_kb_per_cta(M > 8 ? 8 : (M < 1 ? 1 : M)), "%s: K too large for this batch (n_cb=%d, limit %d)", who,
+                n_cb, 8 * max_kb_per_cta(M > 8 ? 8 : (M < 1 ? 1 : M)));
     SX8_REQUIRE(ldx >= K, "%s: ldx (%ld) < K (%d)", who, ldx, K);
     SX8_REQUIRE((reinterpret_cast<uintptr_t>(wt16) % 16) == 0, "%s: wt16 must be 16-byte aligned (TMA bulk copies)", who);
     SX8_REQUIRE((reinterpret_cast<uintptr_t>(bases) % 16) == 0 && (reinterpret_cast<uintptr_t>(x) % 2) == 0 &&
