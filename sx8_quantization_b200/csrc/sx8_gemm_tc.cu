@@ -55,7 +55,7 @@ struct Cfg {
     // stages, packed-slab stages.  Shared memory, in order: X tiles, operand tiles, slabs,
     // barriers, the tensor-memory address.
     static constexpr int smem_bytes(int sa, int sb, int sp) {
-        return sa * MT * A_TILE + sb * B_TILE + sp * P_STAGE + (3 * sa + 2 * sb + 2 * sp + 1) * 8 + 16 +
+        return sa * MT * A_TILE + sb * B_TILE + sp * P_STAGE + (3 * sa + 2 * sb + 2 * sp + 2) * 8 + 16 +
                1024;   // + slack to align the base to 1024 B
     }
 };
@@ -230,6 +230,30 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Split-K hand-over: a 32 x 32 block of accumulator values (one row per lane) as 8 swizzled
+// 16-byte chunks per lane.  store_xfer writes it to this CTA's shared memory, add_xfer adds the
+// block found at a shared::cluster address (the peer CTA's copy) to v.
+__device__ __forceinline__ void store_xfer(uint32_t base, int lane, const uint32_t (&v)[32]) {
+#pragma unroll
+    for (int q = 0; q < 8; q++)
+        sts128(base + lane * 128 + (((uint32_t)q ^ ((uint32_t)lane & 7u)) << 4),
+               make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+}
+__device__ __forceinline__ void add_xfer(uint32_t cluster_base, int lane, uint32_t (&v)[32]) {
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+        float4 u;
+        asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
+                     : "=f"(u.x), "=f"(u.y), "=f"(u.z), "=f"(u.w)
+                     : "r"(cluster_base + lane * 128 + (((uint32_t)q ^ ((uint32_t)lane & 7u)) << 4))
+                     : "memory");
+        v[4 * q] = __float_as_uint(__uint_as_float(v[4 * q]) + u.x);
+        v[4 * q + 1] = __float_as_uint(__uint_as_float(v[4 * q + 1]) + u.y);
+        v[4 * q + 2] = __float_as_uint(__uint_as_float(v[4 * q + 2]) + u.z);
+        v[4 * q + 3] = __float_as_uint(__uint_as_float(v[4 * q + 3]) + u.w);
+    }
+}
+
 // PCA table: pb[kb][j][t] = fp16(scales[kb][j] * bases[kb][32j + t] * 1024), 128 bytes per kb.
 // (The coefficient operand carries the matching 2^-10; the pre-scale keeps the products of
 // small scales and basis entries out of the fp16 subnormal range.)
@@ -260,7 +284,10 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
 
 
 // G = decode groups: the 16 decode warps form G groups of 16/G warps that take every G-th stage.
-template <int MT, int BN, int PAIR, int G>
+// KS = 2 (one-CTA tiles only): a cluster of two CTAs shares one output tile, each taking half of
+// the K range; CTA 1 hands its accumulator to CTA 0 through distributed shared memory.  For
+// small M, where there are fewer tiles than SMs and decoding the weights bounds the time.
+template <int MT, int BN, int PAIR, int G, int KS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap,
                const __grid_constant__ CUtensorMap wmap, Params p) {
@@ -268,6 +295,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     constexpr int kGroupWarps = kDecodeWarps / G;
     constexpr int B_TILE = C::B_TILE, P_SLAB = C::P_SLAB, P_STAGE = C::P_STAGE, TILES = C::TILES, BNU = C::BNU;
     static_assert(MT * BNU <= 512, "accumulators exceed tensor memory");
+    static_assert(KS == 1 || PAIR == 1, "split-K is for one-CTA tiles");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int SA = p.sa, SB = p.sb, SP = p.sp;
@@ -278,17 +306,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     const uint32_t p_full = b_empty + 8 * SB, p_empty = p_full + 8 * SP;
     const uint32_t acc_full = p_empty + 8 * SP;
     const uint32_t a_peer = acc_full + 8;        // leader only: the peer CTA's X tiles have landed
-    const uint32_t tmem_slot = a_peer + 8 * SA;
+    const uint32_t xfer_full = a_peer + 8 * SA;   // KS == 2, CTA 0: the peer's accumulator is in its shared memory
+    const uint32_t tmem_slot = xfer_full + 8;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // PAIR == 2: the cluster is two consecutive CTAs along x; rank 0 leads (issues the MMAs).
     const int rank = (PAIR == 2) ? (int)(blockIdx.x & 1) : 0;
-    const int n0 = (int)(blockIdx.x / PAIR) * BNU;           // first accumulator column
+    const int krank = (KS == 2) ? (int)(blockIdx.x & 1) : 0;
+    const int n0 = (int)(blockIdx.x / (PAIR * KS)) * BNU;    // first accumulator column
     const int m0 = blockIdx.y * (128 * MT * PAIR);
     const int tile0 = (n0 + rank * BN) >> 4;                 // first 16-column tile this CTA decodes
-    const int n_ks = (p.n_cb + KB_STAGE - 1) / KB_STAGE;
+    const int n_ks_all = (p.n_cb + KB_STAGE - 1) / KB_STAGE;
+    const int ks_half = (n_ks_all + KS - 1) / KS;
+    const int ks0 = krank * ks_half;                         // first K stage of this CTA
+    const int n_ks = (KS == 2) ? max(0, min(ks_half, n_ks_all - ks0)) : n_ks_all;
 
     if (threadIdx.x == 0) {
+        mbar_init(xfer_full, kDecodeWarps);
         for (int s = 0; s < SA; s++) { mbar_init(a_full + 8 * s, 1); mbar_init(a_empty + 8 * s, 1); }
         for (int s = 0; s < SA; s++) mbar_init(a_peer + 8 * s, 1);
         for (int s = 0; s < SB; s++) { mbar_init(b_full + 8 * s, kGroupWarps * PAIR); mbar_init(b_empty + 8 * s, 1); }
@@ -307,7 +341,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if constexpr (PAIR == 2) cluster_sync_all();   // the peer's barriers exist before anyone arrives on them
+    if constexpr (PAIR == 2 || KS == 2) cluster_sync_all();   // the peer's barriers exist before anyone arrives on them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = lds32(tmem_slot);
 
@@ -316,7 +350,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         bool ok = true;
         Ring rp(SP);
         for (int ks = 0; ks < n_ks; ks++) {
-            const int kb0 = ks * KB_STAGE;
+            const int kb0 = (ks0 + ks) * KB_STAGE;
             const int rows = min(KB_STAGE, p.n_cb - kb0);
             {   // packed slabs + PCA table: lane i < TILES copies tile i, lane 16 the table
                 const int s = rp.s;
@@ -355,7 +389,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 if (lane == 0) {
                     mbar_expect_tx(a_full + 8 * s, (uint32_t)(MT * A_TILE));
                     for (int mt = 0; mt < MT; mt++)
-                        tma_load_2d(sA + (s * MT + mt) * A_TILE, &xmap, ks * BK, m0 + (mt * PAIR + rank) * 128,
+                        tma_load_2d(sA + (s * MT + mt) * A_TILE, &xmap, (ks0 + ks) * BK, m0 + (mt * PAIR + rank) * 128,
                                     a_full + 8 * s);
                 }
                 __syncwarp();
@@ -439,7 +473,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         uint32_t pre_p = 0, pre_b = (rb.r == 0) ? 1u : 0u;   // answers of the early probes
         for (int ks = grp; ks < n_ks; ks += G) {
             const int sp = rp.s, sb = rb.s;
-            const int rows = min(KB_STAGE, p.n_cb - ks * KB_STAGE);
+            const int rows = min(KB_STAGE, p.n_cb - (ks0 + ks) * KB_STAGE);
             if (!pre_p && ok) ok = mbar_wait(p_full + 8 * sp, rp.r & 1, 0x100u);
             if (!pre_b && ok) ok = mbar_wait_t<PAIR == 2>(b_empty + 8 * sb, (rb.r - 1) & 1, 0x200u);
 #pragma unroll
@@ -534,8 +568,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         // bytes, 16-byte chunks XOR-swizzled with the row index (the Y tensor map's swizzle).
         // (the host checks that the X and operand stages together hold the 64 KB of staging)
         const uint32_t stg = sA + (uint32_t)dw * 4096u;
+        // Split-K: CTA 1 parks its accumulators in its (idle) X, operand and slab stages, 4 KB per
+        // (accumulator, 32-column chunk, lane quarter), and tells CTA 0; CTA 0 adds them in below.
+        uint32_t peer_xfer = 0;
+        auto xfer_off = [&](int mt, int c32) { return (uint32_t)(((mt * (BNU / 32) + c32) * 4 + quarter) * 4096); };
+        if constexpr (KS == 2) {
+            if (krank == 1) {
 #pragma unroll 1
-        for (int mt = 0; mt < MT; mt++) {
+                for (int mt = 0; mt < MT; mt++)
+#pragma unroll 1
+                    for (int c32 = part; c32 < BNU / 32; c32 += 4) {
+                        uint32_t v[32];
+                        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BNU + c32 * 32), v);
+                        store_xfer(sA + xfer_off(mt, c32), lane, v);
+                    }
+                asm volatile("fence.acq_rel.cluster;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cl(mapa_u32(xfer_full, 0u));
+            } else {
+                if (ok) ok = mbar_wait_cl(xfer_full, 0u, 0x2000u);
+                peer_xfer = mapa_u32(sA, 1u);
+            }
+        }
+#pragma unroll 1
+        for (int mt = 0; mt < ((KS == 2 && krank == 1) ? 0 : MT); mt++) {
             const int mrow0 = m0 + (mt * PAIR + rank) * 128 + quarter * 32;
             const long m = (long)mrow0 + lane;
             if (p.tma_store && p.out_f16) {
@@ -546,6 +602,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 const int col = c64 * 64;
                 tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BNU + col), v);
                 tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BNU + col + 32), w);
+                if constexpr (KS == 2) {
+                    add_xfer(peer_xfer + xfer_off(mt, 2 * c64), lane, v);
+                    add_xfer(peer_xfer + xfer_off(mt, 2 * c64 + 1), lane, w);
+                }
                 asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                 __syncwarp();
                 uint32_t h[32];
@@ -573,6 +633,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                     const int col = c32 * 32;
                     uint32_t v[32];
                     tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BNU + col), v);
+                    if constexpr (KS == 2) add_xfer(peer_xfer + xfer_off(mt, c32), lane, v);
                     if (p.tma_store) {
                         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // staging free again
                         __syncwarp();
@@ -612,7 +673,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     __syncthreads();
     // PAIR == 2: neither CTA may free its tensor memory or leave (its shared memory is read by
     // the pair's MMAs and its barriers are arrived on remotely) before both are done.
-    if constexpr (PAIR == 2) cluster_sync_all();
+    if constexpr (PAIR == 2 || KS == 2) cluster_sync_all();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if constexpr (PAIR == 2)
@@ -670,7 +731,7 @@ bool make_ymap(CUtensorMap* map, void* y, int M, int N, int out_f16) {
     return r == CUDA_SUCCESS;
 }
 
-template <int MT, int BN, int PAIR, int G = 2>
+template <int MT, int BN, int PAIR, int G = 2, int KS = 1>
 int launch_tc_bn(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
     CUtensorMap ymap;
     memset(&ymap, 0, sizeof(ymap));
@@ -702,7 +763,7 @@ int launch_tc_bn(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        e = cudaFuncSetAttribute(tc::gemm_tc_kernel<MT, BN, PAIR, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(tc::gemm_tc_kernel<MT, BN, PAIR, G, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  tc::kSmemMax);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemm_tc smem)");
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
@@ -721,7 +782,12 @@ int launch_tc_bn(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
             return SX8_E_CUDA;
         }
     }
-    dim3 grid((unsigned)(PAIR * ((p.N + C::BNU - 1) / C::BNU)),
+    // (the hand-over may run on from the X and operand stages into the slab stages: all idle by then)
+    if (KS == 2 && p.sa * MT * tc::A_TILE + p.sb * C::B_TILE + p.sp * C::P_STAGE < MT * C::BNU * 512) {
+        set_error("sx8_gemm: split-K hand-over does not fit the pipeline stages");
+        return SX8_E_UNSUPPORTED;
+    }
+    dim3 grid((unsigned)(PAIR * KS * ((p.N + C::BNU - 1) / C::BNU)),
               (unsigned)((p.M + 128 * MT * PAIR - 1) / (128 * MT * PAIR)), 1);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -730,12 +796,12 @@ int launch_tc_bn(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = PAIR;
+    attr[0].val.clusterDim.x = PAIR * KS;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = (PAIR == 2) ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, tc::gemm_tc_kernel<MT, BN, PAIR, G>, map, ymap, wmap, p);
+    cfg.numAttrs = (PAIR * KS == 2) ? 1 : 0;
+    e = cudaLaunchKernelEx(&cfg, tc::gemm_tc_kernel<MT, BN, PAIR, G, KS>, map, ymap, wmap, p);
     if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(gemm_tc_kernel)");
     return SX8_OK;
 }
@@ -748,8 +814,15 @@ int launch_tc(const CUtensorMap& map, const tc::Params& p, cudaStream_t stream) 
     const long mtiles = (p.M + 128 * MT - 1) / (128 * MT);
     int bn = 256;
     if (((p.N + 127) / 128) * mtiles <= 148) bn = 128;
-    if (bn == 128 && ((p.N + 63) / 64) * mtiles <= 148 && ((p.N + 127) / 128) * mtiles <= 37) bn = 64;
+    // Split-K over a cluster of two when the 128-column tiles leave at least half of the SMs
+    // idle (74 two-SM clusters fit at once) and K is long enough to halve: 9472 x 2560 at
+    // M = 128 runs in 28.8 us against 35.0, 2560 x 9728 in 61.7 against 86.4 with 64-column
+    // tiles (SX8_GEMM_KSPLIT=0 switches it off).
+    static const int ksplit = getenv("SX8_GEMM_KSPLIT") ? atoi(getenv("SX8_GEMM_KSPLIT")) : 1;
+    const bool can_split = ksplit && ((p.N + 127) / 128) * mtiles <= 74 && p.n_cb >= 32;
+    if (bn == 128 && !can_split && ((p.N + 63) / 64) * mtiles <= 148 && ((p.N + 127) / 128) * mtiles <= 37) bn = 64;
     if (force_bn == 64 || force_bn == 128 || force_bn == 256) bn = force_bn;
+    if (bn == 128 && can_split) return launch_tc_bn<MT, 128, 1, 2, 2>(map, p, stream);
     if (bn == 256) return launch_tc_bn<MT, 256, 1>(map, p, stream);
     if (bn == 128) return launch_tc_bn<MT, 128, 1>(map, p, stream);
     return launch_tc_bn<MT, 64, 1>(map, p, stream);

@@ -110,3 +110,21 @@ def test_empty_inputs():
     assert y.shape == (0, n)
     e = ops.embed(torch.empty(0, dtype=torch.long, device="cuda"), t["wt16"], t["bases"], t["scales"], k, n, t["n_cb"])
     assert e.shape == (0, k)
+
+
+@pytest.mark.parametrize("shape,M", [((2560, 9728), 128), ((2560, 9728), 256), ((4096, 2592), 100), ((1024, 2560), 33)])
+@pytest.mark.parametrize("f16out", [True, False])
+def test_gemm_split_k_cluster(shape, M, f16out):
+    """Few column tiles and M <= 256: two CTAs of a cluster share a tile, each taking half of K
+    (K = 2592 gives an odd number of 64-wide K stages, 21 + 20); the result is deterministic."""
+    import torch
+    from sx8_quantization_b200 import ops, _lib
+    n, k = shape
+    t, w = _tensor(n, k, 95)
+    x = _x(M, k, 13)
+    od = torch.float16 if f16out else torch.float32
+    y = ops.gemm(x, t["wt16"], t["bases"], t["scales"], n, k, t["n_cb"], out_dtype=od)
+    y2 = ops.gemm(x, t["wt16"], t["bases"], t["scales"], n, k, t["n_cb"], out_dtype=od)
+    assert torch.equal(y, y2)
+    assert _rel(y.float(), x.float() @ w.t()) <= (4e-3 if f16out else 3e-3)
+    assert _lib.device_error_flag() == 0
