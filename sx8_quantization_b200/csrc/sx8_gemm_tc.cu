@@ -523,6 +523,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                         // w = dmin + base * (...)   (fp16 pairs; base = (dmax-dmin)*0.25*0.015873*2^9)
                         float bAf = (h2f_bits((uint16_t)(H0 >> 16)) - h2f_bits((uint16_t)H0)) * kBase;
                         float bBf = (h2f_bits((uint16_t)(H1 >> 16)) - h2f_bits((uint16_t)H1)) * kBase;
+                        // A block whose range exceeds ~32000 (possible in the format, absent from real
+                        // weights) would overflow the fp16 step: move a factor 64 from it to the levels.
+                        // (What remains: the step is rounded to fp16 before the multiply, so a weight
+                        // within 0.05 % of the fp16 maximum, 65504, can still round to infinity.)
+                        if (bAf > 60000.0f) {
+                            bAf *= 0.015625f;
+                            wa.x = hfma2_u32(wa.x, 0x54005400u, 0u); wa.y = hfma2_u32(wa.y, 0x54005400u, 0u);
+                            wa.z = hfma2_u32(wa.z, 0x54005400u, 0u); wa.w = hfma2_u32(wa.w, 0x54005400u, 0u);
+                        }
+                        if (bBf > 60000.0f) {
+                            bBf *= 0.015625f;
+                            wb.x = hfma2_u32(wb.x, 0x54005400u, 0u); wb.y = hfma2_u32(wb.y, 0x54005400u, 0u);
+                            wb.z = hfma2_u32(wb.z, 0x54005400u, 0u); wb.w = hfma2_u32(wb.w, 0x54005400u, 0u);
+                        }
                         __half2 bA2 = __float2half2_rn(bAf), bB2 = __float2half2_rn(bBf);
                         uint32_t bA = *reinterpret_cast<uint32_t*>(&bA2), bB = *reinterpret_cast<uint32_t*>(&bB2);
                         uint32_t loA = dup_lo(H0), loB = dup_lo(H1);
