@@ -659,15 +659,18 @@ Choice choose(int N, int n_cb, int M) {
             }
         }
     }
-    // Large matrices (>= 48 MB packed; the 70B-class projections): four-tile groups with a
+    // Large matrices (>= 60 MB packed; the 70B-class projections): four-tile groups with a
     // 2- or 3-way split measured best (28672 x 8192: 78 us against 88; 8192 x 28672: 82 against
     // 85; 8192 x 8192: 27.9 against 29.9 for the rule above) unless N alone gives thousands of
     // groups (the lm_head rule above).
-    if (!f_nt && !f_split && (long)n_tiles * n_cb * T16_UNIT >= (48L << 20) && (n_tiles + 7) / 8 < 6 * kSMs) {
+    if (!f_nt && !f_split && (long)n_tiles * n_cb * T16_UNIT >= (60L << 20) && (n_tiles + 7) / 8 < 6 * kSMs) {
         int g4 = (n_tiles + 3) / 4;
         int nt = 4, sp = g4 <= 256 ? 3 : 2;
         if (M > 4) { nt = 8; sp = 3; }   // batch 5..8: the activation table costs more per CTA (94 us against 116)
-        best = Choice{nt, sp < min_split ? min_split : sp, 0};
+        if (sp < min_split) sp = min_split;
+        // only with enough tile groups to fill the GPU this way (the 55 MB shards of a 4-way
+        // tensor-parallel split ran 13 % slower with it than with the rule above)
+        if ((long)((n_tiles + nt - 1) / nt) * sp >= 256) best = Choice{nt, sp, 0};
     }
     int groups = (n_tiles + best.nt - 1) / best.nt;
     best.grid_x = groups;
