@@ -5,7 +5,7 @@ reference's own CUDA kernels compiled from where they lie into oracle/_ref/.
 TEST INFRASTRUCTURE ONLY -- nothing in the product package imports this.
 
     python oracle/build.py            # C oracle only
-    python oracle/build.py --ref      # also oracle/_ref (needs SX8_REF or /root/reference)
+    python oracle/build.py --ref      # also oracle/_ref (needs a reference checkout, see ref_root)
 """
 import os
 import subprocess

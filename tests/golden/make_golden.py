@@ -1,6 +1,6 @@
 """Generate the golden fixtures under tests/golden/ by running the REFERENCE's own
-code on CPU.  Run in a container that has the reference checkout (SX8_REF, default
-/root/reference); the fixtures it writes are committed, the reference is not.
+code on CPU.  Run where the reference checkout is (its path comes from SX8_REF); the
+fixtures it writes are committed, the reference is not.
 
 What is imported from the reference, unmodified:
   * scripts/quantize_qwen35_4b_sx8_v43_gpu.py -- the script touches a GPU and a model

@@ -1,5 +1,5 @@
 """Generate the file-format fixtures under tests/golden/ with the REFERENCE's own code
-(run where the reference checkout is; SX8_REF, default /root/reference):
+(run where the reference checkout is; its path comes from SX8_REF):
 
   small.sx8v43        two tensors of small_case.npz written by the reference's
                       scripts/sx8_container_v43.py:write_sx43 (from a temporary pkl).
