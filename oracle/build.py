@@ -6,6 +6,16 @@ TEST INFRASTRUCTURE ONLY -- nothing in the product package imports this.
 
     python oracle/build.py            # C oracle only
     python oracle/build.py --ref      # also oracle/_ref (needs a reference checkout, see ref_root)
+
+oracle/_ref/ receives compiled artefacts only, never source text:
+  <name>/<name>.so   the reference's four CUDA files built as torch extensions;
+  pyc/<module>.pyc   byte-compiled copies of the reference's Python callers and of its
+                     numba decoder (sourceless modules: importable, not readable), so that a
+                     GPU machine without the checkout can still run the reference's own
+                     SX8LinearV44 / decode_tensor_gpu_fast against this library;
+  pyc/ref_quantizer_funcs.pyc   the four pure functions of the reference's quantizer script
+                     (taken out of its syntax tree, because the script itself opens a model
+                     at import).
 """
 import os
 import subprocess
@@ -28,8 +38,16 @@ def build_oracle(force=False):
 
 
 def ref_root():
-    root = os.environ.get("SX8_REF", "/root/reference")
-    return root if os.path.isdir(os.path.join(root, "cuda")) else None
+    """Path of the reference checkout: $SX8_REF, else the `reference_path` that
+    BASELINE.json at the repository root records; None when neither exists."""
+    root = os.environ.get("SX8_REF")
+    if not root:
+        try:
+            import json
+            root = json.load(open(os.path.join(os.path.dirname(HERE), "BASELINE.json"))).get("reference_path")
+        except Exception:
+            root = None
+    return root if root and os.path.isdir(os.path.join(root, "cuda")) else None
 
 
 # name -> (cu file, C++ prototypes the reference's own wrapper declares, functions)
@@ -92,6 +110,78 @@ def build_ref(verbose=False):
     return built
 
 
+# Python modules of the reference that the caller-level parity tests import on the GPU box.
+_REF_PY = ["kernel_sx8_v43", "kernel_sx8_v4", "kernel_sx8_fused", "eval_common", "integrate_fused",
+           "integrate_fused_v44", "prepare_v44"]
+_REF_QUANT = "quantize_qwen35_4b_sx8_v43_gpu"
+_REF_QUANT_FUNCS = ("v6_encode_6bit_gpu", "chunked_v6_encode", "pca_correct_gpu", "pack_levels_6bit")
+PYC_DIR = os.path.join(REF_DIR, "pyc")
+
+
+def build_ref_py():
+    """Byte-compile the reference's caller modules from where they lie into oracle/_ref/pyc/
+    (sourceless .pyc files).  The quantizer script runs a model conversion at import, so only
+    its four pure functions are compiled, from its syntax tree, into ref_quantizer_funcs.pyc;
+    the importer supplies the module constants (DEV, B, L63, N_BASES, MAX_BLOCKS_PER_CHUNK)."""
+    import ast
+    import importlib.util
+    import marshal
+    import py_compile
+    root = ref_root()
+    if root is None:
+        raise RuntimeError("no reference checkout (set SX8_REF)")
+    os.makedirs(PYC_DIR, exist_ok=True)
+    done = []
+    for mod in _REF_PY:
+        src = os.path.join(root, "scripts", mod + ".py")
+        # dfile: the name recorded inside the code object (tracebacks), not a path of this machine
+        py_compile.compile(src, cfile=os.path.join(PYC_DIR, mod + ".pyc"), dfile="ref/scripts/" + mod + ".py",
+                           doraise=True)
+        done.append(mod)
+    tree = ast.parse(open(os.path.join(root, "scripts", _REF_QUANT + ".py")).read())
+    body = [n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name in _REF_QUANT_FUNCS]
+    if len(body) != len(_REF_QUANT_FUNCS):
+        raise RuntimeError("the reference quantizer no longer defines " + ", ".join(_REF_QUANT_FUNCS))
+    code = compile(ast.Module(body=body, type_ignores=[]), "ref/scripts/" + _REF_QUANT + ".py", "exec")
+    with open(os.path.join(PYC_DIR, "ref_quantizer_funcs.pyc"), "wb") as f:
+        f.write(importlib.util.MAGIC_NUMBER + b"\0" * 12)   # unchecked, no source: flags 0, mtime 0, size 0
+        f.write(marshal.dumps(code))
+    done.append("ref_quantizer_funcs")
+    return done
+
+
+def load_ref_py(module, alias=None):
+    """Import oracle/_ref/pyc/<module>.pyc under the name `alias` (default: module) without
+    touching sys.modules[module]; None when it was not staged."""
+    import importlib.machinery
+    import importlib.util
+    path = os.path.join(PYC_DIR, module + ".pyc")
+    if not os.path.exists(path):
+        return None
+    name = alias or module
+    loader = importlib.machinery.SourcelessFileLoader(name, path)
+    spec = importlib.util.spec_from_loader(name, loader)
+    mod = importlib.util.module_from_spec(spec)
+    loader.exec_module(mod)
+    return mod
+
+
+def load_ref_quantizer(device):
+    """The reference quantizer's four functions bound to `device` (a torch.device), with the
+    module constants the script defines beside them; None when not staged."""
+    import marshal
+    path = os.path.join(PYC_DIR, "ref_quantizer_funcs.pyc")
+    if not os.path.exists(path):
+        return None
+    import numpy as np
+    import torch
+    ns = dict(torch=torch, np=np, DEV=device, B=32, L63=63, N_BASES=4, MAX_BLOCKS_PER_CHUNK=3_000_000)
+    with open(path, "rb") as f:
+        f.read(16)
+        exec(marshal.loads(f.read()), ns)
+    return ns
+
+
 def load_ref(name):
     """Import a prebuilt reference extension from oracle/_ref (GPU box). Returns
     None when it was not built."""
@@ -110,3 +200,4 @@ if __name__ == "__main__":
     print(build_oracle(force="--force" in sys.argv))
     if "--ref" in sys.argv:
         print(build_ref(verbose="-v" in sys.argv))
+        print(build_ref_py())

@@ -18,13 +18,16 @@ int gemm_tc_launch(const void* x, int M, int K, long ldx, const void* wt16, cons
 
 __global__ void __launch_bounds__(256) f32_to_f16_kernel(const float* __restrict__ in, __half* __restrict__ out, long n) {
     long i = ((long)blockIdx.x * 256 + threadIdx.x) * 4;
-    if (i + 3 < n) {
+    // 8-byte stores only when `out` allows them (an f16 view at an odd element-pair offset is
+    // 4-byte aligned only); uniform over the grid
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(out) & 7) == 0;
+    if (i + 3 < n && vec_ok) {
         float4 v = *reinterpret_cast<const float4*>(in + i);
         __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
         uint2 o = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
         *reinterpret_cast<uint2*>(out + i) = o;
     } else {
-        for (; i < n; i++) out[i] = __float2half_rn(in[i]);
+        for (long e = i + 4 < n ? i + 4 : n; i < e; i++) out[i] = __float2half_rn(in[i]);
     }
 }
 }  // namespace sx8

@@ -24,6 +24,7 @@
 // phase completed long ago.
 // Every wait on an mbarrier is bounded; a wait that runs out sets the device error word and
 // the kernel drains and frees its TMEM.
+#include <atomic>
 #include <cuda.h>
 
 #include "sx8_common.cuh"
@@ -933,7 +934,7 @@ static __device__ __align__(256) unsigned char g_static_pca[kStaticPcaBytes];
 // In host code `g_static_pca` is only a handle for the runtime, not a device address:
 // the address is obtained per device with cudaGetSymbolAddress and cached.
 int static_pca_ptr(__half** out) {
-    static void* cache[64] = {};
+    static std::atomic<void*> cache[64] = {};   // written once per device, possibly from several host threads
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
@@ -941,13 +942,13 @@ int static_pca_ptr(__half** out) {
         set_error("sx8_gemm_static: device index %d out of range", dev);
         return SX8_E_UNSUPPORTED;
     }
-    if (!cache[dev]) {
-        void* ptr = nullptr;
+    void* ptr = cache[dev].load(std::memory_order_acquire);
+    if (!ptr) {
         e = cudaGetSymbolAddress(&ptr, g_static_pca);
         if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static PCA table)");
-        cache[dev] = ptr;
+        cache[dev].store(ptr, std::memory_order_release);   // every thread looks up the same address
     }
-    *out = (__half*)cache[dev];
+    *out = (__half*)ptr;
     return SX8_OK;
 }
 
@@ -966,12 +967,14 @@ extern "C" int sx8_gemm_static(const void* x, int M, int K, long ldx, const void
     SX8_REQUIRE(n_cb <= kStaticMaxNcb,
                 "sx8_gemm_static: n_cb=%d exceeds the built-in scratch (max n_cb %d, i.e. K <= %d); use sx8_gemm "
                 "with a caller workspace", n_cb, kStaticMaxNcb, kStaticMaxNcb * 32);
-    SX8_REQUIRE(ldx >= K && (ldx % 8) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0,
+    SX8_REQUIRE(ldx >= K, "sx8_gemm_static: ldx (%ld) < K (%d)", ldx, K);
+    SX8_REQUIRE((ldx % 8) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0,
                 "sx8_gemm_static: x must be 16-byte aligned with a row stride that is a multiple of 8 elements "
                 "(no scratch is available to stage it); got ldx=%ld", ldx);
     SX8_REQUIRE((reinterpret_cast<uintptr_t>(wt16) % 16) == 0 && (reinterpret_cast<uintptr_t>(bases) % 4) == 0 &&
+                    (reinterpret_cast<uintptr_t>(scales) % 4) == 0 &&
                     (reinterpret_cast<uintptr_t>(y) % (out_f16 ? 2 : 4)) == 0,
-                "sx8_gemm_static: misaligned wt16 / bases / y");
+                "sx8_gemm_static: misaligned wt16 / bases / scales / y");
     if (!encode_fn()) {
         set_error("sx8_gemm_static: the driver does not provide cuTensorMapEncodeTiled");
         return SX8_E_UNSUPPORTED;

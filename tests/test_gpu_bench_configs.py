@@ -1,0 +1,153 @@
+"""Every launch configuration that bench.py times, checked for values.
+
+The full result is compared with a float32 matmul on the library's own full-tensor decode
+(bit-exact against the oracle in test_gpu_parity.py), and a sample of >= 256 output columns
+with the CPU oracle itself (float64 decode of those rows + the reference's comparator, and the
+float32 restatement of the reference kernel's formula): the oracle would need minutes for all
+151,936 rows of the largest case.
+
+  * lm_head-sized GEMVs: N = 151936 (K = 2560) takes the no-split launch rule for thousands of
+    tile groups -- four-tile groups on a plain grid at batch <= 4, eight-tile groups on a
+    persistent grid at batch 8 -- and N = 128256 (K = 8192) the same rule with a long K;
+  * the tensor-core GEMM instantiations of the BASELINE prefill sizes: the gate projection at
+    M = 128 (76 one-CTA 128-column tiles, no split-K) and M = 512 (two-CTA tiles), and a
+    vocabulary-sized N at M = 32 and 256 (256-column one-CTA tiles);
+  * the PCA stage of the quantizer driver (functional parity with the reference algorithm).
+"""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+from oracle import sx8_oracle as orc  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+def _tensor(n, k, seed):
+    from sx8_quantization_b200 import ops, quantizer
+    t = quantizer.quantize_tensor(quantizer.synth_weight_gpu(n, k, seed), with_pca=True, keep_planes=True)
+    w = ops.dequant_t16(t["wt16"], t["bases"], t["scales"], n, k, t["n_cb"], True)
+    return t, w
+
+
+def _x(m, k, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return torch.randn(m, k, generator=g, device="cuda").half()
+
+
+def _rows_for_oracle(t, rows):
+    """qt / bases_info dicts (the reference's formats) of the given output rows only."""
+    p, n_cb = t["planes"], t["n_cb"]
+    r = torch.as_tensor(rows, device="cuda")
+    take = lambda a, per: a.reshape(t["N"], n_cb * per)[r].cpu().numpy().reshape(-1)
+    qt = {"shape": (len(rows), t["K"]), "n_blocks": len(rows) * n_cb, "n_cb": n_cb,
+          "dmin": take(p["dmin"].view(torch.int16), 1).view(np.float16), "dmax": take(p["dmax"].view(torch.int16), 1).view(np.float16),
+          "config": take(p["config"], 1), "levels_hi": take(p["levels_hi"], 16), "levels_lo": take(p["levels_lo"], 8),
+          "coeff": take(p["coeff"], 1).reshape(-1, 1)}
+    bi = {"n_cb": n_cb, "data": t["bases"].cpu().numpy(), "scales": t["scales"].cpu().numpy()}
+    return qt, bi
+
+
+def _check_against_oracle(y, x, t, n_sample=256, tol=2e-3, kernel_tol=None):
+    rng = np.random.default_rng(t["N"] + t["K"])
+    rows = np.sort(rng.choice(t["N"], size=min(n_sample, t["N"]), replace=False))
+    rows[0], rows[-1] = 0, t["N"] - 1                       # the first and the last tile always
+    qt, bi = _rows_for_oracle(t, rows)
+    xh = x.cpu().numpy()
+    ref = orc.matmul_ref(xh, orc.dequant_d64(qt, bi))       # the reference's comparator on those rows
+    got = y[:, torch.as_tensor(rows, device="cuda")].float().cpu().numpy()
+    scale = np.abs(ref).max()
+    assert np.isfinite(got).all()
+    assert np.abs(got - ref).max() <= tol * scale
+    if kernel_tol is not None:                              # float32 restatement of the reference kernel's formula
+        krn = orc.gemv_d32(xh, orc.to_v44(qt, bi))
+        assert np.abs(got - krn).max() <= kernel_tol * scale
+
+
+@pytest.mark.parametrize("shape,M", [((151936, 2560), 1), ((151936, 2560), 4), ((151936, 2560), 8),
+                                     ((128256, 8192), 1)])
+def test_gemv_lm_head_sizes(shape, M):
+    from sx8_quantization_b200 import ops, _lib
+    n, k = shape
+    t, w = _tensor(n, k, 400 + M)
+    x = _x(M, k, 17)
+    y = ops.gemv(x, t["wt16"], t["bases"], t["scales"], n, k, t["n_cb"])
+    ref = x.float() @ w.float().t()
+    assert (y - ref).abs().max().item() <= 2e-3 * ref.abs().max().item()
+    _check_against_oracle(y, x, t, kernel_tol=1e-4)
+    y2 = ops.gemv(x, t["wt16"], t["bases"], t["scales"], n, k, t["n_cb"])
+    assert torch.equal(y, y2)
+    assert _lib.device_error_flag() == 0
+
+
+@pytest.mark.parametrize("shape,M", [((9728, 2560), 128), ((9728, 2560), 512), ((4096, 2560), 128), ((2560, 9728), 512),
+                                     ((19456, 512), 32), ((19456, 512), 256), ((151936, 2560), 32)])
+@pytest.mark.parametrize("f16out", [True, False])
+def test_gemm_bench_instantiations(shape, M, f16out):
+    from sx8_quantization_b200 import ops, _lib
+    n, k = shape
+    t, w = _tensor(n, k, 410)
+    x = _x(M, k, 19)
+    od = torch.float16 if f16out else torch.float32
+    y = ops.gemm(x, t["wt16"], t["bases"], t["scales"], n, k, t["n_cb"], out_dtype=od)
+    ref = x.float() @ w.float().t()
+    tol = 3e-3 + (2.0 ** -10 if f16out else 0.0)            # weights are rounded to fp16 inside the GEMM
+    assert (y.float() - ref).abs().max().item() <= tol * ref.abs().max().item()
+    _check_against_oracle(y, x, t, tol=tol)
+    assert torch.equal(y, ops.gemm(x, t["wt16"], t["bases"], t["scales"], n, k, t["n_cb"], out_dtype=od))
+    assert _lib.device_error_flag() == 0
+
+
+def test_gemm_small_m_f16_output_at_an_odd_pair_offset():
+    """M < 32 with f16 output runs the GEMV passes and a conversion kernel; the output view here
+    starts 4 bytes into an allocation, so it is 4-byte but not 8-byte aligned."""
+    from sx8_quantization_b200 import ops
+    n, k, M = 272, 1024, 9
+    t, w = _tensor(n, k, 420)
+    x = _x(M, k, 21)
+    buf = torch.zeros(M * n + 2, dtype=torch.float16, device="cuda")
+    out = buf[2:].view(M, n)
+    assert out.data_ptr() % 8 == 4
+    ops.gemm(x, t["wt16"], t["bases"], t["scales"], n, k, t["n_cb"], out_dtype=torch.float16, out=out)
+    ref = x.float() @ w.float().t()
+    assert (out.float() - ref).abs().max().item() <= (2e-3 + 2.0 ** -10) * ref.abs().max().item()
+    assert buf[:2].abs().sum().item() == 0
+
+
+@pytest.mark.parametrize("shape", [(1024, 2560), (256, 1000)])
+def test_quantizer_pca_stage_functional_parity(shape):
+    """ref scripts/quantize_qwen35_4b_sx8_v43_gpu.py:75-142 against quantizer._pca_correct: the
+    singular vectors are only defined up to sign and LAPACK build, so the comparison is
+    functional -- reconstruction error after the correction no worse than 1.02 x the reference
+    algorithm's (the oracle's pca_correct on the same matrix), coefficients in the signed
+    4-bit range, orthonormal bases, and a real gain over no correction."""
+    from sx8_quantization_b200 import ops, quantizer
+    out_f, in_f = shape
+    w16 = orc.synth_weight(out_f, in_f, 77)
+    wd = torch.from_numpy(w16).cuda()
+    t = quantizer.quantize_tensor(wd, with_pca=True, keep_planes=True)
+    n_cb = t["n_cb"]
+    qt_o, bi_o = orc.quantize(w16, with_pca=True)
+    # the search stage is bit-exact, so both PCA stages start from the same levels
+    assert np.array_equal(t["planes"]["levels_hi"].cpu().numpy(), qt_o["levels_hi"])
+    w32 = w16.astype(np.float32)
+    mse = lambda W: float(((W.astype(np.float32)[:, :in_f] - w32) ** 2).mean())
+    qt_g, bi_g = quantizer.to_host_dicts(t)
+    e_ours = mse(orc.dequant_d64(qt_g, bi_g))
+    e_ref = mse(orc.dequant_d64(qt_o, bi_o))
+    e_none = mse(orc.dequant_d64(qt_o, bi_o, use_pca=False))
+    assert e_ours <= 1.02 * e_ref
+    assert e_ours < 0.99 * e_none
+    # the library's own decode of its own tensor agrees with the oracle's decode of it, bit for bit
+    W_lib = ops.dequant_t16(t["wt16"], t["bases"], t["scales"], out_f, in_f, n_cb, True).cpu().numpy()
+    assert np.array_equal(W_lib.view(np.uint16), orc.dequant_d64(qt_g, bi_g).view(np.uint16))
+    c = qt_g["coeff"].reshape(-1).astype(np.int16)
+    c0, c1 = c & 15, c >> 4
+    assert c0.max() <= 15 and c1.max() <= 15
+    s4 = lambda v: np.where(v < 8, v, v - 16)
+    assert s4(c0).min() >= -8 and s4(c0).max() <= 7 and s4(c1).min() >= -8
+    assert len(np.unique(s4(c0))) > 4                         # the range is used, not collapsed
+    B = bi_g["data"].reshape(n_cb, 2, 32).astype(np.float64)
+    gram = np.einsum("kit,kjt->kij", B, B)
+    assert np.abs(gram - np.eye(2)[None]).max() < 1e-4
+    assert (bi_g["scales"] > 0).all()
