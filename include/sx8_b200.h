@@ -162,10 +162,18 @@ int sx8_dequant_t16(const void* wt16, const float* bases, const float* scales, l
  * n_cb*32 columns.  Writes the n-major file planes dmin/dmax (f16), config, levels_hi,
  * levels_lo, and optionally the unpacked levels (n_blk, 32) u8 (may be NULL).
  * Bit-exact restatement of ref: scripts/quantize_qwen35_4b_sx8_v43_gpu.py:22-69
- * (v6_encode_6bit_gpu / chunked_v6_encode), :148-167 (pack_levels_6bit), :258-260.   */
+ * (v6_encode_6bit_gpu / chunked_v6_encode), :148-167 (pack_levels_6bit), :258-260.
+ * arith: the reference is torch eager code whose bits depend on torch's back end in two
+ * places (a tensor divided by the host scalar 63, and the summation order of the mean over
+ * 8 squared errors).  SX8_ARITH_TORCH_CUDA reproduces the reference as it runs -- on a GPU
+ * (ref :9 DEV = cuda) --, SX8_ARITH_TORCH_CPU the same functions run on torch CPU (the
+ * arithmetic of golden vectors made without a GPU).  The two differ in about 0.015 % of
+ * the levels.                                                                        */
+#define SX8_ARITH_TORCH_CUDA 0
+#define SX8_ARITH_TORCH_CPU 1
 int sx8_quantize_blocks(const void* w, int w_is_f16, long out_f, long in_f, long ldw,
                         void* dmin_f16, void* dmax_f16, uint8_t* config, uint8_t* levels_hi,
-                        uint8_t* levels_lo, uint8_t* levels_u8, void* stream);
+                        uint8_t* levels_lo, uint8_t* levels_u8, int arith, void* stream);
 
 /* ---- file planes -> device layout -------------------------------------------------
  * sx8_repack_t16 replaces ref: scripts/sx8_decode1_v3.py:57-66 (make_tensors_v44) /

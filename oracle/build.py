@@ -9,11 +9,11 @@ TEST INFRASTRUCTURE ONLY -- nothing in the product package imports this.
 
 oracle/_ref/ receives compiled artefacts only, never source text:
   <name>/<name>.so   the reference's four CUDA files built as torch extensions;
-  pyc/<module>.pyc   byte-compiled copies of the reference's Python callers and of its
+  pyc/<module>.bin   byte-compiled copies of the reference's Python callers and of its
                      numba decoder (sourceless modules: importable, not readable), so that a
                      GPU machine without the checkout can still run the reference's own
                      SX8LinearV44 / decode_tensor_gpu_fast against this library;
-  pyc/ref_quantizer_funcs.pyc   the four pure functions of the reference's quantizer script
+  pyc/ref_quantizer_funcs.bin   the four pure functions of the reference's quantizer script
                      (taken out of its syntax tree, because the script itself opens a model
                      at import).
 """
@@ -120,8 +120,8 @@ PYC_DIR = os.path.join(REF_DIR, "pyc")
 
 def build_ref_py():
     """Byte-compile the reference's caller modules from where they lie into oracle/_ref/pyc/
-    (sourceless .pyc files).  The quantizer script runs a model conversion at import, so only
-    its four pure functions are compiled, from its syntax tree, into ref_quantizer_funcs.pyc;
+    (sourceless byte code, stored as .bin: snapshot tools tend to drop *.pyc).  The quantizer script runs a model conversion at import, so only
+    its four pure functions are compiled, from its syntax tree, into ref_quantizer_funcs.bin;
     the importer supplies the module constants (DEV, B, L63, N_BASES, MAX_BLOCKS_PER_CHUNK)."""
     import ast
     import importlib.util
@@ -135,7 +135,7 @@ def build_ref_py():
     for mod in _REF_PY:
         src = os.path.join(root, "scripts", mod + ".py")
         # dfile: the name recorded inside the code object (tracebacks), not a path of this machine
-        py_compile.compile(src, cfile=os.path.join(PYC_DIR, mod + ".pyc"), dfile="ref/scripts/" + mod + ".py",
+        py_compile.compile(src, cfile=os.path.join(PYC_DIR, mod + ".bin"), dfile="ref/scripts/" + mod + ".py",
                            doraise=True)
         done.append(mod)
     tree = ast.parse(open(os.path.join(root, "scripts", _REF_QUANT + ".py")).read())
@@ -143,19 +143,45 @@ def build_ref_py():
     if len(body) != len(_REF_QUANT_FUNCS):
         raise RuntimeError("the reference quantizer no longer defines " + ", ".join(_REF_QUANT_FUNCS))
     code = compile(ast.Module(body=body, type_ignores=[]), "ref/scripts/" + _REF_QUANT + ".py", "exec")
-    with open(os.path.join(PYC_DIR, "ref_quantizer_funcs.pyc"), "wb") as f:
+    with open(os.path.join(PYC_DIR, "ref_quantizer_funcs.bin"), "wb") as f:
         f.write(importlib.util.MAGIC_NUMBER + b"\0" * 12)   # unchecked, no source: flags 0, mtime 0, size 0
         f.write(marshal.dumps(code))
     done.append("ref_quantizer_funcs")
     return done
 
 
+class RefFinder:
+    """sys.meta_path entry that resolves the reference's bare module names (`import
+    integrate_fused`, `from eval_common import ...`) to the byte code staged in
+    oracle/_ref/pyc/.  Names already in sys.modules (the drop-in modules registered by
+    sx8_quantization_b200.launch) never reach a finder, so they keep precedence."""
+
+    def find_spec(self, name, path=None, target=None):
+        import importlib.machinery
+        import importlib.util
+        if name not in _REF_PY:
+            return None
+        f = os.path.join(PYC_DIR, name + ".bin")
+        if not os.path.exists(f):
+            return None
+        return importlib.util.spec_from_loader(name, importlib.machinery.SourcelessFileLoader(name, f))
+
+
+def install_ref_finder():
+    """Make the staged reference modules importable by bare name; False when none are staged."""
+    if not os.path.exists(os.path.join(PYC_DIR, "integrate_fused_v44.bin")):
+        return False
+    if not any(isinstance(f, RefFinder) for f in sys.meta_path):
+        sys.meta_path.append(RefFinder())
+    return True
+
+
 def load_ref_py(module, alias=None):
-    """Import oracle/_ref/pyc/<module>.pyc under the name `alias` (default: module) without
+    """Import oracle/_ref/pyc/<module>.bin under the name `alias` (default: module) without
     touching sys.modules[module]; None when it was not staged."""
     import importlib.machinery
     import importlib.util
-    path = os.path.join(PYC_DIR, module + ".pyc")
+    path = os.path.join(PYC_DIR, module + ".bin")
     if not os.path.exists(path):
         return None
     name = alias or module
@@ -170,7 +196,7 @@ def load_ref_quantizer(device):
     """The reference quantizer's four functions bound to `device` (a torch.device), with the
     module constants the script defines beside them; None when not staged."""
     import marshal
-    path = os.path.join(PYC_DIR, "ref_quantizer_funcs.pyc")
+    path = os.path.join(PYC_DIR, "ref_quantizer_funcs.bin")
     if not os.path.exists(path):
         return None
     import numpy as np

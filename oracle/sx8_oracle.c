@@ -114,12 +114,20 @@ static inline int s4(int x) { return x < 8 ? x : x - 16; }
 /* ------------------------------------------------------------ quantizer search
  * scripts/quantize_qwen35_4b_sx8_v43_gpu.py:22-47 (v6_encode_6bit_gpu), torch
  * eager float32 semantics restated op by op: IEEE division, separate multiply
- * and add, round-half-even, strict '<' (lowest strategy wins ties), and the
- * mean over 8 as a left-to-right sum divided by 8 (torch CPU order).
+ * and add, round-half-even, strict '<' (lowest strategy wins ties).
+ * cuda_arith = 0: torch CPU -- (hi - lo) / 63 is an IEEE division and the mean over 8 a
+ *   left-to-right sum divided by 8 (pinned by the golden fixtures, which were made by
+ *   running the reference's functions on torch CPU).
+ * cuda_arith = 1: torch CUDA, the back end the reference script runs on (:9) -- a tensor
+ *   divided by the host scalar 63 is multiplied by float(1/63), and the mean over 8 is
+ *   the butterfly sum ((e0+e4)+(e2+e6)) + ((e1+e5)+(e3+e7)) times 1/8 (both observed on a
+ *   B200 against torch 2.11: 0 differences in 8M rows; pinned by the GPU test that runs the
+ *   reference's functions with DEV = cuda).
  * blocks: (n_blk, 32) f32.  Outputs: levels (n_blk,32) u8, dmin/dmax f32,
  * config i32.                                                                  */
-void sx8o_quant_search(const float* blocks, long n_blk, uint8_t* levels,
-                       float* dmin_out, float* dmax_out, int32_t* config_out) {
+void sx8o_quant_search2(const float* blocks, long n_blk, uint8_t* levels,
+                        float* dmin_out, float* dmax_out, int32_t* config_out, int cuda_arith) {
+    const float inv63 = 1.0f / 63.0f;
 #pragma omp parallel for schedule(static)
     for (long b = 0; b < n_blk; b++) {
         const float* x = blocks + b * 32;
@@ -141,10 +149,10 @@ void sx8o_quant_search(const float* blocks, long n_blk, uint8_t* levels,
             uint8_t best_lv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             for (int r = 0; r < 4; r++) {
                 float lo = slo[r], hi = shi[r];
-                float step = (hi - lo) / 63.0f;
+                float step = cuda_arith ? (hi - lo) * inv63 : (hi - lo) / 63.0f;
                 if (step < 1e-10f) step = 1e-10f;
                 uint8_t lv[8];
-                float sum = 0.0f;
+                float sq[8];
                 for (int i = 0; i < 8; i++) {
                     float c = rintf((s[i] - lo) / step);
                     if (c < 0.0f) c = 0.0f;
@@ -154,10 +162,18 @@ void sx8o_quant_search(const float* blocks, long n_blk, uint8_t* levels,
                     float prod = step * (float)ci;
                     float rec = lo + prod;
                     float e = s[i] - rec;
-                    float e2 = e * e;
-                    sum = sum + e2;
+                    sq[i] = e * e;
                 }
-                float mse = sum / 8.0f;
+                float mse;
+                if (cuda_arith) {
+                    float a = (sq[0] + sq[4]) + (sq[2] + sq[6]);
+                    float b2 = (sq[1] + sq[5]) + (sq[3] + sq[7]);
+                    mse = (a + b2) * 0.125f;
+                } else {
+                    float sum = 0.0f;
+                    for (int i = 0; i < 8; i++) sum = sum + sq[i];
+                    mse = sum / 8.0f;
+                }
                 if (mse < best) {
                     best = mse;
                     best_r = r;
@@ -171,6 +187,11 @@ void sx8o_quant_search(const float* blocks, long n_blk, uint8_t* levels,
         dmax_out[b] = dmax;
         config_out[b] = cfg;
     }
+}
+
+void sx8o_quant_search(const float* blocks, long n_blk, uint8_t* levels,
+                       float* dmin_out, float* dmax_out, int32_t* config_out) {
+    sx8o_quant_search2(blocks, n_blk, levels, dmin_out, dmax_out, config_out, 0);
 }
 
 /* scripts/quantize_qwen35_4b_sx8_v43_gpu.py:148-167 (pack_levels_6bit).

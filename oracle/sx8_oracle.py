@@ -78,16 +78,19 @@ def to_blocks(w):
     return np.ascontiguousarray(w.reshape(out_f * n_cb, 32)), n_cb
 
 
-def quant_search(blocks):
+def quant_search(blocks, arith="cpu"):
     """v6_encode_6bit_gpu (quantize...py:22-47) -> levels u8 (n_blk,32), dmin f32,
-    dmax f32, config i32."""
+    dmax f32, config i32.  arith: "cpu" = the function as torch CPU evaluates it (the golden
+    fixtures), "cuda" = as torch CUDA does (the back end the reference runs on); they differ in
+    the division by 63 and in the summation order of the mean (see sx8_oracle.c)."""
     blocks = _c(blocks, np.float32)
     n = blocks.shape[0]
     levels = np.empty((n, 32), np.uint8)
     dmin = np.empty(n, np.float32)
     dmax = np.empty(n, np.float32)
     cfg = np.empty(n, np.int32)
-    lib().sx8o_quant_search(_p(blocks), ctypes.c_long(n), _p(levels), _p(dmin), _p(dmax), _p(cfg))
+    lib().sx8o_quant_search2(_p(blocks), ctypes.c_long(n), _p(levels), _p(dmin), _p(dmax), _p(cfg),
+                             ctypes.c_int({"cpu": 0, "cuda": 1}[arith]))
     return levels, dmin, dmax, cfg
 
 
@@ -141,12 +144,12 @@ def pca_correct(levels, dmin, dmax, config, blocks, n_cb):
     return coeff, data, scales
 
 
-def quantize(w, with_pca=True):
+def quantize(w, with_pca=True, arith="cpu"):
     """Whole-tensor quantisation in the reference's order (quantize...py:235-272):
     search -> PCA -> fp16 endpoints -> pack.  Returns (qt, bi)."""
     out_f, in_f = w.shape
     blocks, n_cb = to_blocks(w)
-    levels, dmin, dmax, cfg = quant_search(blocks)
+    levels, dmin, dmax, cfg = quant_search(blocks, arith)
     if with_pca:
         coeff, data, scales = pca_correct(levels, dmin, dmax, cfg, blocks, n_cb)
     else:

@@ -142,9 +142,16 @@ embed_d32_kernel(const int64_t* __restrict__ ids, const uint8_t* __restrict__ bl
 
 // ------------------------------------------------------------------ quantizer search
 // ref scripts/quantize_qwen35_4b_sx8_v43_gpu.py:22-47, torch eager float32 semantics:
-// IEEE division, separately rounded multiply and add, round-half-even, strict '<'
-// with the lowest strategy winning ties, mean over 8 as a left-to-right sum / 8.
-template <bool F16IN>
+// IEEE division of tensor by tensor, separately rounded multiply and add, round-half-even,
+// strict '<' with the lowest strategy winning ties.  Two operations of that function give
+// different bits on torch's CUDA and CPU back ends, and the reference runs on CUDA (ref :9):
+//   (hi - lo) / 63     CUDA: multiplied by float(1/63) (a tensor divided by a host scalar is
+//                      turned into a multiplication by the reciprocal); CPU: IEEE division
+//   mean over 8        CUDA: butterfly sum ((e0+e4)+(e2+e6)) + ((e1+e5)+(e3+e7)), times 1/8;
+//                      CPU: left-to-right sum, divided by 8
+// Both orders were fixed by comparing against torch on a B200 (8M rows, 0 differences) and
+// against torch CPU.  CUDA_ARITH selects the first set (SX8_ARITH_TORCH_CUDA).
+template <bool F16IN, bool CUDA_ARITH>
 __global__ void __launch_bounds__(256)
 quantize_kernel(const void* __restrict__ w_, long out_f, long in_f, long ldw, int n_cb,
                 __half* __restrict__ dmin_o, __half* __restrict__ dmax_o,
@@ -206,8 +213,10 @@ quantize_kernel(const void* __restrict__ w_, long out_f, long in_f, long ldw, in
     for (int r = 0; r < 4; r++) {
         float lo = (r == 2) ? __fsub_rn(mx, q) : ((r == 3) ? __fadd_rn(mn, q) : mn);
         float hi = (r == 1) ? __fadd_rn(mn, q) : ((r == 3) ? __fsub_rn(mx, q) : mx);
-        float step = fmaxf(__fdiv_rn(__fsub_rn(hi, lo), 63.0f), 1e-10f);
-        float sum = 0.0f;
+        const float kInv63 = 1.0f / 63.0f;   // rounded to float32 once, as torch does on the host
+        float step = CUDA_ARITH ? fmaxf(__fmul_rn(__fsub_rn(hi, lo), kInv63), 1e-10f)
+                                : fmaxf(__fdiv_rn(__fsub_rn(hi, lo), 63.0f), 1e-10f);
+        float e2[8];
         uint32_t phi = 0, plo = 0;
 #pragma unroll
         for (int i = 0; i < 8; i++) {
@@ -216,11 +225,21 @@ quantize_kernel(const void* __restrict__ w_, long out_f, long in_f, long ldw, in
             int ci = (int)c;
             float rec = __fadd_rn(lo, __fmul_rn(step, (float)ci));
             float e = __fsub_rn(x[i], rec);
-            sum = __fadd_rn(sum, __fmul_rn(e, e));
+            e2[i] = __fmul_rn(e, e);
             phi |= (uint32_t)(ci >> 2) << (4 * i);
             plo |= (uint32_t)(ci & 3) << ((i >> 2) * 8 + (3 - (i & 3)) * 2);
         }
-        float mse = __fdiv_rn(sum, 8.0f);
+        float mse;
+        if (CUDA_ARITH) {
+            float a = __fadd_rn(__fadd_rn(e2[0], e2[4]), __fadd_rn(e2[2], e2[6]));
+            float b = __fadd_rn(__fadd_rn(e2[1], e2[5]), __fadd_rn(e2[3], e2[7]));
+            mse = __fmul_rn(__fadd_rn(a, b), 0.125f);
+        } else {
+            float sum = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) sum = __fadd_rn(sum, e2[i]);
+            mse = __fdiv_rn(sum, 8.0f);
+        }
         if (mse < best) {
             best = mse;
             best_r = r;
@@ -519,8 +538,10 @@ extern "C" int sx8_planes_from_blocks(const void* blocks, long n_blk, void* dmin
 
 extern "C" int sx8_quantize_blocks(const void* w, int w_is_f16, long out_f, long in_f, long ldw,
                                    void* dmin, void* dmax, uint8_t* config, uint8_t* hi, uint8_t* lo,
-                                   uint8_t* levels_u8, void* stream) {
+                                   uint8_t* levels_u8, int arith, void* stream) {
     SX8_REQUIRE(w && dmin && dmax && config && hi && lo, "sx8_quantize_blocks: null pointer");
+    SX8_REQUIRE(arith == SX8_ARITH_TORCH_CUDA || arith == SX8_ARITH_TORCH_CPU,
+                "sx8_quantize_blocks: arith must be SX8_ARITH_TORCH_CUDA (0) or SX8_ARITH_TORCH_CPU (1), got %d", arith);
     SX8_REQUIRE(out_f > 0 && in_f > 0 && ldw >= in_f, "sx8_quantize_blocks: need out_f>0, in_f>0, ldw>=in_f (got %ld, %ld, %ld)", out_f, in_f, ldw);
     SX8_REQUIRE(aligned(w, w_is_f16 ? 2 : 4) && aligned(hi, 4) && aligned(lo, 2) && aligned(dmin, 2) && aligned(dmax, 2) &&
                     (!levels_u8 || aligned(levels_u8, 8)),
@@ -529,10 +550,12 @@ extern "C" int sx8_quantize_blocks(const void* w, int w_is_f16, long out_f, long
     long threads = out_f * n_cb * 4;
     SX8_REQUIRE((threads + 255) / 256 <= 0x7FFFFFFFL, "sx8_quantize_blocks: tensor too large for one launch");
     unsigned grid = (unsigned)((threads + 255) / 256);
-    if (w_is_f16)
-        quantize_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(w, out_f, in_f, ldw, n_cb, (__half*)dmin, (__half*)dmax, config, hi, lo, levels_u8);
-    else
-        quantize_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(w, out_f, in_f, ldw, n_cb, (__half*)dmin, (__half*)dmax, config, hi, lo, levels_u8);
+#define SX8_QLAUNCH(F16, CU) quantize_kernel<F16, CU><<<grid, 256, 0, (cudaStream_t)stream>>>( \
+        w, out_f, in_f, ldw, n_cb, (__half*)dmin, (__half*)dmax, config, hi, lo, levels_u8)
+    const bool cu = arith == SX8_ARITH_TORCH_CUDA;
+    if (w_is_f16) { if (cu) SX8_QLAUNCH(true, true); else SX8_QLAUNCH(true, false); }
+    else          { if (cu) SX8_QLAUNCH(false, true); else SX8_QLAUNCH(false, false); }
+#undef SX8_QLAUNCH
     SX8_LAUNCH_CHECK("quantize_kernel");
     return SX8_OK;
 }

@@ -197,9 +197,15 @@ def dequant_t16(wt16, bases, scales, out_f, in_f, n_cb, use_pca=True):
     return out
 
 
-def quantize_blocks(w, want_levels=False):
+ARITH = {"cuda": 0, "cpu": 1}   # SX8_ARITH_TORCH_CUDA / SX8_ARITH_TORCH_CPU
+
+
+def quantize_blocks(w, want_levels=False, arith="cuda"):
     """Per-block search + packing of w (out_f,in_f) f16|f32 -> dict of n-major planes
-    (dmin, dmax f16; config, levels_hi, levels_lo u8 [, levels (n_blk,32) u8])."""
+    (dmin, dmax f16; config, levels_hi, levels_lo u8 [, levels (n_blk,32) u8]).
+    arith: "cuda" = the reference's bits as it runs on torch-CUDA, "cpu" = on torch CPU."""
+    if arith not in ARITH:
+        raise SX8Error("arith must be 'cuda' or 'cpu'")
     if w.dtype not in (torch.float16, torch.float32):
         raise SX8Error("w must be float16 or float32")
     if not w.is_cuda or w.dim() != 2 or w.stride(1) != 1:
@@ -217,7 +223,8 @@ def quantize_blocks(w, want_levels=False):
     with torch.cuda.device(dev):
         rc = _lib.lib().sx8_quantize_blocks(w.data_ptr(), int(w.dtype == torch.float16), out_f, in_f, w.stride(0),
                                             dmin.data_ptr(), dmax.data_ptr(), config.data_ptr(), hi.data_ptr(),
-                                            lo.data_ptr(), lv.data_ptr() if lv is not None else None, _stream(w))
+                                            lo.data_ptr(), lv.data_ptr() if lv is not None else None, ARITH[arith],
+                                            _stream(w))
     _lib.check(rc, "sx8_quantize_blocks")
     out = {"dmin": dmin, "dmax": dmax, "config": config, "levels_hi": hi, "levels_lo": lo,
            "n_cb": n_cb, "n_blocks": n_blk, "shape": (out_f, in_f)}

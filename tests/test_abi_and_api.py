@@ -46,7 +46,7 @@ def test_host_validation_rejects_before_any_launch():
     assert rc == -1 and b"null pointer" in L.sx8_last_error()
     rc = L.sx8_embed(None, 4, None, None, None, 32, 8, 1, None, None)
     assert rc == -1
-    rc = L.sx8_quantize_blocks(None, 1, 8, 32, 32, None, None, None, None, None, None, None)
+    rc = L.sx8_quantize_blocks(None, 1, 8, 32, 32, None, None, None, None, None, None, 0, None)
     assert rc == -1
 
 

@@ -127,7 +127,7 @@ def test_quantizer_pca_stage_functional_parity(shape):
     wd = torch.from_numpy(w16).cuda()
     t = quantizer.quantize_tensor(wd, with_pca=True, keep_planes=True)
     n_cb = t["n_cb"]
-    qt_o, bi_o = orc.quantize(w16, with_pca=True)
+    qt_o, bi_o = orc.quantize(w16, with_pca=True, arith="cuda")   # the driver searches in the torch-CUDA arithmetic
     # the search stage is bit-exact, so both PCA stages start from the same levels
     assert np.array_equal(t["planes"]["levels_hi"].cpu().numpy(), qt_o["levels_hi"])
     w32 = w16.astype(np.float32)

@@ -157,13 +157,16 @@ def test_embed_vs_reference_kernel_build(ops):
 
 @pytest.mark.parametrize("shape,f16", [((48, 80), True), ((64, 256), True), ((136, 1000), False),
                                        ((1024, 2560), True)])
-def test_quantize_bit_exact(ops, shape, f16):
+@pytest.mark.parametrize("arith", ["cpu", "cuda"])
+def test_quantize_bit_exact(ops, shape, f16, arith):
+    """Both arithmetics of the search (the reference's functions on torch CPU and on torch
+    CUDA): kernel against the oracle's restatement of the same one."""
     w = orc.synth_weight(shape[0], shape[1], 41)
     blocks, n_cb = orc.to_blocks(w)
-    lv, dmin, dmax, cfg = orc.quant_search(blocks)
+    lv, dmin, dmax, cfg = orc.quant_search(blocks, arith)
     hi, lo = orc.pack_levels(lv)
     wt = dev(w if f16 else w.astype(np.float32))
-    q = ops.quantize_blocks(wt, want_levels=True)
+    q = ops.quantize_blocks(wt, want_levels=True, arith=arith)
     assert np.array_equal(q["levels"].cpu().numpy(), lv)
     assert np.array_equal(q["dmin"].cpu().numpy().view(np.uint16), dmin.astype(np.float16).view(np.uint16))
     assert np.array_equal(q["dmax"].cpu().numpy().view(np.uint16), dmax.astype(np.float16).view(np.uint16))
@@ -174,7 +177,7 @@ def test_quantize_bit_exact(ops, shape, f16):
 
 def test_quantize_golden_small(ops, golden_dir):
     g = dict(np.load(os.path.join(golden_dir, "small_case.npz")))
-    q = ops.quantize_blocks(dev(g["w"]), want_levels=True)
+    q = ops.quantize_blocks(dev(g["w"]), want_levels=True, arith="cpu")   # the fixture was made on torch CPU
     assert np.array_equal(q["levels"].cpu().numpy(), g["levels"])
     assert np.array_equal(q["config"].cpu().numpy(), g["config"])
     assert np.array_equal(q["dmin"].cpu().numpy().view(np.uint16), g["dmin"].view(np.uint16))
@@ -193,7 +196,7 @@ def test_quantize_and_repack_golden_checksums(ops, name):
     c = CHK[name]
     w = orc.synth_weight(c["out_f"], c["in_f"], c["seed"])
     assert sha(w) == c["w"]
-    q = ops.quantize_blocks(dev(w), want_levels=True)
+    q = ops.quantize_blocks(dev(w), want_levels=True, arith="cpu")        # digests of the torch-CPU run
     assert sha(q["levels"].cpu().numpy()) == c["levels"]
     assert sha(q["dmin"].cpu().numpy()) == c["dmin"]
     assert sha(q["dmax"].cpu().numpy()) == c["dmax"]

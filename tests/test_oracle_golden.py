@@ -140,3 +140,21 @@ def test_pca_functional(small):
     e_raw = ((w_raw - w.astype(np.float64)) ** 2).mean()
     assert e_pca < e_raw
     assert np.allclose(np.linalg.norm(bi["data"].reshape(-1, 2, 32), axis=2), 1.0, atol=1e-4)
+
+
+def test_quant_search_torch_cuda_arithmetic_is_a_small_perturbation_of_the_cpu_one():
+    """The reference runs its search on torch CUDA, where a tensor divided by the scalar 63 is
+    multiplied by float(1/63) and the mean over 8 sums in butterfly order.  Without a GPU the
+    restatement of that arithmetic can only be checked for what it must share with the CPU one
+    (the GPU suite pins it against the reference's functions run with DEV = cuda)."""
+    w = orc.synth_weight(512, 2560, 12)
+    blocks, _ = orc.to_blocks(w)
+    a = orc.quant_search(blocks, "cpu")
+    b = orc.quant_search(blocks, "cuda")
+    assert np.array_equal(a[1], b[1]) and np.array_equal(a[2], b[2])      # dmin, dmax
+    frac = (a[0] != b[0]).mean()
+    assert 0 < frac < 1e-3                                                 # a few levels per 10,000
+    assert (a[3] != b[3]).mean() < 1e-3
+    assert np.abs(a[0].astype(int) - b[0].astype(int)).max() <= 1
+    c = orc.quant_search(blocks, "cuda")
+    assert np.array_equal(b[0], c[0])
