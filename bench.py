@@ -1,6 +1,7 @@
 """Benchmark of the S-X8 v4.3 hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --case gemv|gemm|embed|dequant|quantize --N .. --K .. --M ..   (one kernel, one shape)
 
 N = 1  workload `gemv_sweep_qwen3_4b` (BASELINE config 1): one step = the decode GEMVs of
        a whole Qwen3-4B-shaped model (36 distinct layers x {q,k,v,o,gate,up,down} +
@@ -280,24 +281,37 @@ def run_single(args):
     #      embedding rows, full-tensor decode -- short device-timed loops, reported as extras
     extras = {} if args.no_extras else other_kernels(dev, layers[0], head, fam)
 
-    # ---- e2e: the drop-in wrapper with pinned host buffers, copies inside the timed region
+    # ---- reference kernels on this GPU, beside ours
+    refk = None
+    if not args.no_extras:
+        try:
+            refk = ref_kernels_same_box(dev, fam, per_shape, extras.get("prefill_gemm", {}).get("gate_up_9728x2560", {}))
+        except Exception as e:  # the checker's kernels are optional evidence, never part of the product path
+            refk = {"unavailable": repr(e)[:300]}
+
+    # ---- e2e: the same sweep through the drop-in API (sx8_decode1_v3.decode1_v44, one call per
+    #      projection, eager launches), a decode step's data flow: every step its activations
+    #      come from pinned host memory (one copy per distinct input) and the step's result --
+    #      the lm_head logits of every batch -- is read back into pinned host memory.  The
+    #      projections' outputs stay on the device, as they do between the layers of a decoder.
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
     xh = {k: v.cpu().pin_memory() for k, v in xs.items()}
-    yh = {k: torch.empty(v.shape, dtype=torch.float32).pin_memory() for k, v in ys.items()}
     xd = {k: torch.empty_like(v) for k, v in xs.items()}
-    h2d = sum(xs[(M, t["K"])].numel() * 2 for M in BATCHES for _, t in mats)
-    d2h = sum(M * t["N"] * 4 for M in BATCHES for _, t in mats)
+    yh = {M: torch.empty(M, head["N"], dtype=torch.float32).pin_memory() for M in BATCHES}
+    h2d = sum(v.numel() * 2 for v in xs.values())
+    d2h = sum(v.numel() * 4 for v in yh.values())
+    stubs = [({"n_cb": t["n_cb"], "shape": (t["N"], t["K"])}, t) for _, t in mats]
 
     def e2e_step():
+        for k in xd:
+            xd[k].copy_(xh[k], non_blocking=True)
         for M in BATCHES:
-            for _, t in mats:
-                x = xd[(M, t["K"])]
-                x.copy_(xh[(M, t["K"])], non_blocking=True)
-                Y, _ = drop_in.decode1_v44(x, {"n_cb": t["n_cb"], "shape": (t["N"], t["K"])}, None, None,
-                                           t["wt16"], t["bases"], t["scales"], 6)
-                yh[(M, t["N"])].copy_(Y, non_blocking=True)
+            for q_, t in stubs:
+                Y, _ = drop_in.decode1_v44(xd[(M, t["K"])], q_, None, None, t["wt16"], t["bases"], t["scales"], 6)
+            yh[M].copy_(Y, non_blocking=True)        # the last matrix of a pass is lm_head
         torch.cuda.synchronize()
 
+    e2e_step()
     e2e_step()
     a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
@@ -318,10 +332,8 @@ def run_single(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 x u6 -> f32 accumulate",
         "data": "synthetic (random-init N(0,0.02) + 0.1% x10 outliers, quantised on the device)",
-        "config": {"workload": "gemv_sweep_qwen3_4b", "layers": n_layers, "batches": list(BATCHES),
-                   "matrices_per_pass": len(mats), "packed_bytes_per_pass": bytes_pass,
-                   "l2": "inputs larger than L2 (%.2f GB of distinct packed weights per pass)" % (bytes_pass / 1e9),
-                   "cuda_graph": not args.no_graph, "pdl": not args.no_pdl},
+        "config": workload_config("gemv_sweep_qwen3_4b", args, 1),
+        "launch": {"cuda_graph": not args.no_graph, "pdl": not args.no_pdl},
         "per_batch_GBps": {str(M): round(bytes_pass / (per_batch[M] * 1e-3) / 1e9, 1) for M in BATCHES},
         "tok_per_s_equiv_batch1": round(1e3 / per_batch[1], 1) if n_layers == fam["layers"] else None,
         "per_shape_batch1": per_shape,
@@ -337,10 +349,13 @@ def run_single(args):
                              % (peak_kind, NCU_TRAFFIC_RATIO)},
         "e2e": {"value": round(e2e_val, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps,
-                "api": "sx8_decode1_v3.decode1_v44 with pinned host x and y"},
+                "api": "sx8_decode1_v3.decode1_v44 per projection (eager, torch binding); per step: activations from "
+                       "pinned host memory, lm_head logits of every batch back to pinned host memory",
+                "binding": "torch extension" if _lib.ext() is not None else "ctypes"},
         "clocks": clocks,
         "fused_projections_batch1": fused,
         "other_kernels": extras,
+        "ref_kernels_same_box": refk,
         "e2e_decoder_qwen3_4b": None if (args.no_extras or args.no_decoder) else decoder_e2e(dev),
     }
     if not args.no_cpu:
@@ -386,25 +401,36 @@ def decoder_e2e(dev, prompt=512, new=256):
 
 
 def other_kernels(dev, layer0, head, fam):
-    """Prefill GEMM on the gate projection (M = 128 .. 8192, f16 out), quantizer search,
-    embedding gather and full-tensor decode; fractions are of the measured peaks."""
+    """Prefill GEMM over every distinct projection shape of the family at M = 128 .. 8192 (f16
+    out, BASELINE config 2), quantizer search, embedding gather and full-tensor decode;
+    fractions are of the measured peaks."""
     import torch
     from sx8_quantization_b200 import ops, quantizer
     out = {}
     pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(
-        os.path.join(ROOT, "MEASURED_PEAKS.json")) else {"bf16_tflops": 1590.0, "hbm_gbs": FALLBACK_HBM_GBS}
-    t = layer0["gate"]
+        os.path.join(ROOT, "MEASURED_PEAKS.json")) else {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+                                                         "hbm_gbs": FALLBACK_HBM_GBS}
     g = torch.Generator(device=dev).manual_seed(77)
     gem = {}
-    for M in (128, 512, 2048, 8192):
-        x = torch.randn(M, t["K"], generator=g, device=dev).half()
-        y = torch.empty(M, t["N"], dtype=torch.float16, device=dev)
-        us = _time_us(lambda: ops.gemm(x, t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"],
-                                       out_dtype=torch.float16, out=y))
-        tf = 2.0 * M * t["N"] * t["K"] / us / 1e6
-        gem[str(M)] = {"us": round(us, 1), "TFLOPs": round(tf, 1), "frac_of_bf16_burst": round(tf / pk["bf16_tflops"], 3)}
-        del x, y
-    out["prefill_gemm_gate_9728x2560"] = gem
+    shapes = [("q", layer0["q"]), ("k_v", layer0["k"]), ("o", layer0["o"]), ("gate_up", layer0["gate"]),
+              ("down", layer0["down"]), ("lm_head", head)]
+    for name, t in shapes:
+        row = {}
+        for M in (128, 512, 2048, 8192):
+            x = torch.randn(M, t["K"], generator=g, device=dev).half()
+            y = torch.empty(M, t["N"], dtype=torch.float16, device=dev)
+            us = _time_us(lambda: ops.gemm(x, t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"],
+                                           out_dtype=torch.float16, out=y), iters=5 if name == "lm_head" else 10)
+            tf = 2.0 * M * t["N"] * t["K"] / us / 1e6
+            row[str(M)] = {"us": round(us, 1), "TFLOPs": round(tf, 1), "frac_of_bf16_burst": round(tf / pk["bf16_tflops"], 3),
+                           "frac_of_bf16_sustained": round(tf / pk.get("bf16_tflops_sustained", pk["bf16_tflops"]), 3)}
+            if M == 128:   # the crossover: also as a fraction of HBM (packed weights + x + y)
+                by = tensor_bytes(t) + 2 * M * t["K"] + 2 * M * t["N"]
+                row[str(M)]["frac_of_hbm"] = round(by / us / 1e3 / pk["hbm_gbs"], 3)
+            del x, y
+        gem["%s_%dx%d" % (name, t["N"], t["K"])] = row
+    out["prefill_gemm"] = gem
+    t = layer0["gate"]
     w = quantizer.synth_weight_gpu(t["N"], t["K"], 4242, dev)
     us = _time_us(lambda: ops.quantize_blocks(w))
     n_blk = t["N"] * t["n_cb"]
@@ -422,6 +448,104 @@ def other_kernels(dev, layer0, head, fam):
     us = _time_us(lambda: ops.dequant_t16(t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"], True))
     out["dequant_gate"] = {"us": round(us, 1), "GBps": round(n_blk * (30 + 64) / us / 1e3, 1),
                            "frac_of_hbm": round(n_blk * (30 + 64) / us / 1e3 / pk["hbm_gbs"], 3)}
+    return out
+
+
+def ref_kernels_same_box(dev, fam, our_per_shape, our_gemm):
+    """The reference's own CUDA kernels, compiled unmodified for this GPU into oracle/_ref
+    (checker side; the package never loads them), timed beside this library's on the same
+    shapes: decode1_v44_combined (ref cuda/sx8_decode1_v3.cu:223-246) at M = 1 on the
+    projections of the sweep, rotating over more distinct copies than L2 holds, and gemm_compact
+    (ref cuda/sx8_gemm_compact.cu:171-194) / fused_forward (ref cuda/sx8_fused_wmma.cu:134-154)
+    on the gate projection.  None when oracle/_ref was not built."""
+    import torch
+    from oracle import build as obuild
+    from sx8_quantization_b200 import ops, quantizer
+    d1 = obuild.load_ref("ref_sx8_decode1_v3")
+    if d1 is None:
+        return None
+    out = {"decode1_v44_combined_batch1": {}, "note": "reference kernels built with nvcc -O3 for sm_100 from the reference's "
+           "sources, launched through their own pybind entry points; same CUDA-event timing, graph replay and "
+           "copy rotation as per_shape_batch1"}
+    g = torch.Generator(device=dev).manual_seed(5)
+    st = torch.cuda.Stream(device=dev)
+
+    def v44_of(N, K, seed):
+        t = quantizer.quantize_tensor(quantizer.synth_weight_gpu(N, K, seed, dev), with_pca=True, keep_planes=True)
+        p = t["planes"]
+        hdr, lev = ops.repack_v44(p["dmin"], p["dmax"], p["config"], p["coeff"], p["levels_hi"], p["levels_lo"], N, t["n_cb"], 6)
+        return t, hdr, lev
+
+    for name, N, K, _ in fam["proj"] + [("lm_head", fam["vocab"], fam["hidden"], "col")]:
+        if name in ("v", "up"):
+            continue
+        n_cb = K // 32
+        nbytes = 30 * N * n_cb
+        copies = 1 if nbytes > (200 << 20) else max(2, (300 << 20) // nbytes)
+        sets = []
+        for c in range(copies):
+            t, hdr, lev = v44_of(N, K, 7000 + c)
+            sets.append((hdr, lev, t["bases"], t["scales"]))
+            del t
+        x = torch.randn(K, generator=g, device=dev).half()
+        Z = torch.empty(n_cb, 2, device=dev)
+        Y = torch.empty(N, device=dev)
+        with torch.cuda.stream(st):
+            for hdr, lev, b, s_ in sets[:2]:
+                d1.decode1_v44_combined(x, hdr, lev, b, s_, n_cb, 6, Z, Y)
+            st.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=st):
+                for hdr, lev, b, s_ in sets:
+                    d1.decode1_v44_combined(x, hdr, lev, b, s_, n_cb, 6, Z, Y)
+            gr.replay(); st.synchronize()
+            a = torch.cuda.Event(enable_timing=True); e = torch.cuda.Event(enable_timing=True)
+            a.record(st)
+            for _ in range(5):
+                gr.replay()
+            e.record(st); st.synchronize()
+        us = a.elapsed_time(e) * 1e3 / (5 * len(sets))
+        ours = our_per_shape.get(name, {}).get("us_per_launch")
+        out["decode1_v44_combined_batch1"][name] = {
+            "N": N, "K": K, "ref_us_per_call": round(us, 3), "ref_GBps": round(nbytes / us / 1e3, 1),
+            "ours_us_per_launch": ours, "speedup": round(us / ours, 2) if ours else None, "resident_copies": len(sets),
+            "ref_launches_per_call": 2}
+        del sets
+        torch.cuda.empty_cache()
+    # prefill kernels on the gate projection
+    gc = obuild.load_ref("ref_sx8_gemm_compact")
+    wm = obuild.load_ref("ref_sx8_fused_wmma")
+    N, K = 9728, 2560
+    n_cb = K // 32
+    t, hdr, lev = v44_of(N, K, 7100)
+    p = t["planes"]
+    kbm = lambda a, per: a.reshape(N, n_cb, per).transpose(0, 1).contiguous().reshape(-1)
+    planar = (kbm(p["dmin"].view(torch.uint8), 2).view(torch.float16), kbm(p["dmax"].view(torch.uint8), 2).view(torch.float16),
+              kbm(p["config"], 1), kbm(p["coeff"], 1), kbm(p["levels_hi"], 16), kbm(p["levels_lo"], 8),
+              t["bases"].reshape(-1).contiguous(), t["scales"].reshape(-1).contiguous())
+    gem = {}
+    for M in (128, 2048):
+        x = torch.randn(M, K, generator=g, device=dev).half()
+        row = {}
+        if gc is not None:
+            def f_compact():
+                Zb = gc.compute_z44_batch(x, t["bases"], t["scales"], n_cb)
+                return gc.gemm_compact(x, hdr, lev, Zb, n_cb, 6)
+            us = _time_us(f_compact, iters=5, warm=2)
+            row["gemm_compact_us"] = round(us, 1)
+            row["gemm_compact_TFLOPs"] = round(2.0 * M * N * K / us / 1e6, 2)
+        if wm is not None:
+            torch.cuda.synchronize()
+            us = _time_us(lambda: wm.fused_forward(x, *planar, n_cb), iters=5, warm=2)   # launches on the legacy default stream
+            row["fused_wmma_us"] = round(us, 1)
+            row["fused_wmma_TFLOPs"] = round(2.0 * M * N * K / us / 1e6, 2)
+        ours = our_gemm.get(str(M), {}).get("us")
+        row["ours_us"] = ours
+        if ours:
+            best = min(v for k, v in row.items() if k.endswith("_us") and k != "ours_us" and v)
+            row["speedup_vs_best_ref"] = round(best / ours, 1)
+        gem[str(M)] = row
+    out["prefill_gate_9728x2560"] = gem
     return out
 
 
@@ -459,110 +583,265 @@ def cpu_baseline(budget_s=12.0):
                       "median of %d calls, %.1f ms per call" % (len(ts), med * 1e3)}
 
 
+def cpu_dequant_matmul(orc, qt, bi, x):
+    """One call of the reference's CPU comparator: full-tensor decode, then the fp32 matmul."""
+    import torch
+    W = torch.from_numpy(orc.dequant_d64(qt, bi))
+    return x.float() @ W.float().t()
+
+
 def run_reference(args):
-    """--impl reference: the reference's CPU path on the host cores (oracle port; the
-    reference has no CPU inference path of its own, its comparator is dequant + matmul)."""
+    """--impl reference: the reference's own CPU-runnable path for this workload -- its
+    comparator Y = X.float() @ decode(W).float().t() (ref scripts/sx8_decode1_v3.py:130-131),
+    decode by the oracle's C port of the reference decoder (OpenMP, all host cores), matmul by
+    torch on all host cores -- timed on the workload the other arm names.  A step is a bounded
+    sample of that workload: every distinct matrix shape of the model once (one layer's seven
+    projections, and lm_head for the sweep) at every batch size of the workload; no decoded
+    weight is kept between calls, as on the reference's fused path.  Rank 0 only."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    import numpy as np
+    import torch
+    from oracle import sx8_oracle as orc
+    from sx8_quantization_b200 import model_shapes as ms
+    n = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    torch.set_num_threads(os.cpu_count() or 1)
+    if n == 1:
+        fam, batches, wl = ms.QWEN3_4B, BATCHES, "gemv_sweep_qwen3_4b"
+        shapes = [(nm, N, K) for nm, N, K, _ in fam["proj"]] + [("lm_head", fam["vocab"], fam["hidden"])]
+    else:
+        fam, batches, wl = ms.LLAMA_70B, TP_BATCHES, "tp_decode_llama70b"
+        shapes = [(nm, N, K) for nm, N, K, _ in fam["proj"]]
+    mats = []
+    for i, (nm, N, K) in enumerate(shapes):
+        qt, bi = orc.quantize(orc.synth_weight(N, K, 100 + i), with_pca=False)
+        mats.append((nm, N, K, qt, bi))
+    xs = {(M, K): torch.from_numpy(orc.synth_x(M, K, 3 + M)) for M in batches for K in {k for _, _, k in shapes}}
+    bytes_step = sum(ms.packed_bytes(N, K) for _, N, K, _, _ in mats) * len(batches)
+
+    def step():
+        for M in batches:
+            for _, N, K, qt, bi in mats:
+                cpu_dequant_matmul(orc, qt, bi, xs[(M, K)])
+
     ts = []
     for i in range(args.warmup + args.steps):
-        c = cpu_baseline(budget_s=1.0)
+        t0 = time.perf_counter()
+        step()
         if i >= args.warmup:
-            ts.append(c["value"])
-    v = sum(ts) / len(ts)
-    c["value"] = round(v, 4)
-    n = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+            ts.append(time.perf_counter() - t0)
+    sec = sum(ts) / len(ts)
+    v = bytes_step / sec / 1e9
+    sample = ("per step: %s at batch %s, %d calls of C-oracle decode (OpenMP, %d threads) + torch fp32 matmul, "
+              "%.2f s; the full workload repeats these shapes over %d layers" %
+              (", ".join(nm for nm, *_ in mats), "/".join(str(b) for b in batches), len(mats) * len(batches),
+               orc.num_threads(), sec, fam["layers"]))
+    c = {"value": round(v, 4), "unit": "GB/s", "cores": os.cpu_count(), "kind": "port", "threads": orc.num_threads(),
+         "sample": sample}
     print(json.dumps({
         "impl": "reference", "metric": "sx8_decode_gemv_weight_GBps", "value": round(v, 4), "unit": "GB/s",
-        "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(30 * 9728 * 80 / (v * 1e9) * 1e3, 3),   # one call of the sample (gate projection)
-        "higher_is_better": True,
-        "scaling": "weak" if n == 1 else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "gemv_sweep_qwen3_4b" if n == 1 else "tp_decode_llama70b",
-                   "sample": c["sample"]},
+        "n_gpus": n, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 2),
+        "higher_is_better": True, "scaling": "weak" if n == 1 else "strong", "vs_baseline": None,
+        "dtype": "f64 decode -> f16 W, f32 matmul", "data": "synthetic",
+        "config": workload_config(wl, args, n),
         "cpu_baseline": c,
         "e2e": {"value": round(v, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
+def workload_config(wl, args, world):
+    """The `config` object of a workload: the same for both arms."""
+    from sx8_quantization_b200 import model_shapes as ms
+    if wl == "gemv_sweep_qwen3_4b":
+        fam = ms.QWEN3_4B
+        n_layers = args.layers if args.layers > 0 else fam["layers"]
+        bytes_pass = n_layers * ms.layer_bytes(fam) + ms.packed_bytes(fam["vocab"], fam["hidden"])
+        return {"workload": wl, "layers": n_layers, "batches": list(BATCHES),
+                "matrices_per_pass": n_layers * len(fam["proj"]) + 1, "packed_bytes_per_pass": bytes_pass,
+                "l2": "inputs larger than L2 (%.2f GB of distinct packed weights per pass)" % (bytes_pass / 1e9)}
+    fam = ms.LLAMA_70B
+    n_layers = args.layers if args.layers > 0 else TP_LAYERS
+    return {"workload": wl, "layers": n_layers, "batches": list(TP_BATCHES), "parallelism": "tp%d" % world,
+            "packed_bytes_per_layer": ms.layer_bytes(fam),
+            "l2": "per-rank weights %.0f MB of distinct layers (> L2)" % (n_layers * ms.layer_bytes(fam) / world / 1e6)}
+
+
 # ------------------------------------------------------------------------- N > 1
 
+TP_BATCHES = (1, 16)
+TP_LAYERS = 16
+TP_PREFILL = 2048
+
+
+def _graph_time(fn, st, steps, warm=3):
+    """CUDA-graph capture of fn() on stream st, then the mean replay time in ms (device events)."""
+    import torch
+    with torch.cuda.stream(st):
+        fn(); fn()
+        st.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=st):
+            fn()
+        for _ in range(warm):
+            gr.replay()
+        st.synchronize()
+        a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+        a.record(st)
+        for _ in range(steps):
+            gr.replay()
+        b.record(st)
+        st.synchronize()
+    return a.elapsed_time(b) / steps, gr
+
+
 def run_tp(args, rank, world, local_rank):
-    """Llama-70B-shaped tensor-parallel decode: q,k,v (column) -> o (row, all-reduce) ->
-    gate, up (column) -> down (row, all-reduce) per layer; every rank streams its shard.
-    Strong scaling: the model is fixed, the shard shrinks with N."""
+    """BASELINE config 4: Llama-70B-shaped layers as column/row tensor-parallel S-X8 linears.
+    A step is one decode pass through the resident layers and the vocabulary-sharded lm_head
+    at batch 1 and at batch 16 (tp.TPStack: column-parallel outputs feed the row-parallel
+    linears, two summed reductions per layer, logit shards gathered).  Strong scaling: the
+    model is fixed, the shard shrinks with N; rank 0 also times the unsharded stack (tp1) in
+    the same process.  Secondary figures: a 2048-token prefill pass through the GEMM + NCCL,
+    and the quantizer's throughput on the 70B shapes."""
     import torch
     import torch.distributed as dist
-    from sx8_quantization_b200 import ops, tp, model_shapes as ms
+    from sx8_quantization_b200 import ops, tp, quantizer, _lib, model_shapes as ms
     fam = ms.LLAMA_70B
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=dev)
-    n_layers = args.layers if args.layers > 0 else 4
-    # --emulate-world W on one GPU: time rank 0's shard of a W-way split without any exchange
-    shard_world = args.emulate_world if (world == 1 and args.emulate_world > 1) else world
-    layers = build_model(fam, n_layers, dev, with_pca=True, shard=(rank, shard_world))
-    batches = (1, 8)
-    g = torch.Generator(device=dev).manual_seed(5 + rank)
-    bytes_rank = sum(tensor_bytes(t) for L in layers for t in L.values())
-    xs, ys = {}, {}
-    for M in batches:
-        for L in layers[:1]:
-            for name, t in L.items():
-                xs[(M, name)] = torch.randn(M, t["K"], generator=g, device=dev).half()
-                ys[(M, name)] = torch.zeros(M, t["N"], dtype=torch.float32, device=dev)
-    ws = ops.Workspace.get(dev, max(t["n_cb"] for L in layers for t in L.values()) * 512)
+    n_layers = args.layers if args.layers > 0 else TP_LAYERS
+    H, V = fam["hidden"], fam["vocab"]
     flags = 0 if args.no_pdl else ops.SX8_F_PDL
+    st = torch.cuda.Stream(device=dev)
+
+    # ---- quantise the full matrices, keep this rank's shard (rank 0 keeps the full tensors too)
+    t_q0 = time.monotonic()
+    quant_blocks = 0
+    layers, full_layers = [], []
+    for li in range(n_layers):
+        sh, fu = {}, {}
+        for pi, (name, N, K, style) in enumerate(fam["proj"]):
+            w = quantizer.synth_weight_gpu(N, K, 1000 + li * 16 + pi, dev)
+            t = quantizer.quantize_tensor(w, with_pca=True)
+            del w
+            quant_blocks += N * t["n_cb"]
+            sh[name] = tp.shard_tensor(t, style, rank, world) if world > 1 else tp.shard_tensor(t, style, 0, 1)
+            if rank == 0 and world > 1 and not args.no_tp1:
+                fu[name] = tp.shard_tensor(t, style, 0, 1)
+        layers.append(sh)
+        full_layers.append(fu)
+    w = quantizer.synth_weight_gpu(V, H, 999, dev)
+    t_head = quantizer.quantize_tensor(w, with_pca=True)
+    del w
+    head = tp.shard_tensor(t_head, "col", rank, world) if world > 1 else tp.shard_tensor(t_head, "col", 0, 1)
+    full_head = tp.shard_tensor(t_head, "col", 0, 1) if (rank == 0 and world > 1 and not args.no_tp1) else None
+    torch.cuda.synchronize()
+    build_s = time.monotonic() - t_q0
+
+    # ---- quantizer throughput on the 70B shapes (search + PCA + layout, one tensor at a time)
+    quant = {}
+    for name, N, K in (("q_8192x8192", 8192, 8192), ("gate_28672x8192", 28672, 8192)):
+        w = quantizer.synth_weight_gpu(N, K, 4242, dev)
+        us_s = _time_us(lambda: ops.quantize_blocks(w), iters=3, warm=1)
+        us_f = _time_us(lambda: quantizer.quantize_tensor(w, with_pca=True), iters=2, warm=1)
+        nb = N * (K // 32)
+        quant[name] = {"search_Mblocks_per_s": round(nb / us_s, 1), "search_GBps_fp16_in": round(nb * 64 / us_s / 1e3, 1),
+                       "full_with_pca_Mblocks_per_s": round(nb / us_f, 1), "full_GBps_fp16_in": round(nb * 64 / us_f / 1e3, 1)}
+        del w
+    quant["note"] = ("per GPU; ranks quantise disjoint tensors of a model independently, so N GPUs give N times this; "
+                     "building this run's %d layers + lm_head (%.1f M blocks incl. weight generation) took %.1f s per rank"
+                     % (n_layers, quant_blocks / 1e6, build_s))
+    torch.cuda.empty_cache()
+
     exchange = None
-    if world > 1 and args.allreduce == "fused":
+    if world > 1 and args.allreduce in ("fused", "auto"):
         try:
-            exchange = tp.PeerExchange(8 * fam["hidden"], dev)
+            exchange = tp.PeerExchange(8 * H, dev)
         except Exception as e:
             if rank == 0:
                 print("peer exchange unavailable, using NCCL:", repr(e)[:300], file=sys.stderr)
-            exchange = None
+    g = torch.Generator(device=dev).manual_seed(5)           # same activations on every rank
+    x0 = {M: torch.randn(M, H, generator=g, device=dev).half() for M in TP_BATCHES + (TP_PREFILL,)}
 
-    def one_pass(M):
-        for L in layers:
-            for name, _, _, style in fam["proj"]:
-                t = L[name]
-                if style == "row" and world > 1:
-                    tp.linear(xs[(M, name)], t, out=ys[(M, name)], flags=flags, exchange=exchange)
-                else:
-                    ops.gemv(xs[(M, name)], t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"],
-                             out=ys[(M, name)], flags=flags, workspace=ws)
-
-    st = torch.cuda.Stream(device=dev)
-    graphs = {}
-    with torch.cuda.stream(st):
-        for M in batches:
-            one_pass(M)
-        st.synchronize()
-        if not args.no_graph:
-            try:
-                for M in batches:
-                    gr = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(gr, stream=st):
-                        one_pass(M)
-                    graphs[M] = gr
-            except Exception as e:  # NCCL capture unavailable: run eagerly and say so
-                graphs = {}
-                if rank == 0:
-                    print("graph capture failed, running eagerly:", repr(e)[:200], file=sys.stderr)
-
-    def step():
-        for M in batches:
-            if graphs:
-                graphs[M].replay()
+    # ---- correctness of the row-parallel reduction, before anything is timed: the o projection of
+    #      layer 0 three ways (fused exchange, NCCL, unsharded on rank 0), and one whole decode step
+    #      sharded vs unsharded
+    tp_check = None
+    if world > 1:
+        t_sh = layers[0]["o"]
+        k0, k1 = t_sh["k_range"]
+        xg = torch.randn(8, fam["proj"][3][2], generator=g, device=dev).half()
+        xl = xg[:, k0:k1].contiguous()
+        y_nccl = tp.linear(xl, t_sh, flags=0).clone()
+        y_fused = tp.linear(xl, t_sh, flags=0, exchange=exchange).clone() if exchange is not None else None
+        y_full = torch.empty_like(y_nccl)
+        if rank == 0:
+            if full_layers[0]:
+                tf = full_layers[0]["o"]
+                y_full = ops.gemv(xg, tf["wt16"], tf["bases"], tf["scales"], tf["N"], tf["K"], tf["n_cb"]).clone()
             else:
-                one_pass(M)
+                y_full.copy_(y_nccl)
+        dist.broadcast(y_full, 0)
+        sc = y_full.abs().max()
+        rel = lambda a: float(((a - y_full).abs().max() / sc).item())
+        chk = torch.tensor([rel(y_nccl), rel(y_fused) if y_fused is not None else 0.0,
+                            float(((y_fused - y_nccl).abs().max() / sc).item()) if y_fused is not None else 0.0],
+                           device=dev, dtype=torch.float64)
+        dist.all_reduce(chk, op=dist.ReduceOp.MAX)
+        tp_check = {"nccl_vs_unsharded": chk[0].item(), "fused_vs_unsharded": chk[1].item() if exchange is not None else None,
+                    "fused_vs_nccl": chk[2].item() if exchange is not None else None,
+                    "what": "o projection of layer 0, batch 8: max |diff| / max |y| over all ranks"}
+
+    def make_stack(M, lay, hd, ex):
+        return tp.TPStack(lay, hd, H, M, dev, exchange=ex, flags=flags)
+
+    def time_stack(stack, M, steps):
+        stack.reset(x0[M])
+        def fn():
+            stack.step()
+        return _graph_time(fn, st, steps)
+
+    # ---- tp1 on rank 0 alone (same layers, same process), before the sharded runs
+    tp1 = {}
+    if world > 1 and rank == 0 and not args.no_tp1:
+        for M in TP_BATCHES:
+            s1 = make_stack(M, full_layers, full_head, None)
+            s1.world = 1
+            ms1, gr = time_stack(s1, M, max(3, args.steps // 2))
+            tp1[M] = ms1
+            del gr, s1
+        torch.cuda.empty_cache()
+    if world > 1:
+        dist.barrier()
+
+    # ---- choose the reduction: fused peer-memory exchange or NCCL, whichever replays faster at batch 1
+    choice, trial = "nccl", {}
+    if world > 1 and exchange is not None:
+        if args.allreduce == "fused":
+            choice = "fused"
+        else:
+            for name, ex in (("nccl", None), ("fused", exchange)):
+                sT = make_stack(1, layers, head, ex)
+                m_, gr = time_stack(sT, 1, 5)
+                tt = torch.tensor([m_], device=dev, dtype=torch.float64)
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                trial[name] = round(float(tt.item()), 4)
+                del gr, sT
+            choice = "fused" if trial["fused"] < trial["nccl"] else "nccl"
+    stacks = {M: make_stack(M, layers, head, exchange if (choice == "fused" and M <= 8) else None) for M in TP_BATCHES}
+    graphs = {}
+    for M in TP_BATCHES:
+        stacks[M].reset(x0[M])
+        _, graphs[M] = _graph_time(lambda M=M: stacks[M].step(), st, 1, warm=1)
+    bytes_rank = stacks[TP_BATCHES[0]].packed_bytes
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
     with torch.cuda.stream(st):
         for _ in range(args.warmup):
-            step()
+            for M in TP_BATCHES:
+                graphs[M].replay()
         st.synchronize()
         torch.cuda.synchronize()
         if world > 1:
@@ -570,19 +849,16 @@ def run_tp(args, rank, world, local_rank):
         torch.cuda.synchronize()
         t0 = time.monotonic()
         e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-        eb = torch.cuda.Event(enable_timing=True)
+        eb = [torch.cuda.Event(enable_timing=True) for _ in range(len(TP_BATCHES) + 1)]
         e0.record(st)
         for k in range(args.steps):
-            if graphs:
-                graphs[batches[0]].replay()
-            else:
-                one_pass(batches[0])
-            if k == args.steps - 1:
-                eb.record(st)
-            if graphs:
-                graphs[batches[1]].replay()
-            else:
-                one_pass(batches[1])
+            last = k == args.steps - 1
+            if last:
+                eb[0].record(st)
+            for i, M in enumerate(TP_BATCHES):
+                graphs[M].replay()
+                if last:
+                    eb[i + 1].record(st)
         e1.record(st)
         st.synchronize()
         torch.cuda.synchronize()
@@ -591,23 +867,40 @@ def run_tp(args, rank, world, local_rank):
         torch.cuda.synchronize()
         t1 = time.monotonic()
     ms_local = e0.elapsed_time(e1) / args.steps
+    per_batch_ms = [eb[i].elapsed_time(eb[i + 1]) for i in range(len(TP_BATCHES))]
 
-    # ---- e2e: the same pass through the public tp.linear call, activations coming from pinned
-    #      host memory every step and the last projection's result read back
+    # ---- 2048-token prefill pass: GEMM linears, NCCL all-reduce after o and down, no lm_head
+    pre = make_stack(TP_PREFILL, layers, None, None)
+    pre.reset(x0[TP_PREFILL])
+    pre.step(); pre.step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(3):
+        pre.step()
+    b.record(); torch.cuda.synchronize()
+    prefill_ms = a.elapsed_time(b) / 3
+    del pre
+
+    # ---- e2e: the same step through the public API (tp.TPStack.step, eager), the step's input
+    #      activations coming from pinned host memory and the gathered logits read back
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
-    xh = {k: v.cpu().pin_memory() for k, v in xs.items()}
-    last = fam["proj"][-1][0]
-    yh = {M: torch.empty(M, layers[0][last]["N"], dtype=torch.float32).pin_memory() for M in batches}
-    h2d = sum(v.numel() * 2 for v in xs.values()) * n_layers
+    xh = {M: x0[M].cpu().pin_memory() for M in TP_BATCHES}
+    vloc = head["N"]
+    yh = {M: torch.empty(world, M, vloc, dtype=torch.float32).pin_memory() for M in TP_BATCHES}
+    h2d = sum(v.numel() * 2 for v in xh.values())
     d2h = sum(v.numel() * 4 for v in yh.values())
 
     def e2e_step():
-        for M in batches:
-            for L in layers:
-                for name, _, _, style in fam["proj"]:
-                    xs[(M, name)].copy_(xh[(M, name)], non_blocking=True)
-                    y = tp.linear(xs[(M, name)], L[name], out=ys[(M, name)], flags=flags, exchange=exchange)
-            yh[M].copy_(y, non_blocking=True)
+        for M in TP_BATCHES:
+            s_ = stacks[M]
+            s_.h.zero_()
+            s_.x.copy_(xh[M], non_blocking=True)
+            out = s_.step()
+            yh[M].view(-1).copy_(out.view(-1), non_blocking=True)
         torch.cuda.synchronize()
 
     e2e_step()
@@ -621,43 +914,64 @@ def run_tp(args, rank, world, local_rank):
     b.record(); torch.cuda.synchronize()
     e2e_ms = a.elapsed_time(b) / e2e_steps
 
-    tm = torch.tensor([ms_local, e2e_ms], device=dev, dtype=torch.float64)
+    tm = torch.tensor([ms_local, e2e_ms, prefill_ms] + per_batch_ms, device=dev, dtype=torch.float64)
     tb = torch.tensor([float(bytes_rank)], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(tm, op=dist.ReduceOp.MAX)
         dist.all_reduce(tb, op=dist.ReduceOp.SUM)
-    ms_per_step = float(tm[0].item())
-    e2e_ms = float(tm[1].item())
-    bytes_step = float(tb.item()) * len(batches)
+    ms_per_step, e2e_ms, prefill_ms = float(tm[0].item()), float(tm[1].item()), float(tm[2].item())
+    per_batch_ms = [float(v) for v in tm[3:].tolist()]
+    bytes_step = float(tb.item()) * len(TP_BATCHES)
     value = bytes_step / (ms_per_step * 1e-3) / 1e9
+    flag = _lib.device_error_flag()
     if rank == 0:
         clocks = sampler.summary(t0, t1)
         sampler.stop()
         peak, peak_kind = peaks()
-        n_gemv = n_layers * len(fam["proj"]) * len(batches)
-        full_layer = ms.layer_bytes(fam)
-        from sx8_quantization_b200 import _lib
+        pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(
+            os.path.join(ROOT, "MEASURED_PEAKS.json")) else {"bf16_tflops": 1590.0}
+        launches_per_pass = {M: (n_layers * (7 if M <= 8 else 10) + 1) for M in TP_BATCHES}
+        layer_flops = 2.0 * TP_PREFILL * sum(N * K for _, N, K, _ in fam["proj"])
+        strong = None
+        if tp1:
+            t1ms = sum(tp1[M] for M in TP_BATCHES)
+            strong = {"tp1_ms_per_step": round(t1ms, 4), "speedup": round(t1ms / ms_per_step, 3),
+                      "efficiency": round(t1ms / ms_per_step / world, 3),
+                      "tp1_ms_by_batch": {str(M): round(tp1[M], 4) for M in TP_BATCHES},
+                      "note": "tp1 = the same layers and lm_head unsharded, timed on rank 0 alone in this process "
+                              "before the sharded run"}
+        cfg = workload_config("tp_decode_llama70b", args, world)
+        launch = {"allreduce": ("fused into the GEMV epilogue over peer memory (fp32, rank-ordered sum) at batch <= 8, NCCL above"
+                                if choice == "fused" else "nccl fp32 sum") + " after o and down; logits all-gather",
+                  "allreduce_trial_ms_batch1": trial or None, "cuda_graph": True, "pdl": not args.no_pdl}
         line = {
             "metric": "sx8_decode_gemv_weight_GBps", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16 x u6 -> f32 accumulate", "data": "synthetic (random-init, quantised on the device)",
-            "config": {"workload": "tp_decode_llama70b", "layers": n_layers, "batches": list(batches),
-                       "parallelism": "tp%d" % world if shard_world == world else "rank 0 of tp%d, no exchange" % shard_world,
-                       "allreduce": ("fused into the GEMV epilogue over peer memory (fp32, rank-ordered sum)"
-                                     if exchange is not None else "nccl fp32 sum") + " after o and down",
-                       "packed_bytes_per_layer": full_layer,
-                       "l2": "per-rank weights %.0f MB (> L2 when above 126 MB)" % (bytes_rank / 1e6),
-                       "cuda_graph": bool(graphs), "pdl": not args.no_pdl},
-            "tok_per_s_80_layers_equiv": round(1e3 / (ms_per_step / len(batches)) * n_layers / fam["layers"], 2),
-            "gpu_launches": n_gemv * args.steps,
-            "device_error_flag": _lib.device_error_flag(),
+            "config": cfg,
+            "launch": launch,
+            "decode": {str(M): {"ms_per_step": round(per_batch_ms[i], 4),
+                                "tok_per_s_%d_layers" % n_layers: round(M / per_batch_ms[i] * 1e3, 1),
+                                "tok_per_s_80_layers_equiv": round(M / per_batch_ms[i] * 1e3 * n_layers / fam["layers"], 2)}
+                       for i, M in enumerate(TP_BATCHES)},
+            "prefill_2048": {"ms_per_pass": round(prefill_ms, 3), "layers": n_layers,
+                             "tok_per_s_80_layers_equiv": round(TP_PREFILL / prefill_ms * 1e3 * n_layers / fam["layers"], 1),
+                             "TFLOPs_aggregate": round(layer_flops * n_layers / prefill_ms / 1e9, 1),
+                             "frac_of_bf16_burst_per_gpu": round(layer_flops * n_layers / prefill_ms / 1e9 / world / pk["bf16_tflops"], 3),
+                             "allreduce": "nccl fp32, 2 x %d MB per layer" % (TP_PREFILL * H * 4 >> 20)},
+            "quantizer_70b_shapes": quant,
+            "strong_scaling": strong,
+            "tp_check_max_rel": tp_check,
+            "gpu_launches": sum(launches_per_pass.values()) * args.steps,
+            "device_error_flag": flag,
             "roofline": {"bound": "hbm", "achieved": round(value / world, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(value / world / peak, 4), "traffic": None,
-                         "note": "per-GPU packed weight bytes / step wall time incl. all-reduces, of %s peak" % peak_kind},
+                         "note": "per-GPU packed weight bytes / step wall time incl. reductions and glue kernels, of %s peak" % peak_kind},
             "e2e": {"value": round(bytes_step / (e2e_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 3),
-                    "steps": e2e_steps, "api": "tp.linear per projection, pinned host activations, NCCL all-reduce"},
+                    "steps": e2e_steps, "api": "tp.TPStack.step (eager), input activations from pinned host memory, "
+                                               "gathered logits back to pinned host memory; reduction: " + choice},
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
@@ -672,6 +986,44 @@ def run_tp(args, rank, world, local_rank):
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(0)
+
+
+def run_case(args):
+    """--case: ONE kernel of the library on one synthetic tensor, a handful of launches, and its
+    CUDA-event time -- the command profilers are pointed at."""
+    import torch
+    from sx8_quantization_b200 import _lib, ops, quantizer
+    dev = torch.device("cuda:0")
+    N, K, M = args.N, args.K, args.M
+    w = quantizer.synth_weight_gpu(N, K, 3, device=dev)
+    g = torch.Generator(device=dev).manual_seed(4)
+    if args.case == "quantize":
+        fn = lambda: ops.quantize_blocks(w)
+        units, unit = N * ((K + 31) // 32), "blocks"
+    else:
+        t = quantizer.quantize_tensor(w, with_pca=True)
+        del w
+        n_cb = t["n_cb"]
+        x = torch.randn(M, K, generator=g, device=dev).half()
+        if args.case == "gemv":
+            y = torch.empty(M, N, dtype=torch.float32, device=dev)
+            fn = lambda: ops.gemv(x, t["wt16"], t["bases"], t["scales"], N, K, n_cb, out=y)
+            units, unit = N * n_cb * 30, "packed bytes"
+        elif args.case == "gemm":
+            y = torch.empty(M, N, dtype=torch.float16, device=dev)
+            fn = lambda: ops.gemm(x, t["wt16"], t["bases"], t["scales"], N, K, n_cb, out_dtype=torch.float16, out=y)
+            units, unit = 2 * M * N * K, "flop"
+        elif args.case == "embed":
+            ids = torch.randint(0, N, (M,), generator=g, device=dev)
+            fn = lambda: ops.embed(ids, t["wt16"], t["bases"], t["scales"], K, N, n_cb)
+            units, unit = M, "rows"
+        else:
+            fn = lambda: ops.dequant_t16(t["wt16"], t["bases"], t["scales"], N, K, n_cb, True)
+            units, unit = N * n_cb * 30, "packed bytes"
+    us = _time_us(fn, iters=args.iters, warm=args.warmup)
+    flag = _lib.device_error_flag()
+    print(json.dumps({"case": args.case, "N": N, "K": K, "M": M, "us_per_call": round(us, 2),
+                      "per_second": units / (us * 1e-6), "unit": unit + "/s", "device_error_flag": flag}))
 
 
 def _watchdog(seconds):
@@ -703,14 +1055,22 @@ def main():
     ap.add_argument("--no-decoder", action="store_true", help="skip the end-to-end decoder leg")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--e2e-steps", type=int, default=10)
-    ap.add_argument("--emulate-world", type=int, default=0,
-                    help="single GPU: run rank 0's shard of a W-way tensor-parallel split, no exchange")
-    ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
-                    help="row-parallel reduction: fused peer-memory exchange or NCCL")
+    ap.add_argument("--allreduce", default="auto", choices=["auto", "fused", "nccl"],
+                    help="row-parallel reduction: fused peer-memory exchange, NCCL, or whichever replays faster")
+    ap.add_argument("--no-tp1", action="store_true", help="N > 1: skip the unsharded run on rank 0")
+    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "embed", "dequant", "quantize"],
+                    help="time one kernel on one synthetic tensor (for profilers)")
+    ap.add_argument("--N", type=int, default=9728)
+    ap.add_argument("--K", type=int, default=2560)
+    ap.add_argument("--M", type=int, default=1)
+    ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--max-seconds", type=int, default=900, help="watchdog for the whole run")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     _watchdog(args.max_seconds)
+    if args.case:
+        args.warmup = min(args.warmup, 3)
+        return run_case(args)
     if args.impl == "reference":
         return run_reference(args)
     world = int(os.environ.get("WORLD_SIZE", "1"))

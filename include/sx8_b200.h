@@ -61,8 +61,9 @@ const char* sx8_last_error(void);
  * decode1_v44_combined) and, for M in 2..8, the small-M use of
  * ref: cuda/sx8_gemm_compact.cu:157-194.
  * workspace: sx8_gemv_workspace_bytes(n_cb, M) bytes of device scratch, 256-byte
- * aligned, private to this call until it completes on the stream (used to stage x when
- * K is not a multiple of 32 or x is not 16-byte aligned row by row).
+ * aligned, private to this call until it completes on the stream: used to stage x when
+ * K is not a multiple of 32 or x is not 16-byte aligned row by row (ldx a multiple of
+ * 8).  When x needs no staging the workspace is not touched and may be NULL.
  * flags: SX8_F_PDL launches with programmatic dependent launch so that the weight
  * prefetch overlaps the preceding kernel on the stream.
  * Requires n_cb <= 1024.                                                             */

@@ -1,4 +1,7 @@
-"""ctypes binding of libsx8b200.so (the C ABI declared in include/sx8_b200.h).
+"""Bindings of libsx8b200.so (the C ABI declared in include/sx8_b200.h): ctypes for every
+entry point, and -- for the calls a decode loop makes hundreds of times per token -- the thin
+torch extension _sx8_torch.so (csrc/sx8_torch_binding.cpp), which resolves device, stream and
+data pointers in C++.
 
 There is no fallback: if the shared library is missing the import of any kernel
 wrapper raises, and every non-zero status from the library becomes an exception."""
@@ -71,6 +74,28 @@ def lib():
             fn.argtypes = args
         _lib = l
     return _lib
+
+
+_ext = None
+_ext_tried = False
+
+
+def ext():
+    """The torch binding module, or None when it is not built or when SX8_LIB_PATH points the
+    ctypes binding at another build of the library (the extension is linked to the in-tree one)."""
+    global _ext, _ext_tried
+    if not _ext_tried:
+        _ext_tried = True
+        path = os.path.join(_HERE, "_sx8_torch.so")
+        if os.path.exists(path) and not os.environ.get("SX8_LIB_PATH") and os.environ.get("SX8_NO_TORCH_EXT") != "1":
+            import importlib.util
+            import torch  # noqa: F401  (libtorch must be loaded first)
+            lib()
+            spec = importlib.util.spec_from_file_location("_sx8_torch", path)
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            _ext = mod
+    return _ext
 
 
 def check(rc, what):

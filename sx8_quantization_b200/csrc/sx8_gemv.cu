@@ -741,6 +741,11 @@ extern "C" size_t sx8_gemv_workspace_bytes(int n_cb, int M) {
 }
 
 namespace sx8 {
+// x can be fetched by 16-byte bulk copies as it is: no staging copy, no workspace needed
+static inline bool x_direct(const void* x, int K, long ldx, int n_cb) {
+    return K == n_cb * 32 && (ldx % 8) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0;
+}
+
 // Shared by sx8_gemv and the 8-row passes of sx8_gemm.  Arguments already validated.
 int gemv_launch_ex(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
                    const float* scales, int N, int n_cb, float* y, void* workspace, unsigned flags,
@@ -758,7 +763,7 @@ int gemv_launch_ex(const void* x, int M, int K, long ldx, const void* wt16, cons
     const __half* xp = (const __half*)x;
     long ld = ldx;
     const int Kp = n_cb * 32;
-    if (K != Kp || (ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x) % 16) != 0) {
+    if (!x_direct(x, K, ldx, n_cb)) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)(((long)M * Kp + 255) / 256), 1, 1);
         cfg.blockDim = dim3(256, 1, 1);
@@ -826,7 +831,7 @@ int gemv_launch_multi(const void* x, int M, int K, long ldx, int count, const vo
     const __half* xp = (const __half*)x;
     long ld = ldx;
     const int Kp = n_cb * 32;
-    if (K != Kp || (ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x) % 16) != 0) {
+    if (!x_direct(x, K, ldx, n_cb)) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)(((long)M * Kp + 255) / 256), 1, 1);
         cfg.blockDim = dim3(256, 1, 1);
@@ -860,6 +865,18 @@ int gemv_launch_multi(const void* x, int M, int K, long ldx, int count, const vo
     return launch_gemv<2, 8, 4>(p, g0, flags, stream);
 }
 
+int gemv_workspace_check(const char* who, const void* x, int M, int K, long ldx, int n_cb, const void* workspace,
+                         size_t workspace_bytes) {
+    if (x_direct(x, K, ldx, n_cb)) return SX8_OK;
+    if (!workspace || workspace_bytes < sx8_gemv_workspace_bytes(n_cb, M) ||
+        (reinterpret_cast<uintptr_t>(workspace) % 256) != 0) {
+        set_error("%s: x needs a staging copy (K not a multiple of 32, or rows not 16-byte aligned): workspace must be "
+                  "256-byte aligned and hold %zu bytes (got %zu)", who, sx8_gemv_workspace_bytes(n_cb, M), workspace_bytes);
+        return SX8_E_WORKSPACE;
+    }
+    return SX8_OK;
+}
+
 int gemv_check(const char* who, const void* x, int M, int Mmax, int K, long ldx, const void* wt16,
                const float* bases, const float* scales, int N, int n_cb, const void* y) {
     SX8_REQUIRE(x && wt16 && bases && scales && y, "%s: null pointer", who);
@@ -882,12 +899,8 @@ extern "C" int sx8_gemv(const void* x, int M, int K, long ldx, const void* wt16,
                         size_t workspace_bytes, unsigned flags, void* stream) {
     int rc = gemv_check("sx8_gemv", x, M, SX8_GEMV_MAX_BATCH, K, ldx, wt16, bases, scales, N, n_cb, y);
     if (rc != SX8_OK) return rc;
-    if (!workspace || workspace_bytes < sx8_gemv_workspace_bytes(n_cb, M) ||
-        (reinterpret_cast<uintptr_t>(workspace) % 256) != 0) {
-        set_error("sx8_gemv: workspace must be 256-byte aligned and hold %zu bytes (got %zu)",
-                  sx8_gemv_workspace_bytes(n_cb, M), workspace_bytes);
-        return SX8_E_WORKSPACE;
-    }
+    rc = gemv_workspace_check("sx8_gemv", x, M, K, ldx, n_cb, workspace, workspace_bytes);
+    if (rc != SX8_OK) return rc;
     return gemv_launch(x, M, K, ldx, wt16, bases, scales, N, n_cb, y, workspace, flags, (cudaStream_t)stream);
 }
 
@@ -905,12 +918,8 @@ extern "C" int sx8_gemv_allreduce(const void* x, int M, int K, long ldx, const v
         SX8_REQUIRE(peers->data[q] && peers->flags[q] && (reinterpret_cast<uintptr_t>(peers->data[q]) % 16) == 0 &&
                         (reinterpret_cast<uintptr_t>(peers->flags[q]) % 4) == 0,
                     "sx8_gemv_allreduce: null or misaligned peer pointer for rank %d", q);
-    if (!workspace || workspace_bytes < sx8_gemv_workspace_bytes(n_cb, M) ||
-        (reinterpret_cast<uintptr_t>(workspace) % 256) != 0) {
-        set_error("sx8_gemv_allreduce: workspace must be 256-byte aligned and hold %zu bytes (got %zu)",
-                  sx8_gemv_workspace_bytes(n_cb, M), workspace_bytes);
-        return SX8_E_WORKSPACE;
-    }
+    rc = gemv_workspace_check("sx8_gemv_allreduce", x, M, K, ldx, n_cb, workspace, workspace_bytes);
+    if (rc != SX8_OK) return rc;
     return gemv_launch_ex(x, M, K, ldx, wt16, bases, scales, N, n_cb, y, workspace, flags, peers,
                           (cudaStream_t)stream);
 }
@@ -921,17 +930,14 @@ extern "C" int sx8_gemv_multi(const void* x, int M, int K, long ldx, int count, 
                               unsigned flags, void* stream) {
     SX8_REQUIRE(count >= 1 && count <= kMaxSeg, "sx8_gemv_multi: count must be in 1..%d (got %d)", kMaxSeg, count);
     SX8_REQUIRE(wt16 && bases && scales && N && y, "sx8_gemv_multi: null array");
+    int rc = SX8_OK;
     for (int i = 0; i < count; i++) {
-        int rc = gemv_check("sx8_gemv_multi", x, M, SX8_GEMV_MAX_BATCH, K, ldx, wt16[i], bases[i], scales[i], N[i],
+        rc = gemv_check("sx8_gemv_multi", x, M, SX8_GEMV_MAX_BATCH, K, ldx, wt16[i], bases[i], scales[i], N[i],
                             n_cb, y[i]);
         if (rc != SX8_OK) return rc;
     }
-    if (!workspace || workspace_bytes < sx8_gemv_workspace_bytes(n_cb, M) ||
-        (reinterpret_cast<uintptr_t>(workspace) % 256) != 0) {
-        set_error("sx8_gemv_multi: workspace must be 256-byte aligned and hold %zu bytes (got %zu)",
-                  sx8_gemv_workspace_bytes(n_cb, M), workspace_bytes);
-        return SX8_E_WORKSPACE;
-    }
+    rc = gemv_workspace_check("sx8_gemv_multi", x, M, K, ldx, n_cb, workspace, workspace_bytes);
+    if (rc != SX8_OK) return rc;
     return gemv_launch_multi(x, M, K, ldx, count, wt16, bases, scales, N, y, n_cb, workspace, flags,
                              (cudaStream_t)stream);
 }

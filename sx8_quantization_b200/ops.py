@@ -22,15 +22,22 @@ def _need(t, dtype, name):
 
 
 class Workspace:
-    """Grow-only device scratch buffers, one per (device, tag); the analogue of the
-    reference's pooled Z/Y buffers (ref scripts/sx8_decode1_v3.py:80-88)."""
+    """Grow-only device scratch buffers, one per (device, stream, tag); the analogue of the
+    reference's pooled Z/Y buffers (ref scripts/sx8_decode1_v3.py:80-88).  Calls on different
+    streams get different buffers (a workspace is private to a call until it completes on its
+    stream).  A buffer that is outgrown is kept alive, never freed: a CUDA graph captured
+    earlier may have its address baked in."""
     _bufs = {}
+    _retired = []
 
     @classmethod
     def get(cls, device, nbytes, tag="gemv"):
-        key = (device.index if device.index is not None else torch.cuda.current_device(), tag)
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        key = (idx, torch.cuda.current_stream(idx).cuda_stream, tag)
         b = cls._bufs.get(key)
         if b is None or b.numel() < nbytes:
+            if b is not None:
+                cls._retired.append(b)
             b = torch.empty(max(int(nbytes), 1 << 16), dtype=torch.uint8, device=device)
             cls._bufs[key] = b
         return b
@@ -44,6 +51,17 @@ def _wt(wt16, N, n_cb):
     return wt16
 
 
+_NO_WS = None
+
+
+def _no_workspace(device):
+    """Stand-in passed to the torch binding when a call needs no staging (never dereferenced)."""
+    global _NO_WS
+    if _NO_WS is None or _NO_WS.device != device:
+        _NO_WS = torch.empty(0, dtype=torch.uint8, device=device)
+    return _NO_WS
+
+
 def gemv(x, wt16, bases, scales, N, K, n_cb, out=None, flags=0, workspace=None):
     """y (M,N) f32 = x (M,K) f16 times the packed matrix (T16 blob); M in 1..8."""
     if x.dim() == 1:
@@ -53,20 +71,33 @@ def gemv(x, wt16, bases, scales, N, K, n_cb, out=None, flags=0, workspace=None):
     if x.stride(1) != 1 or x.stride(0) < x.shape[1]:
         x = x.contiguous()
     M = x.shape[0]
-    _wt(wt16, N, n_cb)
-    _need(bases, torch.float32, "bases"); _need(scales, torch.float32, "scales")
     if out is None:
         out = torch.empty((M, N), dtype=torch.float32, device=x.device)
-    else:
-        _need(out, torch.float32, "out")
-        if out.numel() != M * N:
-            raise SX8Error("out has %d elements, need %d" % (out.numel(), M * N))
+    if workspace is None:
+        # scratch is only used to stage activations that bulk copies cannot fetch as they are
+        if (K & 31) or (x.stride(0) & 7) or (x.data_ptr() & 15):
+            workspace = Workspace.get(x.device, _lib.lib().sx8_gemv_workspace_bytes(n_cb, M))
+    E = _lib.ext()
+    if E is not None:
+        try:
+            rc = E.gemv(x, wt16, bases, scales, N, K, n_cb, out, workspace if workspace is not None else _no_workspace(x.device),
+                        flags)
+        except RuntimeError as e:       # argument checks of the binding
+            raise SX8Error(str(e).split("\n")[0]) from None
+        if rc:
+            _lib.check(rc, "sx8_gemv")
+        return out
+    _wt(wt16, N, n_cb)
+    _need(bases, torch.float32, "bases"); _need(scales, torch.float32, "scales")
+    _need(out, torch.float32, "out")
+    if out.numel() != M * N:
+        raise SX8Error("out has %d elements, need %d" % (out.numel(), M * N))
     L = _lib.lib()
-    need = L.sx8_gemv_workspace_bytes(n_cb, M)
-    ws = workspace if workspace is not None else Workspace.get(x.device, need)
+    ws = workspace
     with torch.cuda.device(x.device):
         rc = L.sx8_gemv(x.data_ptr(), M, K, x.stride(0), wt16.data_ptr(), bases.data_ptr(), scales.data_ptr(),
-                        N, n_cb, out.data_ptr(), ws.data_ptr(), ws.numel(), flags, _stream(x))
+                        N, n_cb, out.data_ptr(), ws.data_ptr() if ws is not None else None,
+                        ws.numel() if ws is not None else 0, flags, _stream(x))
     _lib.check(rc, "sx8_gemv")
     return out
 
@@ -149,6 +180,15 @@ def gemm(x, wt16, bases, scales, N, K, n_cb, out_dtype=torch.float32, out=None):
     L = _lib.lib()
     need = L.sx8_gemm_workspace_bytes(M, N, n_cb)
     ws = Workspace.get(x.device, need, "gemm")
+    E = _lib.ext()
+    if E is not None:
+        try:
+            rc = E.gemm(x, wt16, bases, scales, N, K, n_cb, out, ws)
+        except RuntimeError as e:
+            raise SX8Error(str(e).split("\n")[0]) from None
+        if rc:
+            _lib.check(rc, "sx8_gemm")
+        return out
     with torch.cuda.device(x.device):
         rc = L.sx8_gemm(x.data_ptr(), M, K, x.stride(0), wt16.data_ptr(), bases.data_ptr(), scales.data_ptr(),
                         N, n_cb, out.data_ptr(), int(out_dtype == torch.float16), ws.data_ptr(), ws.numel(),
@@ -168,6 +208,15 @@ def embed(ids, wt16, bases, scales, K, N, n_cb, out=None):
         _need(out, torch.float16, "out")
         if out.numel() < T * K:
             raise SX8Error("out too small")
+    E = _lib.ext()
+    if E is not None:
+        try:
+            rc = E.embed(ids, wt16, bases, scales, K, N, n_cb, out)
+        except RuntimeError as e:
+            raise SX8Error(str(e).split("\n")[0]) from None
+        if rc:
+            _lib.check(rc, "sx8_embed")
+        return out
     with torch.cuda.device(ids.device):
         rc = _lib.lib().sx8_embed(ids.data_ptr(), T, wt16.data_ptr(), bases.data_ptr(), scales.data_ptr(),
                                   K, N, n_cb, out.data_ptr(), _stream(ids))

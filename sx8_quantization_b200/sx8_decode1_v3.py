@@ -59,29 +59,32 @@ def best_split_k(N, n_cb):
 _BUF = {}
 
 
-def _buf(key, shape, device):
+def _buf(N, M, device):
     """Pooled fp32 output buffers, as ref scripts/sx8_decode1_v3.py:80-88: the returned
-    Y aliases the pool and is overwritten by the next call with the same shape."""
-    key = (key, device.index)
+    Y aliases the pool and is overwritten by the next call with the same N (and batch).
+    Returns (Y (M,N), its row 0 as a 1-D view)."""
+    key = (N, M, device.index)
     b = _BUF.get(key)
-    if b is None or tuple(b.shape) != tuple(shape):
-        b = torch.empty(*shape, dtype=torch.float32, device=device)
-        _BUF[key] = b
+    if b is None:
+        y = torch.empty(M, N, dtype=torch.float32, device=device)
+        b = _BUF[key] = (y, y[0])
     return b
 
 
 def decode1_v44(X, qt, bases_info, hdr_t=None, lvl_t=None, bas_t=None, sca_t=None,
                 hdr_bytes=6, split_k=1):
-    """ref scripts/sx8_decode1_v3.py:91-110."""
+    """ref scripts/sx8_decode1_v3.py:91-110.  Launched with programmatic dependent launch: when
+    the previous kernel on the stream is another of this library's, the weight stream of this
+    call starts under its tail."""
     if lvl_t is None:
         hdr_t, lvl_t, bas_t, sca_t = make_tensors_v44(qt, bases_info, hdr_aligned=(hdr_bytes == 8),
                                                       device=X.device if X.is_cuda else None)
-    n_cb = int(qt["n_cb"])
-    N = int(qt["shape"][0])
-    Xc = X.contiguous().half()
-    one_d = Xc.dim() == 1
-    K = Xc.shape[-1]
-    M = 1 if one_d else Xc.shape[0]
-    Y = _buf(("Y", N, M), (M, N), Xc.device)
-    ops.gemv(Xc, lvl_t, bas_t, sca_t, N, min(K, n_cb * 32), n_cb, out=Y)
-    return (Y[0] if one_d else Y), (hdr_t, lvl_t, bas_t, sca_t)
+    n_cb = qt["n_cb"]
+    N = qt["shape"][0]
+    if X.dtype is not torch.float16 or not X.is_contiguous():
+        X = X.contiguous().half()
+    one_d = X.dim() == 1
+    K = X.shape[-1]
+    Y, Y0 = _buf(N, 1 if one_d else X.shape[0], X.device)
+    ops.gemv(X, lvl_t, bas_t, sca_t, N, K if K < n_cb * 32 else n_cb * 32, n_cb, out=Y, flags=ops.SX8_F_PDL)
+    return (Y0 if one_d else Y), (hdr_t, lvl_t, bas_t, sca_t)

@@ -117,3 +117,97 @@ def linear(x, t, out=None, flags=0, group=None, reduce=True, exchange=None):
     if row:
         torch.distributed.all_reduce(y, group=group)
     return y
+
+
+class TPStack:
+    """A stack of Llama-shaped decoder layers as tensor-parallel S-X8 linears, one rank's part:
+    per layer  x -> q|k|v (column) -> o (row, summed over ranks) -> residual + RMSNorm ->
+    gate|up (column) -> SiLU(gate)*up -> down (row, summed) -> residual + RMSNorm, then a
+    vocabulary-sharded lm_head whose logit shards are gathered.  Column-parallel outputs feed
+    the row-parallel linears directly, so every rank only ever holds its own slice of the
+    q / ffn activations.  Attention over a KV cache is not part of the S-X8 path and is stood
+    in for by a cast of the local q slice (the o projection then reads (M, n_q/world) values
+    as it would after attention).
+
+    M <= 8 runs the decode GEMV (q|k|v and gate|up as one launch each), larger M the GEMM.
+    layers: list of dicts name -> this rank's shard (shard_tensor); head: column shard or None.
+    exchange: a PeerExchange for the fused GEMV + all-reduce (M <= 8), else NCCL."""
+
+    def __init__(self, layers, head, hidden, M, device, group=None, exchange=None, flags=0, eps=1e-5):
+        self.layers, self.head, self.M, self.dev = layers, head, int(M), device
+        self.group, self.exchange, self.flags, self.eps = group, exchange, flags, eps
+        self.world = torch.distributed.get_world_size(group) if torch.distributed.is_initialized() else 1
+        o = layers[0]["o"]
+        if o.get("global") is None or o["global"][1] == o["K"]:     # unsharded tensors: one rank's whole model
+            self.world = 1
+        f16, f32 = dict(dtype=torch.float16, device=device), dict(dtype=torch.float32, device=device)
+        L0 = layers[0]
+        self.h = torch.zeros(M, hidden, **f32)                     # residual stream
+        self.x = torch.zeros(M, hidden, **f16)                     # normalised input of the next linear
+        self.gamma = torch.ones(hidden, **f32)
+        self.attn = torch.empty(M, L0["o"]["K"], **f16)
+        self.act = torch.empty(M, L0["down"]["K"], **f16)
+        self.y_o = torch.empty(M, hidden, **f32)
+        self.y_d = torch.empty(M, hidden, **f32)
+        self.multi = None
+        if M <= 8:
+            self.multi = [(ops.MultiGemv([L["q"], L["k"], L["v"]], M, device), ops.MultiGemv([L["gate"], L["up"]], M, device))
+                          for L in layers]
+        else:
+            self.q = torch.empty(M, L0["q"]["N"], **f32)
+            self.kv = torch.empty(M, L0["k"]["N"], **f32)
+            self.g = torch.empty(M, L0["gate"]["N"], **f32)
+            self.u = torch.empty(M, L0["up"]["N"], **f32)
+        self.logits_local = torch.empty(M, head["N"], **f32) if head is not None else None
+        self.logits = None
+        if head is not None and self.world > 1:
+            self.logits = torch.empty(self.world, M, head["N"], **f32)
+        self.packed_bytes = sum(30 * t["N"] * t["n_cb"] for L in layers for t in L.values()) + \
+            (30 * head["N"] * head["n_cb"] if head is not None else 0)
+
+    def _row(self, x, t, out):
+        return linear(x, t, out=out, flags=self.flags, group=self.group,
+                      exchange=self.exchange if self.world > 1 else None, reduce=self.world > 1)
+
+    def step(self):
+        """One pass over all layers from the current self.x / self.h; leaves the gathered logits
+        (world, M, vocab/world) in self.logits (self.logits_local when world == 1)."""
+        M = self.M
+        for i, L in enumerate(self.layers):
+            if self.multi is not None:
+                q, _, _ = self.multi[i][0](self.x, flags=self.flags)
+            else:
+                q = ops.gemm(self.x, L["q"]["wt16"], L["q"]["bases"], L["q"]["scales"], L["q"]["N"], L["q"]["K"],
+                             L["q"]["n_cb"], out=self.q)
+                for nm in ("k", "v"):
+                    ops.gemm(self.x, L[nm]["wt16"], L[nm]["bases"], L[nm]["scales"], L[nm]["N"], L[nm]["K"],
+                             L[nm]["n_cb"], out=self.kv)
+            self.attn.copy_(q)                                        # stand-in for attention over the cache
+            self._row(self.attn, L["o"], self.y_o)
+            ops.glue_add_rmsnorm(self.h, self.y_o, self.gamma, self.eps, self.x)
+            if self.multi is not None:
+                g, u = self.multi[i][1](self.x, flags=self.flags)
+            else:
+                g = ops.gemm(self.x, L["gate"]["wt16"], L["gate"]["bases"], L["gate"]["scales"], L["gate"]["N"],
+                             L["gate"]["K"], L["gate"]["n_cb"], out=self.g)
+                u = ops.gemm(self.x, L["up"]["wt16"], L["up"]["bases"], L["up"]["scales"], L["up"]["N"], L["up"]["K"],
+                             L["up"]["n_cb"], out=self.u)
+            ops.glue_silu_mul(g, u, self.act)
+            self._row(self.act, L["down"], self.y_d)
+            ops.glue_add_rmsnorm(self.h, self.y_d, self.gamma, self.eps, self.x)
+        if self.head is not None:
+            t = self.head
+            if M <= 8:
+                ops.gemv(self.x, t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"], out=self.logits_local,
+                         flags=self.flags)
+            else:
+                ops.gemm(self.x, t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"], out=self.logits_local)
+            if self.logits is not None:
+                torch.distributed.all_gather_into_tensor(self.logits, self.logits_local, group=self.group)
+                return self.logits
+        return self.logits_local
+
+    def reset(self, x0):
+        """Start of a sequence of steps: residual stream zero, first input x0 (M, hidden) f16."""
+        self.h.zero_()
+        self.x.copy_(x0)

@@ -108,3 +108,17 @@ def test_reference_signatures_match_checkout_if_present():
         tree = ast.parse(open(os.path.join(ref, "scripts", mod + ".py")).read())
         node = next(n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == fn)
         assert [a.arg for a in node.args.args] == want, (mod, fn)
+
+
+def test_torch_binding_is_built_and_forwards_to_the_c_abi():
+    """The thin torch extension over the C ABI loads without a GPU and answers the size queries
+    with the library's own numbers."""
+    from sx8_quantization_b200 import _lib
+    E = _lib.ext()
+    assert E is not None, "_sx8_torch.so not built (python -m sx8_quantization_b200.build)"
+    L = _lib.lib()
+    assert E.gemv_workspace_bytes(80, 8) == L.sx8_gemv_workspace_bytes(80, 8)
+    assert E.gemm_workspace_bytes(128, 1024, 80) == L.sx8_gemm_workspace_bytes(128, 1024, 80)
+    assert isinstance(E.last_error(), str)
+    for fn in ("gemv", "gemm", "embed"):
+        assert callable(getattr(E, fn))

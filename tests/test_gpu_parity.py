@@ -401,7 +401,11 @@ def test_argument_errors_raise(ops):
         ops.gemv(x[:1], wt, b, s, 128, 256, qt["n_cb"])        # blob size does not match N
     with pytest.raises(ops.SX8Error):
         ops.gemv(x[:1], wt, b, s, 64, 256, qt["n_cb"] + 1)     # n_cb != ceil(K/32)
+    # a workspace is only needed (and checked) when x has to be staged: K not a multiple of 32
+    w2, qt2, bi2, v442 = case(136, 1000, 59)
+    wt2, b2, s2 = t16_dev(qt2, v442)
     with pytest.raises(ops.SX8Error):
-        ops.gemv(x[:1], wt, b, s, 64, 256, qt["n_cb"], workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
+        ops.gemv(dev(orc.synth_x(1, 1000, 1)), wt2, b2, s2, 136, 1000, qt2["n_cb"],
+                 workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
     with pytest.raises(ops.SX8Error):
         ops.gemv(x[:1].float(), wt, b, s, 64, 256, qt["n_cb"])
