@@ -108,13 +108,9 @@ int sx8_gemv_allreduce(const void* x_f16, int M, int K, long ldx, const void* wt
                        const float* scales, int N, int n_cb, float* y, void* workspace,
                        size_t workspace_bytes, unsigned flags, const sx8_peers_t* peers, void* stream);
 
-/* Tuning hook for experiments: force the GEMV's tile-group width (nt = 2, 4 or 8 tiles of 16
- * columns), cluster split-K (1..8) and persistent grid size; 0 = automatic, -1 = take the
- * SX8_GEMV_NT / SX8_GEMV_SPLIT / SX8_GEMV_GRID environment variables.  Process-wide.       */
-void sx8_gemv_tune(int nt, int split, int grid);
-
 /* ---- prefill GEMM, any M ----------------------------------------------------------
  * Y (M, N) = X (M, K) * W^T, fp32 accumulate; out_f16 != 0 writes Y as f16, else f32.
+ * M <= 16 runs on the GEMV kernel (one pass over the weights), larger M on the tensor cores.
  * Replaces ref: cuda/sx8_gemm_compact.cu:157-194 (compute_z44_batch, gemm_compact) and
  * ref: cuda/sx8_fused_wmma.cu:134-154 (fused_forward).                               */
 size_t sx8_gemm_workspace_bytes(int M, int N, int n_cb);
@@ -194,7 +190,7 @@ int sx8_repack_v44(const void* dmin_f16, const void* dmax_f16, const uint8_t* co
 /* ---- interleaved 30-byte blocks (GGUF tensor data) -----------------------------------
  * A block_sx8 record is {dmin f16 @0, dmax f16 @2, config @4, qh[16] @5, ql[8] @21,
  * coeff @29}, n-major (bid = n*n_cb + kb): the layout of the llama.cpp fork's GGUF files
- * (ref: scripts/convert_pkl_to_gguf_sx8.py:20-38 blockify_vec; patches/llama-cpp-sx8.patch
+ * (ref: scripts/convert_pkl_to_gguf_sx8.py:20-38 blockify_vec; llama-cpp-sx8.patch
  * :136-144 struct block_sx8) and of docs/SX8_FLASH_V4_3_SPEC.md:13-25.
  * sx8_repack_t16_blocks: records -> device layout in one pass (GGUF tensor -> GEMV-ready).
  * sx8_blocks_from_planes / sx8_planes_from_blocks: the container's planes <-> records,

@@ -22,7 +22,6 @@ SIGNATURES = {
     "sx8_gemv": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _i, _i, _vp, _vp, _sz, _u, _vp]),
     "sx8_gemv_multi": (_i, [_vp, _i, _i, _l, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _sz, _u, _vp]),
     "sx8_gemv_allreduce": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _i, _i, _vp, _vp, _sz, _u, _vp, _vp]),
-    "sx8_gemv_tune": (None, [_i, _i, _i]),
     "sx8_gemm_workspace_bytes": (_sz, [_i, _i, _i]),
     "sx8_gemm": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _sz, _vp]),
     "sx8_gemm_static_max_ncb": (_sz, []),
@@ -43,6 +42,11 @@ SIGNATURES = {
     "sx8_glue_attn_decode": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, ctypes.c_float, _vp, _vp, _sz, _vp]),
     "sx8_glue_silu_mul": (_i, [_vp, _vp, _l, _vp, _vp]),
     "sx8_device_error_flag": (_i, [ctypes.POINTER(ctypes.c_uint)]),
+}
+
+# include/sx8_b200_test.h: hooks for the test suite, not part of the library's contract
+TEST_SIGNATURES = {
+    "sx8_gemv_tune": (None, [_i, _i, _i]),
 }
 
 SX8_F_PDL = 1
@@ -68,7 +72,7 @@ def lib():
             raise SX8Error("libsx8b200.so is not built (run `python -m sx8_quantization_b200.build`); "
                            "there is no CPU or PyTorch fallback for the S-X8 kernels")
         l = ctypes.CDLL(LIB_PATH)
-        for name, (res, args) in SIGNATURES.items():
+        for name, (res, args) in list(SIGNATURES.items()) + list(TEST_SIGNATURES.items()):
             fn = getattr(l, name)
             fn.restype = res
             fn.argtypes = args

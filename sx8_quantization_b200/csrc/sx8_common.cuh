@@ -1,5 +1,6 @@
 // sx8_common.cuh -- shared device/host helpers for the S-X8 v4.3 kernels (sm_100a).
 #pragma once
+#include <stdlib.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -75,6 +76,20 @@ __device__ __forceinline__ RangeD64 range_d64(float lo_f, float hi_f, int s) {
     if (step < 1e-10) step = 1e-10;
     return {rlo, step};
 }
+
+// Launch-shape and timing experiments are compiled in only with -DSX8_EXPERIMENT (some of them
+// make the kernels produce wrong results on purpose); the default build reads no environment
+// variable and carries none of those branches.
+#ifdef SX8_EXPERIMENT
+inline int exp_env(const char* name, int dflt) {
+    const char* v = getenv(name);
+    return v ? atoi(v) : dflt;
+}
+#define SX8_DBG(p) ((p).debug)
+#else
+#define exp_env(name, dflt) (dflt)
+#define SX8_DBG(p) 0
+#endif
 
 __device__ __forceinline__ float h2f_bits(uint16_t b) { return __half2float(__ushort_as_half(b)); }
 

@@ -1,13 +1,17 @@
 // sx8_gemm.cu -- S-X8 v4.3 prefill GEMM entry point (Y = X * W^T, W decoded on the fly).
 //
-// Small and ragged M run as 8-row passes of the decode-GEMV kernel (weights stay in
-// L2 between passes); large M runs on the tcgen05 kernel in sx8_gemm_tc.cu.
+// M <= 16 runs on the decode-GEMV kernel in one pass over the weights (two blocks of 8
+// activation rows per decoded weight fragment); larger M runs on the tcgen05 kernel in
+// sx8_gemm_tc.cu.
 #include "sx8_common.cuh"
 
 namespace sx8 {
 int gemv_launch(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
                 const float* scales, int N, int n_cb, float* y, void* workspace, unsigned flags,
                 cudaStream_t stream);
+int gemv_rows_launch(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
+                     const float* scales, int N, int n_cb, float* y, void* xstage, void* table, unsigned flags,
+                     cudaStream_t stream);
 int gemv_check(const char* who, const void* x, int M, int Mmax, int K, long ldx, const void* wt16,
                const float* bases, const float* scales, int N, int n_cb, const void* y);
 size_t gemm_tc_workspace_bytes(int M, int N, int n_cb);
@@ -35,13 +39,15 @@ __global__ void __launch_bounds__(256) f32_to_f16_kernel(const float* __restrict
 using namespace sx8;
 
 static size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
+static const int kGemvRowsMax = 16;   // batch rows the GEMV kernel takes in one pass
 
 extern "C" size_t sx8_gemm_workspace_bytes(int M, int N, int n_cb) {
     if (M <= 0 || N <= 0 || n_cb <= 0) return 0;
-    size_t table = round256(sx8_gemv_workspace_bytes(n_cb, 8));
-    size_t y32 = round256((size_t)M * (size_t)N * 4);
+    // small-M path: [staged x (M, 32 n_cb) f16][activation table n_cb * M * 16][f32 result when Y is f16]
+    size_t a = 0;
+    if (M <= kGemvRowsMax)
+        a = round256((size_t)M * n_cb * 64) + round256((size_t)M * n_cb * 16) + round256((size_t)M * (size_t)N * 4);
     size_t tc = gemm_tc_workspace_bytes(M, N, n_cb);
-    size_t a = table + y32;
     return a > tc ? a : tc;
 }
 
@@ -58,16 +64,21 @@ extern "C" int sx8_gemm(const void* x, int M, int K, long ldx, const void* wt16,
                   sx8_gemm_workspace_bytes(M, N, n_cb), workspace_bytes);
         return SX8_E_WORKSPACE;
     }
-    if (gemm_tc_supported(M, N, K, n_cb))
+    if (M > kGemvRowsMax && gemm_tc_supported(M, N, K, n_cb))
         return gemm_tc_launch(x, M, K, ldx, wt16, bases, scales, N, n_cb, y, out_f16, workspace, stream);
-    uint8_t* table = (uint8_t*)workspace;
-    float* y32 = out_f16 ? (float*)((uint8_t*)workspace + round256(sx8_gemv_workspace_bytes(n_cb, 8))) : (float*)y;
-    for (int m0 = 0; m0 < M; m0 += 8) {
-        int mc = (M - m0 < 8) ? (M - m0) : 8;
-        rc = gemv_launch((const __half*)x + (long)m0 * ldx, mc, K, ldx, wt16, bases, scales, N, n_cb,
-                         y32 + (long)m0 * N, table, 0u, stream);
-        if (rc != SX8_OK) return rc;
+    if (M > kGemvRowsMax) {
+        set_error("sx8_gemm: the tensor-core path is unavailable (driver without cuTensorMapEncodeTiled) and M=%d is "
+                  "beyond the %d rows of the GEMV path", M, kGemvRowsMax);
+        return SX8_E_UNSUPPORTED;
     }
+    uint8_t* xstage = (uint8_t*)workspace;
+    uint8_t* table = xstage + round256((size_t)M * n_cb * 64);
+    float* y32 = out_f16 ? (float*)(table + round256((size_t)M * n_cb * 16)) : (float*)y;
+    if (M <= 8)
+        rc = gemv_launch(x, M, K, ldx, wt16, bases, scales, N, n_cb, y32, xstage, 0u, stream);
+    else
+        rc = gemv_rows_launch(x, M, K, ldx, wt16, bases, scales, N, n_cb, y32, xstage, table, 0u, stream);
+    if (rc != SX8_OK) return rc;
     if (out_f16) {
         long n = (long)M * N;
         f32_to_f16_kernel<<<(unsigned)((n / 4 + 255) / 256 + 1), 256, 0, stream>>>(y32, (__half*)y, n);

@@ -357,7 +357,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 const int s = rp.s;
                 if (rp.r > 0 && ok) ok = mbar_wait(p_empty + 8 * s, (rp.r - 1) & 1, 0x10u);
                 rp = rp.next();
-                if (p.debug & 4) {
+                if (SX8_DBG(p) & 4) {
                     if (lane == 0) mbar_arrive(p_full + 8 * s);
                     continue;
                 }
@@ -383,7 +383,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 const int s = ra.s;
                 if (ra.r > 0 && ok) ok = mbar_wait(a_empty + 8 * s, (ra.r - 1) & 1, 0x20u);
                 ra = ra.next();
-                if (p.debug & 8) {
+                if (SX8_DBG(p) & 8) {
                     if (lane == 0) mbar_arrive(a_full + 8 * s);
                     continue;
                 }
@@ -429,7 +429,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             if (lane == 0) {
                 const uint64_t bdesc = umma_desc(sB + sb * B_TILE);
 #pragma unroll
-                for (int mt = 0; mt < MT && !(p.debug & 2); mt++) {
+                for (int mt = 0; mt < MT && !(SX8_DBG(p) & 2); mt++) {
                     const uint64_t adesc = umma_desc(sA + (sa * MT + mt) * A_TILE);
 #pragma unroll
                     for (int k = 0; k < BK / 16; k++) {   // +32 bytes along K inside the swizzle atom
@@ -441,7 +441,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                                      idesc_for(BNU, 128), (ks > 0 || k > 0) ? 1u : 0u);
                     }
                 }
-                if (p.debug & 32) {   // handshake experiment: plain arrivals instead of commits
+                if (SX8_DBG(p) & 32) {   // handshake experiment: plain arrivals instead of commits
                     mbar_arrive(a_empty + 8 * sa);
                     mbar_arrive(b_empty + 8 * sb);
                     if (ks == n_ks - 1) mbar_arrive(acc_full);
@@ -486,7 +486,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             const uint32_t pst = sP + sp * P_STAGE, bst = sB + sb * B_TILE;
             // work items (tile, block row) are dealt round-robin to the group's warps
 #pragma unroll
-            for (int item = gw; item < TILES * KB_STAGE && !(p.debug & 1); item += kGroupWarps) {
+            for (int item = gw; item < TILES * KB_STAGE && !(SX8_DBG(p) & 1); item += kGroupWarps) {
                 const int tl = item % TILES, r = item / TILES;
                 const bool tile_ok = tile0 + tl < p.n_tiles;
                 // Column 16*tl + g sits in operand row 16*tl + rho(g), rho(g) = 4*(g&1) + (g>>1): the
@@ -564,7 +564,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                     sts128(bst + rowB * 128 + ((c ^ (rowB & 7u)) << 4), wb);
                 }
             }
-            if (!(p.debug & 64))
+            if (!(SX8_DBG(p) & 64))
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic stores -> tensor-core reads
             __syncwarp();
             if (lane == 0) {
@@ -754,10 +754,10 @@ int launch_tc_bn(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
     using C = tc::Cfg<MT, BN, PAIR>;
     // Pipeline depths.  The packed slabs come from HBM with the longest latency and get every
     // stage that is left (at most 8); X tiles come from L2.
-    static const int env_sa = getenv("SX8_GEMM_SA") ? atoi(getenv("SX8_GEMM_SA")) : 0;
-    static const int env_sb = getenv("SX8_GEMM_SB") ? atoi(getenv("SX8_GEMM_SB")) : 0;
-    static const int env_sp = getenv("SX8_GEMM_SP") ? atoi(getenv("SX8_GEMM_SP")) : 0;
-    static const int env_debug = getenv("SX8_GEMM_DEBUG") ? atoi(getenv("SX8_GEMM_DEBUG")) : 0;
+    static const int env_sa = exp_env("SX8_GEMM_SA", 0);
+    static const int env_sb = exp_env("SX8_GEMM_SB", 0);
+    static const int env_sp = exp_env("SX8_GEMM_SP", 0);
+    static const int env_debug = exp_env("SX8_GEMM_DEBUG", 0);
     p.debug = env_debug;
     p.sa = env_sa > 0 ? env_sa : 3;
     p.sb = env_sb > 0 ? env_sb : ((BN >= 256) ? 2 : (PAIR == 2 ? 4 : 3));
@@ -825,7 +825,7 @@ int launch_tc_bn(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
 // only while twice as many CTAs still fit in one wave -- a second wave costs more than it gains.
 template <int MT>
 int launch_tc(const CUtensorMap& map, const tc::Params& p, cudaStream_t stream) {
-    static const int force_bn = getenv("SX8_GEMM_BN") ? atoi(getenv("SX8_GEMM_BN")) : 0;
+    static const int force_bn = exp_env("SX8_GEMM_BN", 0);
     const long mtiles = (p.M + 128 * MT - 1) / (128 * MT);
     int bn = 256;
     if (((p.N + 127) / 128) * mtiles <= 148) bn = 128;
@@ -833,7 +833,7 @@ int launch_tc(const CUtensorMap& map, const tc::Params& p, cudaStream_t stream) 
     // idle (74 two-SM clusters fit at once) and K is long enough to halve: 9472 x 2560 at
     // M = 128 runs in 28.8 us against 35.0, 2560 x 9728 in 61.7 against 86.4 with 64-column
     // tiles (SX8_GEMM_KSPLIT=0 switches it off).
-    static const int ksplit = getenv("SX8_GEMM_KSPLIT") ? atoi(getenv("SX8_GEMM_KSPLIT")) : 1;
+    static const int ksplit = exp_env("SX8_GEMM_KSPLIT", 1);
     const bool can_split = ksplit && ((p.N + 127) / 128) * mtiles <= 74 && p.n_cb >= 32;
     if (bn == 128 && !can_split && ((p.N + 63) / 64) * mtiles <= 148 && ((p.N + 127) / 128) * mtiles <= 37) bn = 64;
     if (force_bn == 64 || force_bn == 128 || force_bn == 256) bn = force_bn;
@@ -848,10 +848,10 @@ int launch_tc(const CUtensorMap& map, const tc::Params& p, cudaStream_t stream) 
 // SX8_GEMM_PAIR overrides for experiments: 0 = never pair, 2 = always 512-row pairs,
 // 3 = always 256-row pairs.
 int launch_auto(const CUtensorMap& map, const tc::Params& p, cudaStream_t stream) {
-    static const int pair_mode = getenv("SX8_GEMM_PAIR") ? atoi(getenv("SX8_GEMM_PAIR")) : 1;
-    static const int force_mt = getenv("SX8_GEMM_MT") ? atoi(getenv("SX8_GEMM_MT")) : 0;
+    static const int pair_mode = exp_env("SX8_GEMM_PAIR", 1);
+    static const int force_mt = exp_env("SX8_GEMM_MT", 0);
     if (pair_mode == 3) return launch_tc_bn<1, 128, 2>(map, p, stream);
-    static const int groups = getenv("SX8_GEMM_GROUPS") ? atoi(getenv("SX8_GEMM_GROUPS")) : 4;
+    static const int groups = exp_env("SX8_GEMM_GROUPS", 4);
     if (pair_mode == 2 || (pair_mode == 1 && p.M > 256)) {
         if (groups == 2) return launch_tc_bn<2, 128, 2, 2>(map, p, stream);
         return launch_tc_bn<2, 128, 2, 4>(map, p, stream);
@@ -871,8 +871,7 @@ size_t gemm_tc_workspace_bytes(int M, int N, int n_cb) {
 
 bool gemm_tc_supported(int M, int N, int K, int n_cb) {
     (void)N; (void)K; (void)n_cb;
-    static const int min_m = getenv("SX8_GEMM_TC_MIN_M") ? atoi(getenv("SX8_GEMM_TC_MIN_M")) : 32;
-    return M >= min_m && encode_fn() != nullptr;
+    return M >= 1 && encode_fn() != nullptr;
 }
 
 int gemm_tc_launch(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,

@@ -30,6 +30,7 @@
 
 #include "sx8_common.cuh"
 #include "sx8_layout.cuh"
+#include "../../include/sx8_b200_test.h"
 
 #define SX8_MAX_PEERS 8
 
@@ -63,14 +64,20 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One wait attempt.  The thread is suspended by the hardware until the phase completes or the
+// time hint (ns) runs out, so a waiting warp does not burn issue slots polling: the producer
+// warp waits for an empty stage most of the time and shares its scheduler with two consumer
+// warps (measured on 151936 x 2560: the polling loops were ~25 of 108 instructions per
+// 512-weight unit).
+constexpr uint32_t kWaitHintNs = 100000u;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kWaitHintNs)
         : "memory");
     return ok != 0;
 }
@@ -88,11 +95,21 @@ __device__ __forceinline__ uint32_t mbar_probe(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok;
 }
-// Bounded wait: gives up after kSpinLimit polls, records the failure in the device
-// error word and returns false; the caller then stops waiting for the rest of the kernel.
+// Bounded wait: gives up after kSpinLimit attempts or about two seconds, whichever comes first,
+// records the failure in the device error word and returns false; the caller then stops
+// waiting for the rest of the kernel.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned code) {
-    for (uint32_t i = 0; i < kSpinLimit; i++)
+    if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (uint32_t i = 0; i < kSpinLimit; i++) {
         if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 15u) == 15u) {
+            unsigned long long t1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (t1 - t0 > 2000000000ull) break;
+        }
+    }
     atomicOr(&g_sx8_error_flag, code);
     return false;
 }
@@ -108,6 +125,14 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// d = A * B (accumulator input zero: no registers to clear)
+__device__ __forceinline__ void mma16816_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                           uint32_t b0, uint32_t b1) {
+    asm(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
 __device__ __forceinline__ void mma1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
     asm(
@@ -149,14 +174,6 @@ __device__ __forceinline__ void consumer_bar() {  // the 8 consumer warps only
     asm volatile("bar.sync 1, 256;" ::: "memory");
 }
 
-// x >> 8.  With SX8_UMULHI the shift runs as a multiply-high on the FMA pipe, taking load
-// off the integer/logic pipe that bounds this kernel.
-#ifdef SX8_UMULHI
-#define SHR8(x) __umulhi((x), 0x01000000u)
-#else
-#define SHR8(x) ((x) >> 8)
-#endif
-
 // fp32 -> (hi, lo) fp16 pair: hi + lo == v to ~22 bits.
 __device__ __forceinline__ void split_hilo(float v, uint32_t& hi, uint32_t& lo) {
     __half h = __float2half_rn(v);
@@ -196,7 +213,7 @@ struct GemvParams {
     const __half* x;       // (M, >= 32*n_cb), rows 16-byte aligned
     long ldx;
     int nseg, n_cb, M, split, groups;
-    int debug;   // bit 0: consumers skip the math (pipeline-only timing experiments)
+    const uint8_t* table;  // batches above 8 rows: the activation table in global scratch (n_cb, M, 16 B)
     // Row-parallel exchange (world > 1): instead of y, every finished tile is stored into slot
     // `rank` of each peer's receive buffer (peer memory, plain stores over NVLink), then a
     // per-peer arrival counter is bumped; reduce_peers_kernel sums the slots.
@@ -224,26 +241,90 @@ __device__ __forceinline__ void signal_tile(const GemvParams& p, int lane) {
     if (lane < p.world) atomicAdd_system(p.peer_flag[lane], 1u);
 }
 
-template <int NT, int KB_S, int STAGES>
+// Activation-side operands of one (block row kb, batch row m): 16 bytes, two 8-byte entries
+// read by lanes t = 0 and t = 1 of the main loop:
+//   entry t=0: { {SxB_hi, 0}, {Z0_hi, Z1_hi} }    entry t=1: { {SxB_lo, 0}, {Z0_lo, Z1_lo} }
+// The first word multiplies the {dmin, dmax} pair of a column (the zero half cancels dmax), the
+// second the {c0, c1} * 2^-10 pair; Zj (ref cuda/sx8_decode1_v3.cu:44-65) is pre-multiplied by
+// 1024.  The four lanes t = 0..3 of a lane group compute one item from 8 activations each.
+__device__ __forceinline__ void act_item(const uint4 raw, const float4 (&bq)[4], float s0, float s1, int t,
+                                         uint32_t& w0, uint32_t& w1) {
+    const __half* hh = reinterpret_cast<const __half*>(&raw);
+    const float bb0[8] = {bq[0].x, bq[0].y, bq[0].z, bq[0].w, bq[1].x, bq[1].y, bq[1].z, bq[1].w};
+    const float bb1[8] = {bq[2].x, bq[2].y, bq[2].z, bq[2].w, bq[3].x, bq[3].y, bq[3].z, bq[3].w};
+    float sx = 0.f, z0 = 0.f, z1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        float xv = __half2float(hh[i]);
+        sx += xv;
+        z0 = fmaf(xv, bb0[i], z0);
+        z1 = fmaf(xv, bb1[i], z1);
+    }
+#pragma unroll
+    for (int off = 1; off <= 2; off <<= 1) {
+        sx += __shfl_xor_sync(0xFFFFFFFFu, sx, off);
+        z0 += __shfl_xor_sync(0xFFFFFFFFu, z0, off);
+        z1 += __shfl_xor_sync(0xFFFFFFFFu, z1, off);
+    }
+    z0 = s0 * z0 * 1024.0f;
+    z1 = s1 * z1 * 1024.0f;
+    uint32_t sh, sl, z0h, z0l, z1h, z1l;
+    split_hilo(sx, sh, sl);
+    split_hilo(z0, z0h, z0l);
+    split_hilo(z1, z1h, z1l);
+    w0 = (t == 0) ? sh : sl;
+    w1 = (t == 0) ? (z0h | (z1h << 16)) : (z0l | (z1l << 16));
+}
+
+// The table for batches above 8 rows, built once per launch into global scratch (n_cb, M, 16 B)
+// instead of once per CTA into shared memory: the main kernel's producer then brings each
+// stage's slice in with one bulk copy, and a CTA's K range is not limited by table space.
+__global__ void __launch_bounds__(256)
+act_table_kernel(const __half* __restrict__ x, long ldx, int M, int n_cb, const float* __restrict__ bases,
+                 const float* __restrict__ scales, uint2* __restrict__ table) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int t = threadIdx.x & 3;
+    const long n_items = (long)n_cb * M;
+    long item = (long)blockIdx.x * 64 + (threadIdx.x >> 2);
+    const bool valid = item < n_items;
+    if (!valid) item = n_items - 1;
+    const int kb = (int)(item / M), m = (int)(item - (long)kb * M);
+    float4 bq[4];
+    const float4* b0p = reinterpret_cast<const float4*>(bases + (long)kb * 64 + t * 8);
+    const float4* b1p = reinterpret_cast<const float4*>(bases + (long)kb * 64 + 32 + t * 8);
+    bq[0] = b0p[0]; bq[1] = b0p[1]; bq[2] = b1p[0]; bq[3] = b1p[1];
+    uint4 raw = *reinterpret_cast<const uint4*>(x + (long)m * ldx + (long)kb * 32 + t * 8);
+    uint32_t w0, w1;
+    act_item(raw, bq, scales[kb * 2], scales[kb * 2 + 1], t, w0, w1);
+    if (t < 2 && valid) table[item * 2 + t] = make_uint2(w0, w1);
+}
+
+// MB = batch rows in blocks of 8 (1 or 2): a decoded weight fragment feeds MB activation
+// blocks, so the decode cost per weight is paid once for up to 16 rows.
+template <int NT, int KB_S, int STAGES, int MB>
 struct GemvCfg {
     static constexpr int KS = kConsumerWarps / NT;        // warps sharing a tile split the kb rows
     static constexpr int XROW = KB_S * 64 + 64;           // padded: conflict-free 128-bit x reads
     static constexpr int OFF_X = NT * KB_S * T16_UNIT;
-    static constexpr int STAGE = OFF_X + 8 * XROW;
-    static constexpr int RED_BYTES = kConsumerWarps * 32 * 16;
-    static constexpr int FIXED = STAGES * STAGE + RED_BYTES + 2 * STAGES * 8 + 16;
-    static int smem_bytes(int kb_per_cta, int M) { return FIXED + kb_per_cta * table_stride(M) + 128; }
+    static constexpr int OFF_T = OFF_X + 8 * MB * XROW;   // MB > 1: this stage's slice of the global table
+    static constexpr int STAGE = OFF_T + (MB > 1 ? KB_S * 8 * MB * 16 : 0);
+    static constexpr int RED_BYTES = kConsumerWarps * 32 * 16 * MB;
+    static constexpr int FIXED = STAGES * STAGE + RED_BYTES + 2 * STAGES * 8 + 16 + 16;
+    // MB == 1: the CTA's own table (kb_per_cta rows) follows, padded for the lanes of rows >= M
+    static int smem_bytes(int kb_per_cta, int M) { return FIXED + (MB > 1 ? 0 : kb_per_cta * table_stride(M) + 128); }
 };
 
-template <int NT, int KB_S, int STAGES, int MINB = 3>
+template <int NT, int KB_S, int STAGES, int MINB, int MB>
 __global__ void __launch_bounds__(kThreads, MINB) gemv_kernel(GemvParams p) {
-    using C = GemvCfg<NT, KB_S, STAGES>;
+    using C = GemvCfg<NT, KB_S, STAGES, MB>;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     const uint32_t red = sbase + STAGES * C::STAGE;
     const uint32_t bar_full = red + C::RED_BYTES;
     const uint32_t bar_empty = bar_full + STAGES * 8;
-    const uint32_t dtab = bar_empty + STAGES * 8 + 16;
+    const uint32_t zslot = bar_empty + STAGES * 8 + 16;   // 16 zero bytes: table operand of lanes t >= 2
+    const uint32_t dtab = zslot + 16;
     const int dt_kb = table_stride(p.M);
 
     asm volatile("griddepcontrol.launch_dependents;");
@@ -269,247 +350,258 @@ __global__ void __launch_bounds__(kThreads, MINB) gemv_kernel(GemvParams p) {
             mbar_init(bar_empty + 8 * s, kConsumerWarps);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        sts32(zslot, 0u); sts32(zslot + 4, 0u); sts32(zslot + 8, 0u); sts32(zslot + 12, 0u);
     }
     __syncthreads();
 
-    float accF[4] = {0.f, 0.f, 0.f, 0.f}, accD[4] = {0.f, 0.f, 0.f, 0.f};
+    float accF[MB][4], accD[MB][4];
+#pragma unroll
+    for (int nb = 0; nb < MB; nb++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) accF[nb][i] = accD[nb][i] = 0.f;
+    const float kBase = 0.25f * 0.015873f * 16384.0f;   // q = (dmax-dmin)/4, step unit 0.015873, operands scaled by 2^-14
 
     if (warp == kConsumerWarps) {
-        // ---------------------------------------------- producer warp: lane i < NT copies
-        // the slab of tile i, lane 8+m the slice of activation row m.
-        auto coords = [&](int it, int& grp, int& kb0, int& rows) {
-            int gi = it / n_iter, j = it - gi * n_iter;
-            grp = (int)blockIdx.x + gi * (int)gridDim.x - sg.group0;
-            kb0 = kb_begin + j * KB_S;
-            rows = min(KB_S, kb_end - kb0);
+        // ---------------------------------------------- producer warp: lane i < NT copies the
+        // slab of tile i, lane m < M the slice of activation row m, lane 31 the table slice.
+        // Stage coordinates advance incrementally (tile group, K step): no divisions in the loop.
+        struct Pos { int grp, j, s; uint32_t ph; };
+        auto advance = [&](Pos& q) {
+            if (++q.j == n_iter) { q.j = 0; q.grp += (int)gridDim.x; }
+            if (++q.s == STAGES) { q.s = 0; q.ph ^= 1u; }
         };
-        auto arm = [&](int it) {   // lane 0: announce the bytes of stage `it`
-            int grp, kb0, rows;
-            coords(it, grp, kb0, rows);
-            int tiles = min(NT, sg.n_tiles - grp * NT);
-            mbar_expect_tx(bar_full + 8 * (it % STAGES),
-                           (uint32_t)rows * ((uint32_t)tiles * T16_UNIT + (uint32_t)p.M * 64u));
-        };
-        auto issue_w = [&](int it) {
-            int grp, kb0, rows;
-            coords(it, grp, kb0, rows);
-            int s = it % STAGES;
-            long T = (long)grp * NT + lane;
-            if (lane < NT && T < sg.n_tiles)
-                bulk_g2s(sbase + s * C::STAGE + lane * (KB_S * T16_UNIT),
-                         sg.blob + (T * p.n_cb + kb0) * T16_UNIT, (uint32_t)rows * T16_UNIT, bar_full + 8 * s);
-        };
-        auto issue_x = [&](int it) {
-            int grp, kb0, rows;
-            coords(it, grp, kb0, rows);
-            int s = it % STAGES;
-            int m = lane - 8;
-            if (m >= 0 && m < p.M)
-                bulk_g2s(sbase + s * C::STAGE + C::OFF_X + m * C::XROW, p.x + (long)m * p.ldx + (long)kb0 * 32,
-                         (uint32_t)rows * 64u, bar_full + 8 * s);
+        auto issue = [&](const Pos& q, bool with_w, bool with_x) {
+            const int kb0 = kb_begin + q.j * KB_S;
+            const int rows = min(KB_S, kb_end - kb0);
+            const uint32_t stage = sbase + q.s * C::STAGE, bar = bar_full + 8 * q.s;
+            if (with_w) {
+                if (lane == 0) {
+                    int tiles = min(NT, sg.n_tiles - q.grp * NT);
+                    mbar_expect_tx(bar, (uint32_t)rows * ((uint32_t)tiles * T16_UNIT + (uint32_t)p.M * (MB > 1 ? 80u : 64u)));
+                }
+                __syncwarp();
+                long T = (long)q.grp * NT + lane;
+                if (lane < NT && T < sg.n_tiles)
+                    bulk_g2s(stage + lane * (KB_S * T16_UNIT), sg.blob + (T * p.n_cb + kb0) * T16_UNIT,
+                             (uint32_t)rows * T16_UNIT, bar);
+            }
+            if (with_x) {
+                if (lane < p.M)
+                    bulk_g2s(stage + C::OFF_X + lane * C::XROW, p.x + (long)lane * p.ldx + (long)kb0 * 32,
+                             (uint32_t)rows * 64u, bar);
+                if (MB > 1 && lane == 31)
+                    bulk_g2s(stage + C::OFF_T, p.table + (long)kb0 * dt_kb, (uint32_t)(rows * dt_kb), bar);
+            }
         };
         bool ok = true;
         // Weights do not depend on the preceding kernel: request them before waiting
-        // for it (programmatic dependent launch); activations after.
+        // for it (programmatic dependent launch); activations (and their table) after.
         const int pre = min(total_iters, STAGES);
-        for (int it = 0; it < pre; it++) {
-            if (lane == 0) arm(it);
-            __syncwarp();
-            issue_w(it);
-        }
+        Pos q{(int)blockIdx.x - sg.group0, 0, 0, 0u};
+        Pos q0 = q;
+        for (int it = 0; it < pre; it++) { issue(q, true, false); advance(q); }
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        for (int it = 0; it < pre; it++) issue_x(it);
+        for (int it = 0; it < pre; it++) { issue(q0, false, true); advance(q0); }
+        // q.ph is the parity of the fill about to be issued; the consumers' release of the
+        // previous fill of the same stage completed phase (q.ph ^ 1) of its empty barrier
         for (int it = pre; it < total_iters; it++) {
-            int s = it % STAGES;
-            if (ok) ok = mbar_wait(bar_empty + 8 * s, ((it / STAGES) - 1) & 1, 1u);
-            if (lane == 0) arm(it);
-            __syncwarp();
-            issue_w(it);
-            issue_x(it);
+            if (ok) ok = mbar_wait(bar_empty + 8 * q.s, q.ph ^ 1u, 1u);
+            issue(q, true, true);
+            advance(q);
         }
     } else {
         // ---------------------------------------------- consumers
         const int ti = warp % NT, kpart = warp / NT;
         const int g = lane >> 2, t = lane & 3;
-        const bool row_ok = g < p.M;
-        // ---- activation-side table for kb_begin..kb_end.  A work item is (block row kb, batch
-        // row m); the four lanes t = 0..3 of a lane group take one item (8 activations each), a
-        // warp takes 2 x 8 items per pass, the CTA 128: at batch 1 that is 128 block rows per
-        // pass, so even a CTA with a long K range builds its table in one round of loads.
-        // Two 8-byte entries per (kb, m), read by lanes t = 0 and t = 1 of the main loop:
-        //   entry t=0: { {SxB_hi, 0}, {Z0_hi, Z1_hi} }    entry t=1: { {SxB_lo, 0}, {Z0_lo, Z1_lo} }
-        // The first word multiplies the {dmin, dmax} pair of a column (the zero half cancels
-        // dmax), the second the {c0, c1} * 2^-10 pair; Zj (ref cuda/sx8_decode1_v3.cu:44-65)
-        // is pre-multiplied by 1024.
-        // PCA bases and scales are weights: those of the first pass are fetched before waiting
-        // for the preceding kernel, like the producer's weight copies.
-        const int n_items = (kb_end - kb_begin) * p.M;
-        constexpr int kPass = 16 * kConsumerWarps;
-        float4 bq[2][4];
-        float sc[2][2];
-        int ikb[2], im[2];
-        auto locate = [&](int i0) {
+        if (MB == 1) {
+            // ---- the CTA's own activation table for kb_begin..kb_end (act_item).  A work item is
+            // (block row kb, batch row m); a warp takes 2 x 8 items per pass, the CTA 128: at batch
+            // 1 that is 128 block rows per pass, so even a CTA with a long K range builds its table
+            // in one round of loads.  PCA bases and scales are weights: those of the first pass are
+            // fetched before waiting for the preceding kernel, like the producer's weight copies.
+            const int n_items = (kb_end - kb_begin) * p.M;
+            constexpr int kPass = 16 * kConsumerWarps;
+            float4 bq[2][4];
+            float sc[2][2];
+            int ikb[2], im[2];
+            auto locate = [&](int i0) {
 #pragma unroll
-            for (int u = 0; u < 2; u++) {
-                int item = min(i0 + u * (kPass / 2) + warp * 8 + g, max(n_items - 1, 0));
-                int q = item / p.M;
-                ikb[u] = kb_begin + q;
-                im[u] = item - q * p.M;
-            }
-        };
-        auto load_bases = [&]() {
+                for (int u = 0; u < 2; u++) {
+                    int item = min(i0 + u * (kPass / 2) + warp * 8 + g, max(n_items - 1, 0));
+                    int q = item / p.M;
+                    ikb[u] = kb_begin + q;
+                    im[u] = item - q * p.M;
+                }
+            };
+            auto load_bases = [&]() {
 #pragma unroll
-            for (int u = 0; u < 2; u++) {
-                const int kb = ikb[u];
-                const float4* b0p = reinterpret_cast<const float4*>(sg.bases + (long)kb * 64 + t * 8);
-                const float4* b1p = reinterpret_cast<const float4*>(sg.bases + (long)kb * 64 + 32 + t * 8);
-                bq[u][0] = b0p[0]; bq[u][1] = b0p[1]; bq[u][2] = b1p[0]; bq[u][3] = b1p[1];
-                sc[u][0] = sg.scales[kb * 2 + 0];
-                sc[u][1] = sg.scales[kb * 2 + 1];
-            }
-        };
-        if (n_items > 0) {
-            locate(0);
-            load_bases();
-        }
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-
-        for (int i0 = 0; i0 < n_items; i0 += kPass) {
-            uint4 raw[2];
-            if (i0 > 0) {
-                locate(i0);
+                for (int u = 0; u < 2; u++) {
+                    const int kb = ikb[u];
+                    const float4* b0p = reinterpret_cast<const float4*>(sg.bases + (long)kb * 64 + t * 8);
+                    const float4* b1p = reinterpret_cast<const float4*>(sg.bases + (long)kb * 64 + 32 + t * 8);
+                    bq[u][0] = b0p[0]; bq[u][1] = b0p[1]; bq[u][2] = b1p[0]; bq[u][3] = b1p[1];
+                    sc[u][0] = sg.scales[kb * 2 + 0];
+                    sc[u][1] = sg.scales[kb * 2 + 1];
+                }
+            };
+            if (n_items > 0) {
+                locate(0);
                 load_bases();
             }
-#pragma unroll
-            for (int u = 0; u < 2; u++)
-                raw[u] = *reinterpret_cast<const uint4*>(p.x + (long)im[u] * p.ldx + (long)ikb[u] * 32 + t * 8);
-#pragma unroll
-            for (int u = 0; u < 2; u++) {
-                const bool valid = i0 + u * (kPass / 2) + warp * 8 + g < n_items;
-                const __half* hh = reinterpret_cast<const __half*>(&raw[u]);
-                float bb0[8] = {bq[u][0].x, bq[u][0].y, bq[u][0].z, bq[u][0].w, bq[u][1].x, bq[u][1].y, bq[u][1].z, bq[u][1].w};
-                float bb1[8] = {bq[u][2].x, bq[u][2].y, bq[u][2].z, bq[u][2].w, bq[u][3].x, bq[u][3].y, bq[u][3].z, bq[u][3].w};
-                float sx = 0.f, z0 = 0.f, z1 = 0.f;
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    float xv = __half2float(hh[i]);
-                    sx += xv;
-                    z0 = fmaf(xv, bb0[i], z0);
-                    z1 = fmaf(xv, bb1[i], z1);
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            for (int i0 = 0; i0 < n_items; i0 += kPass) {
+                uint4 raw[2];
+                if (i0 > 0) {
+                    locate(i0);
+                    load_bases();
                 }
 #pragma unroll
-                for (int off = 1; off <= 2; off <<= 1) {
-                    sx += __shfl_xor_sync(0xFFFFFFFFu, sx, off);
-                    z0 += __shfl_xor_sync(0xFFFFFFFFu, z0, off);
-                    z1 += __shfl_xor_sync(0xFFFFFFFFu, z1, off);
-                }
-                z0 = sc[u][0] * z0 * 1024.0f;
-                z1 = sc[u][1] * z1 * 1024.0f;
-                uint32_t sh, sl, z0h, z0l, z1h, z1l;
-                split_hilo(sx, sh, sl);
-                split_hilo(z0, z0h, z0l);
-                split_hilo(z1, z1h, z1l);
-                if (t < 2 && valid) {
-                    uint32_t w0 = (t == 0) ? sh : sl;
-                    uint32_t w1 = (t == 0) ? (z0h | (z1h << 16)) : (z0l | (z1l << 16));
-                    uint32_t a = dtab + (ikb[u] - kb_begin) * dt_kb + im[u] * 16 + t * 8;
-                    sts32(a, w0);
-                    sts32(a + 4, w1);
+                for (int u = 0; u < 2; u++)
+                    raw[u] = *reinterpret_cast<const uint4*>(p.x + (long)im[u] * p.ldx + (long)ikb[u] * 32 + t * 8);
+#pragma unroll
+                for (int u = 0; u < 2; u++) {
+                    const bool valid = i0 + u * (kPass / 2) + warp * 8 + g < n_items;
+                    uint32_t w0, w1;
+                    act_item(raw[u], bq[u], sc[u][0], sc[u][1], t, w0, w1);
+                    if (t < 2 && valid) {
+                        uint32_t a = dtab + (ikb[u] - kb_begin) * dt_kb + im[u] * 16 + t * 8;
+                        sts32(a, w0);
+                        sts32(a + 4, w1);
+                    }
                 }
             }
+            consumer_bar();
+        } else {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
         }
-        consumer_bar();
 
         const uint32_t sh2 = 8u + 2u * (uint32_t)t;
+        // Shared-memory operand addresses of this lane.  Rows beyond M read the last row (their
+        // results are never stored); lanes t >= 2 read the zero slot instead of the table (stride 0).
+        uint32_t xoff[MB];
+#pragma unroll
+        for (int nb = 0; nb < MB; nb++) xoff[nb] = (uint32_t)(min(nb * 8 + g, p.M - 1) * C::XROW + t * 16);
+        const uint32_t tstride = (t < 2) ? (uint32_t)dt_kb : 0u;        // per block row
+        const uint32_t tnb = (t < 2) ? 128u : 0u;                       // per block of 8 batch rows
+        const uint32_t tlane = (t < 2) ? (uint32_t)(g * 16 + t * 8) : 0u;
+
+        // One (16-column tile, block row) unit: 512 weights of this warp.
+        //   unit: the 480-byte T16 unit; xa: this block row in the activation rows; ta: its table row
+        auto unit_body = [&](const uint32_t unit, const uint32_t xa, const uint32_t ta) {
+            uint32_t W0 = lds32(unit + lane * 4), W1 = lds32(unit + 128 + lane * 4), W2 = lds32(unit + 256 + lane * 4);
+            uint32_t H0 = lds32(unit + 384 + g * 4), H1 = lds32(unit + 416 + g * 4), H2 = lds32(unit + 448 + g * 4);
+            // per sub-block constants looked up by range strategy:
+            //   mult * 2^8  = 1024, 256, 256, 512     63*off * 2^-14 = 0, 0, 189*2^-14, 63*2^-14
+            uint32_t u = (H2 >> sh2) & 0x00030003u;
+            uint32_t sel = u * 0x2222u + 0x10101010u;
+            uint32_t selB = sel >> 16;
+            uint32_t mA = __byte_perm(0x5C006400u, 0x60005C00u, sel);
+            uint32_t aA = __byte_perm(0x00000000u, 0x1BE021E8u, sel);
+            uint32_t mB = __byte_perm(0x5C006400u, 0x60005C00u, selB);
+            uint32_t aB = __byte_perm(0x00000000u, 0x1BE021E8u, selB);
+            // bytes hold level << 2; read as fp16 bit patterns they are level * 2^-22, so
+            // fma gives (mult*level + 63*off) * 2^-14, exact
+            uint32_t V3 = ((W0 << 2) & 0x0C0C0C0Cu) | ((W1 << 4) & 0x30303030u) | ((W2 << 6) & 0xC0C0C0C0u);
+            uint32_t fa0 = hfma2_u32(W0 & 0x00FC00FCu, mA, aA);
+            uint32_t fa1 = hfma2_u32((W0 >> 8) & 0x00FC00FCu, mA, aA);
+            uint32_t fa2 = hfma2_u32(W1 & 0x00FC00FCu, mA, aA);
+            uint32_t fa3 = hfma2_u32((W1 >> 8) & 0x00FC00FCu, mA, aA);
+            uint32_t fb0 = hfma2_u32(W2 & 0x00FC00FCu, mB, aB);
+            uint32_t fb1 = hfma2_u32((W2 >> 8) & 0x00FC00FCu, mB, aB);
+            uint32_t fb2 = hfma2_u32(V3 & 0x00FF00FFu, mB, aB);
+            uint32_t fb3 = hfma2_u32((V3 >> 8) & 0x00FF00FFu, mB, aB);
+            // Signed 4-bit coefficient n -> fp16 n * 2^-10: (n ^ 8) under the exponent of 1024
+            // (column A, nibble at mantissa bits 0..3) or (column B, bits 4..7: 1024 + 16 (n ^ 8)).
+            uint32_t ccA = hfma2_u32((H2 & 0x000F000Fu) ^ 0x64086408u, 0x14001400u, 0xBC08BC08u);
+            uint32_t ccB = hfma2_u32((H2 & 0x00F000F0u) ^ 0x64806480u, 0x04000400u, 0xAC80AC80u);
+            // (dmax - dmin) per column; the constant 0.25 * 0.015873 * 2^14 is applied once, at the end
+            float2 eA = __half22float2(*reinterpret_cast<const __half2*>(&H0));
+            float2 eB = __half22float2(*reinterpret_cast<const __half2*>(&H1));
+            const float baseA = eA.y - eA.x, baseB = eB.y - eB.x;
+#pragma unroll
+            for (int nb = 0; nb < MB; nb++) {
+                uint4 xq = lds128(xa + xoff[nb]);
+                uint32_t dv0, dv1;
+                asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(dv0), "=r"(dv1) : "r"(ta + nb * tnb) : "memory");
+                float d[4];
+                mma16816_z(d, fa0, fb0, fa1, fb1, xq.x, xq.y);
+                mma16816(d, fa2, fb2, fa3, fb3, xq.z, xq.w);
+                // direct terms: {dmin,dmax} x {SxB_hi|lo, 0} and {c0,c1} * 2^-10 x 1024*Z; lanes
+                // t = 0,1 carry the hi and lo halves of the activation sums, lanes 2,3 zeros
+                mma1688(accD[nb], H0, H1, dv0);
+                mma1688(accD[nb], ccA, ccB, dv1);
+                accF[nb][0] = fmaf(baseA, d[0], accF[nb][0]);
+                accF[nb][1] = fmaf(baseA, d[1], accF[nb][1]);
+                accF[nb][2] = fmaf(baseB, d[2], accF[nb][2]);
+                accF[nb][3] = fmaf(baseB, d[3], accF[nb][3]);
+            }
+        };
+        constexpr int kRowsPerWarp = KB_S / C::KS;
+        const uint32_t unit0 = sbase + (ti * KB_S + kpart) * T16_UNIT;
+        const uint32_t x0 = sbase + C::OFF_X + kpart * 64;
+        // MB == 1: the CTA's table, indexed by block row within the K range; MB > 1: the stage's slice
+        const uint32_t tab0 = (t < 2) ? ((MB > 1 ? sbase + C::OFF_T : dtab) + kpart * (uint32_t)dt_kb + tlane) : zslot;
         bool ok = true;
-        int it = 0;
+        int s = 0;            // stage of this iteration and the parity of its current fill
+        uint32_t ph = 0u;
         uint32_t pre = 0;   // answer of the early probe of this iteration's barrier
         for (int gi = 0; gi < my_groups; gi++) {
             const int grp = (int)blockIdx.x + gi * (int)gridDim.x - sg.group0;
-            for (int j = 0; j < n_iter; j++, it++) {
-                int s = it % STAGES;
-                if (!pre && ok) ok = mbar_wait(bar_full + 8 * s, (it / STAGES) & 1, 2u);
-                pre = mbar_probe(bar_full + 8 * ((it + 1) % STAGES), ((it + 1) / STAGES) & 1);
-                int rows = min(KB_S, kb_end - (kb_begin + j * KB_S));
-                uint32_t st = sbase + s * C::STAGE;
+            for (int j = 0; j < n_iter; j++) {
+                if (!pre && ok) ok = mbar_wait(bar_full + 8 * s, ph, 2u);
+                int s1 = s + 1;
+                uint32_t ph1 = ph;
+                if (s1 == STAGES) { s1 = 0; ph1 ^= 1u; }
+                pre = mbar_probe(bar_full + 8 * s1, ph1);
+                const int rows = min(KB_S, kb_end - (kb_begin + j * KB_S));
+                const uint32_t so = (uint32_t)(s * C::STAGE);
+                const uint32_t tj = tab0 + (MB > 1 ? ((t < 2) ? so : 0u) : (uint32_t)(j * KB_S) * tstride);
+                if (rows == KB_S) {   // full stage: no per-row checks
 #pragma unroll
-                for (int ri = 0; ri < KB_S / C::KS; ri++) {
-                    const int r = kpart + ri * C::KS;
-                    if (r >= rows || (p.debug & 1)) break;
-                    uint32_t unit = st + (ti * KB_S + r) * T16_UNIT;
-                    uint32_t W0 = lds32(unit + lane * 4), W1 = lds32(unit + 128 + lane * 4),
-                             W2 = lds32(unit + 256 + lane * 4);
-                    uint32_t H0 = lds32(unit + 384 + g * 4), H1 = lds32(unit + 416 + g * 4),
-                             H2 = lds32(unit + 448 + g * 4);
-                    uint4 xq = make_uint4(0u, 0u, 0u, 0u);
-                    if (row_ok) xq = lds128(st + C::OFF_X + g * C::XROW + r * 64 + t * 16);
-                    uint32_t dv0 = 0u, dv1 = 0u;
-                    if (t < 2) {
-                        uint32_t a = dtab + (j * KB_S + r) * dt_kb + g * 16 + t * 8;
-                        asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(dv0), "=r"(dv1) : "r"(a) : "memory");
+                    for (int ri = 0; ri < kRowsPerWarp; ri++)
+                        unit_body(unit0 + so + ri * C::KS * T16_UNIT, x0 + so + ri * C::KS * 64,
+                                  tj + (uint32_t)(ri * C::KS) * tstride);
+                } else {
+#pragma unroll 1
+                    for (int ri = 0; ri < kRowsPerWarp; ri++) {
+                        if (kpart + ri * C::KS >= rows) break;
+                        unit_body(unit0 + so + ri * C::KS * T16_UNIT, x0 + so + ri * C::KS * 64,
+                                  tj + (uint32_t)(ri * C::KS) * tstride);
                     }
-
-                    // per sub-block constants looked up by range strategy:
-                    //   mult * 2^8  = 1024, 256, 256, 512     63*off * 2^-14 = 0, 0, 189*2^-14, 63*2^-14
-                    uint32_t u = (H2 >> sh2) & 0x00030003u;
-                    uint32_t sel = u * 0x2222u + 0x10101010u;
-                    uint32_t selB = sel >> 16;
-                    uint32_t mA = __byte_perm(0x5C006400u, 0x60005C00u, sel);
-                    uint32_t aA = __byte_perm(0x00000000u, 0x1BE021E8u, sel);
-                    uint32_t mB = __byte_perm(0x5C006400u, 0x60005C00u, selB);
-                    uint32_t aB = __byte_perm(0x00000000u, 0x1BE021E8u, selB);
-                    // bytes hold level << 2; read as fp16 bit patterns they are level * 2^-22, so
-                    // fma gives (mult*level + 63*off) * 2^-14, exact
-                    uint32_t V3 = ((W0 << 2) & 0x0C0C0C0Cu) | ((W1 << 4) & 0x30303030u) | ((W2 << 6) & 0xC0C0C0C0u);
-                    uint32_t fa0 = hfma2_u32(W0 & 0x00FC00FCu, mA, aA);
-                    uint32_t fa1 = hfma2_u32(SHR8(W0) & 0x00FC00FCu, mA, aA);
-                    uint32_t fa2 = hfma2_u32(W1 & 0x00FC00FCu, mA, aA);
-                    uint32_t fa3 = hfma2_u32(SHR8(W1) & 0x00FC00FCu, mA, aA);
-                    uint32_t fb0 = hfma2_u32(W2 & 0x00FC00FCu, mB, aB);
-                    uint32_t fb1 = hfma2_u32(SHR8(W2) & 0x00FC00FCu, mB, aB);
-                    uint32_t fb2 = hfma2_u32(V3 & 0x00FF00FFu, mB, aB);
-                    uint32_t fb3 = hfma2_u32(SHR8(V3) & 0x00FF00FFu, mB, aB);
-                    float d[4] = {0.f, 0.f, 0.f, 0.f};
-                    mma16816(d, fa0, fb0, fa1, fb1, xq.x, xq.y);
-                    mma16816(d, fa2, fb2, fa3, fb3, xq.z, xq.w);
-                    // direct terms: {dmin,dmax} x {SxB_hi|lo, 0} and {c0,c1} * 2^-10 x 1024*Z; lanes
-                    // t = 0,1 carry the hi and lo halves of the activation sums, lanes 2,3 zeros
-                    uint32_t ccA = hfma2_u32((H2 & 0x000F000Fu) ^ 0x64086408u, 0x14001400u, 0xBC08BC08u);
-                    uint32_t ccB = hfma2_u32(((H2 >> 4) & 0x000F000Fu) ^ 0x64086408u, 0x14001400u, 0xBC08BC08u);
-                    mma1688(accD, H0, H1, dv0);
-                    mma1688(accD, ccA, ccB, dv1);
-                    const float kBase = 0.25f * 0.015873f * 16384.0f;
-                    float baseA = (h2f_bits((uint16_t)(H0 >> 16)) - h2f_bits((uint16_t)H0)) * kBase;
-                    float baseB = (h2f_bits((uint16_t)(H1 >> 16)) - h2f_bits((uint16_t)H1)) * kBase;
-                    accF[0] = fmaf(baseA, d[0], accF[0]);
-                    accF[1] = fmaf(baseA, d[1], accF[1]);
-                    accF[2] = fmaf(baseB, d[2], accF[2]);
-                    accF[3] = fmaf(baseB, d[3], accF[3]);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+                s = s1;
+                ph = ph1;
             }
             if (kDirectStore && p.split == 1) {
-                int nA = (grp * NT + ti) * 16 + g, nB = nA + 8, m0 = 2 * t, m1 = m0 + 1;
-                float v0 = accF[0] + accD[0], v1 = accF[1] + accD[1], v2 = accF[2] + accD[2], v3 = accF[3] + accD[3];
-                if (nA < sg.N) {
-                    if (m0 < p.M) put_out(p, sg.y, (long)m0 * sg.N + nA, v0);
-                    if (m1 < p.M) put_out(p, sg.y, (long)m1 * sg.N + nA, v1);
-                }
-                if (nB < sg.N) {
-                    if (m0 < p.M) put_out(p, sg.y, (long)m0 * sg.N + nB, v2);
-                    if (m1 < p.M) put_out(p, sg.y, (long)m1 * sg.N + nB, v3);
+                const int nA = (grp * NT + ti) * 16 + g, nB = nA + 8;
+#pragma unroll
+                for (int nb = 0; nb < MB; nb++) {
+                    const int m0 = nb * 8 + 2 * t, m1 = m0 + 1;
+                    float v0 = fmaf(accF[nb][0], kBase, accD[nb][0]), v1 = fmaf(accF[nb][1], kBase, accD[nb][1]),
+                          v2 = fmaf(accF[nb][2], kBase, accD[nb][2]), v3 = fmaf(accF[nb][3], kBase, accD[nb][3]);
+                    if (nA < sg.N) {
+                        if (m0 < p.M) put_out(p, sg.y, (long)m0 * sg.N + nA, v0);
+                        if (m1 < p.M) put_out(p, sg.y, (long)m1 * sg.N + nA, v1);
+                    }
+                    if (nB < sg.N) {
+                        if (m0 < p.M) put_out(p, sg.y, (long)m0 * sg.N + nB, v2);
+                        if (m1 < p.M) put_out(p, sg.y, (long)m1 * sg.N + nB, v3);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; i++) accF[nb][i] = accD[nb][i] = 0.f;
                 }
                 if (grp * NT + ti < sg.n_tiles) signal_tile(p, lane);
-#pragma unroll
-                for (int i = 0; i < 4; i++) accF[i] = accD[i] = 0.f;
             }
         }
         if (!(kDirectStore && p.split == 1)) {
-            float4 v = make_float4(accF[0] + accD[0], accF[1] + accD[1], accF[2] + accD[2], accF[3] + accD[3]);
-            asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(red + (warp * 32 + lane) * 16), "f"(v.x),
-                         "f"(v.y), "f"(v.z), "f"(v.w)
-                         : "memory");
+#pragma unroll
+            for (int nb = 0; nb < MB; nb++)
+                asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(red + ((nb * kConsumerWarps + warp) * 32 + lane) * 16),
+                             "f"(fmaf(accF[nb][0], kBase, accD[nb][0])), "f"(fmaf(accF[nb][1], kBase, accD[nb][1])),
+                             "f"(fmaf(accF[nb][2], kBase, accD[nb][2])), "f"(fmaf(accF[nb][3], kBase, accD[nb][3]))
+                             : "memory");
         }
     }
     if (kDirectStore && p.split == 1) return;   // uniform over the whole grid
@@ -517,27 +609,33 @@ __global__ void __launch_bounds__(kThreads, MINB) gemv_kernel(GemvParams p) {
 
     // ---- reduce the KS kb-parts of each tile, in fixed order, into slot kpart 0
     if (warp < NT) {
-        uint32_t a = red + (warp * 32 + lane) * 16;
-        float4 v;
-        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
-        for (int k = 1; k < C::KS; k++) {
-            float4 u;
-            asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
-                         : "=f"(u.x), "=f"(u.y), "=f"(u.z), "=f"(u.w)
-                         : "r"(a + k * NT * 32 * 16));
-            v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+#pragma unroll
+        for (int nb = 0; nb < MB; nb++) {
+            uint32_t a = red + ((nb * kConsumerWarps + warp) * 32 + lane) * 16;
+            float4 v;
+            asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
+            for (int k = 1; k < C::KS; k++) {
+                float4 u;
+                asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                             : "=f"(u.x), "=f"(u.y), "=f"(u.z), "=f"(u.w)
+                             : "r"(a + k * NT * 32 * 16));
+                v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+            }
+            accF[nb][0] = v.x; accF[nb][1] = v.y; accF[nb][2] = v.z; accF[nb][3] = v.w;
+            if (p.split > 1)
+                asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(a), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
         }
-        accF[0] = v.x; accF[1] = v.y; accF[2] = v.z; accF[3] = v.w;
-        if (p.split > 1)
-            asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(a), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
     }
     if (p.split > 1) {
         cluster_sync_all();
         if (rank == 0 && warp < NT) {
-            uint32_t a = red + (warp * 32 + lane) * 16;
-            for (int rk = 1; rk < p.split; rk++) {
-                float4 u = ld_cluster_f4(a, (uint32_t)rk);
-                accF[0] += u.x; accF[1] += u.y; accF[2] += u.z; accF[3] += u.w;
+#pragma unroll
+            for (int nb = 0; nb < MB; nb++) {
+                uint32_t a = red + ((nb * kConsumerWarps + warp) * 32 + lane) * 16;
+                for (int rk = 1; rk < p.split; rk++) {
+                    float4 u = ld_cluster_f4(a, (uint32_t)rk);
+                    accF[nb][0] += u.x; accF[nb][1] += u.y; accF[nb][2] += u.z; accF[nb][3] += u.w;
+                }
             }
         }
         cluster_sync_all();  // peers keep their shared memory alive until rank 0 has read it
@@ -545,15 +643,18 @@ __global__ void __launch_bounds__(kThreads, MINB) gemv_kernel(GemvParams p) {
     if (rank == 0 && warp < NT && (int)blockIdx.x < p.groups) {
         const int g = lane >> 2, t = lane & 3;
         const int tl = ((int)blockIdx.x - sg.group0) * NT + warp;   // tile within this CTA's matrix
-        int nA = tl * 16 + g, nB = nA + 8;
-        int m0 = 2 * t, m1 = 2 * t + 1;
-        if (nA < sg.N) {
-            if (m0 < p.M) put_out(p, sg.y, (long)m0 * sg.N + nA, accF[0]);
-            if (m1 < p.M) put_out(p, sg.y, (long)m1 * sg.N + nA, accF[1]);
-        }
-        if (nB < sg.N) {
-            if (m0 < p.M) put_out(p, sg.y, (long)m0 * sg.N + nB, accF[2]);
-            if (m1 < p.M) put_out(p, sg.y, (long)m1 * sg.N + nB, accF[3]);
+        const int nA = tl * 16 + g, nB = nA + 8;
+#pragma unroll
+        for (int nb = 0; nb < MB; nb++) {
+            const int m0 = nb * 8 + 2 * t, m1 = m0 + 1;
+            if (nA < sg.N) {
+                if (m0 < p.M) put_out(p, sg.y, (long)m0 * sg.N + nA, accF[nb][0]);
+                if (m1 < p.M) put_out(p, sg.y, (long)m1 * sg.N + nA, accF[nb][1]);
+            }
+            if (nB < sg.N) {
+                if (m0 < p.M) put_out(p, sg.y, (long)m0 * sg.N + nB, accF[nb][2]);
+                if (m1 < p.M) put_out(p, sg.y, (long)m1 * sg.N + nB, accF[nb][3]);
+            }
         }
         if (tl < sg.n_tiles) signal_tile(p, lane);
     }
@@ -611,10 +712,6 @@ struct Choice {
 
 int g_tune_nt = -1, g_tune_split = -1, g_tune_grid = -1;   // -1: take the environment / automatic choice
 
-int env_int(const char* name) {
-    const char* v = getenv(name);
-    return v ? atoi(v) : 0;
-}
 
 // Tile-group width NT (x16 columns), cluster split-K and grid size.  Measured on B200 over the
 // Qwen3-4B- and Llama-70B-shaped projections (and their tensor-parallel shards): the best
@@ -622,10 +719,10 @@ int env_int(const char* name) {
 // leaves room for the next launch's prefetching CTAs), prefer wide tile groups, and use as
 // little split-K as that allows.  Very large N runs a persistent grid without split-K.
 Choice choose(int N, int n_cb, int M) {
-    static const int e_nt = env_int("SX8_GEMV_NT"), e_split = env_int("SX8_GEMV_SPLIT"),
-                     e_grid = env_int("SX8_GEMV_GRID");
+    static const int e_nt = exp_env("SX8_GEMV_NT", 0), e_split = exp_env("SX8_GEMV_SPLIT", 0),
+                     e_grid = exp_env("SX8_GEMV_GRID", 0);
     const int f_nt = g_tune_nt >= 0 ? g_tune_nt : e_nt, f_split = g_tune_split >= 0 ? g_tune_split : e_split,
-              f_grid = g_tune_grid >= 0 ? g_tune_grid : e_grid;
+              f_grid = g_tune_grid >= 0 ? g_tune_grid : e_grid;   // test hook (sx8_b200_test.h), else automatic
     const int n_tiles = (int)t16_tiles(N);
     const int min_split = (n_cb + max_kb_per_cta(M) - 1) / max_kb_per_cta(M);
     Choice best{8, min_split, 0};
@@ -674,7 +771,7 @@ Choice choose(int N, int n_cb, int M) {
     }
     int groups = (n_tiles + best.nt - 1) / best.nt;
     best.grid_x = groups;
-    static const int verbose = env_int("SX8_GEMV_VERBOSE");
+    static const int verbose = exp_env("SX8_GEMV_VERBOSE", 0);
     if (verbose) fprintf(stderr, "sx8 gemv launch shape: N=%d n_cb=%d M=%d -> nt=%d split=%d groups=%d\n", N, n_cb, M, best.nt, best.split, groups);
     if (best.split == 1) {   // persistent grid: eight-tile groups by default, others on request
         int cap = f_grid > 0 ? f_grid : (best.nt == 8 ? 3 * kSMs : 0);
@@ -686,15 +783,15 @@ Choice choose(int N, int n_cb, int M) {
     return best;
 }
 
-template <int NT, int KB_S, int STAGES, int MINB = 3>
+template <int NT, int KB_S, int STAGES, int MINB = 3, int MB = 1>
 int launch_gemv(const GemvParams& p, int grid_x, unsigned flags, cudaStream_t stream) {
-    using C = GemvCfg<NT, KB_S, STAGES>;
+    using C = GemvCfg<NT, KB_S, STAGES, MB>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        e = cudaFuncSetAttribute(gemv_kernel<NT, KB_S, STAGES, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(gemv_kernel<NT, KB_S, STAGES, MINB, MB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  C::smem_bytes(kTableBytes / 16, 1));
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemv smem)");
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
@@ -721,7 +818,7 @@ int launch_gemv(const GemvParams& p, int grid_x, unsigned flags, cudaStream_t st
     }
     cfg.attrs = attrs;
     cfg.numAttrs = na;
-    e = cudaLaunchKernelEx(&cfg, gemv_kernel<NT, KB_S, STAGES, MINB>, p);
+    e = cudaLaunchKernelEx(&cfg, gemv_kernel<NT, KB_S, STAGES, MINB, MB>, p);
     if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(gemv_kernel)");
     return SX8_OK;
 }
@@ -780,13 +877,12 @@ int gemv_launch_ex(const void* x, int M, int K, long ldx, const void* wt16, cons
     }
     Choice c = choose(N, n_cb, M);
     const int n_tiles = (int)t16_tiles(N);
-    static const int dbg = env_int("SX8_GEMV_DEBUG");
     GemvParams p{};
     p.nseg = 1;
     p.seg[0] = SegDesc{(const uint8_t*)wt16, bases, scales, y, N, n_tiles, 0};
     p.x = xp; p.ldx = ld;
     p.n_cb = n_cb; p.M = M; p.split = c.split;
-    p.groups = (n_tiles + c.nt - 1) / c.nt; p.debug = dbg;
+    p.groups = (n_tiles + c.nt - 1) / c.nt;
     p.rank = 0; p.world = 1; p.slot_elems = 0;
     if (peers && peers->world > 1) {
         const int par = peers->parity & 1;
@@ -823,6 +919,54 @@ int gemv_launch_ex(const void* x, int M, int K, long ldx, const void* wt16, cons
     return SX8_OK;
 }
 
+// 9..16 batch rows in one pass over the weights: the activation table goes to global scratch
+// (one small launch), then the GEMV kernel with two blocks of 8 rows per decoded fragment.
+// xstage: (M, 32*n_cb) f16 scratch, used only when x cannot be fetched as it is; table:
+// n_cb * M * 16 bytes, 16-byte aligned.  Arguments already validated.
+int gemv_rows_launch(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
+                     const float* scales, int N, int n_cb, float* y, void* xstage, void* table, unsigned flags,
+                     cudaStream_t stream) {
+    const __half* xp = (const __half*)x;
+    long ld = ldx;
+    const int Kp = n_cb * 32;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cfg.attrs = &attr;
+    cfg.numAttrs = (flags & SX8_F_PDL) ? 1 : 0;
+    if (!x_direct(x, K, ldx, n_cb)) {
+        cfg.gridDim = dim3((unsigned)(((long)M * Kp + 255) / 256), 1, 1);
+        cudaError_t e = cudaLaunchKernelEx(&cfg, xpad_kernel, (const __half*)x, M, K, ldx, Kp, (__half*)xstage);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(xpad_kernel)");
+        xp = (const __half*)xstage;
+        ld = Kp;
+    }
+    cfg.gridDim = dim3((unsigned)(((long)n_cb * M + 63) / 64), 1, 1);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, act_table_kernel, xp, ld, M, n_cb, bases, scales, (uint2*)table);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(act_table_kernel)");
+    const int n_tiles = (int)t16_tiles(N);
+    const int groups = (n_tiles + 3) / 4;          // four-tile groups, two CTAs per SM
+    int split = 1;
+    while (split < 8 && (long)groups * split < 2 * kSMs && n_cb / (split + 1) >= 8) split++;
+    // one tile group per CTA: two warps share a tile here, and their partial sums are only
+    // combined once, at the end of the CTA
+    const int grid_x = groups;
+    GemvParams p{};
+    p.nseg = 1;
+    p.seg[0] = SegDesc{(const uint8_t*)wt16, bases, scales, y, N, n_tiles, 0};
+    p.x = xp; p.ldx = ld; p.table = (const uint8_t*)table;
+    p.n_cb = n_cb; p.M = M; p.split = split; p.groups = groups;
+    p.rank = 0; p.world = 1; p.slot_elems = 0;
+    // Two row blocks only: every further block adds two m16n8k16 and two m16n8k8 mma.sync per
+    // 512 weights, and on this GPU those run at about 32 and 16 cycles each per scheduler
+    // (28672 x 8192: 72 us at 8 rows, 106 us at 16, 234 us at 32 with four blocks against 137 us
+    // on the tcgen05 kernel), so from 17 rows on the tensor-core GEMM is the faster path.
+    return launch_gemv<4, 8, 3, 2, 2>(p, grid_x, flags, stream);
+}
+
 // Several matrices that share the activations, one launch (q|k|v, gate|up).  Each CTA owns one
 // tile group of one matrix; groups never straddle matrices.
 int gemv_launch_multi(const void* x, int M, int K, long ldx, int count, const void* const* wt16,
@@ -849,7 +993,6 @@ int gemv_launch_multi(const void* x, int M, int K, long ldx, int count, const vo
     long n_total = 0;
     for (int i = 0; i < count; i++) n_total += (long)t16_tiles(N[i]) * 16;
     Choice c = choose((int)n_total, n_cb, M);
-    static const int dbg = env_int("SX8_GEMV_DEBUG");
     GemvParams p{};
     p.nseg = count;
     int g0 = 0;
@@ -858,7 +1001,7 @@ int gemv_launch_multi(const void* x, int M, int K, long ldx, int count, const vo
         p.seg[i] = SegDesc{(const uint8_t*)wt16[i], bases[i], scales[i], y[i], N[i], nt_i, g0};
         g0 += (nt_i + c.nt - 1) / c.nt;
     }
-    p.x = xp; p.ldx = ld; p.n_cb = n_cb; p.M = M; p.split = c.split; p.groups = g0; p.debug = dbg;
+    p.x = xp; p.ldx = ld; p.n_cb = n_cb; p.M = M; p.split = c.split; p.groups = g0;
     p.rank = 0; p.world = 1; p.slot_elems = 0;
     if (c.nt == 8) return launch_gemv<8, 4, 3>(p, g0, flags, stream);   // one group per CTA: grid = groups
     if (c.nt == 4) return launch_gemv<4, 8, 3>(p, g0, flags, stream);

@@ -332,11 +332,12 @@ def test_gemv_matches_reference_kernel_build(ops):
     assert (y - Y).abs().max().item() <= TOL_VS_KERNEL_FORMULA * Y.abs().max().item()
 
 
-@pytest.mark.parametrize("M", [9, 16, 33, 128, 200, 512])
+@pytest.mark.parametrize("M", [2, 9, 13, 16, 17, 31, 33, 128, 200, 512])
 @pytest.mark.parametrize("f16out", [False, True])
 def test_gemm_m_sweep(ops, M, f16out):
-    """M < 32: 8-row passes of the GEMV kernel; M >= 32: the tcgen05 kernel (one or two
-    128-row accumulators, ragged last row tile)."""
+    """M <= 8: the GEMV kernel; 9..16: the GEMV kernel with two blocks of eight rows per decoded
+    fragment and the activation table in global scratch; M >= 17: the tcgen05 kernel (one or
+    two 128-row accumulators, ragged last row tile)."""
     w, qt, bi, v44 = case(1024, 2560, 58)
     x = orc.synth_x(M, 2560, 9)
     y_cmp = orc.matmul_ref(x, orc.dequant_d64(qt, bi))
@@ -346,6 +347,31 @@ def test_gemm_m_sweep(ops, M, f16out):
     scale = np.abs(y_cmp).max()
     tol = TOL_VS_COMPARATOR + (2.0 ** -10 if f16out else 0.0)
     assert np.abs(y - y_cmp).max() <= tol * scale
+
+
+@pytest.mark.parametrize("shape,M", [((136, 1000), 12), ((2560, 9728), 16), ((9728, 2560), 10), ((60000, 64), 16),
+                                     ((60, 64), 9), ((8, 32), 11), ((4096, 8192), 15)])
+def test_gemm_two_row_blocks(ops, shape, M):
+    """The 9..16-row path: K not a multiple of 32 (staged activations), long K with a cluster
+    split, a persistent grid over many tile groups, ragged last tiles, one-block K."""
+    w, qt, bi, v44 = case(shape[0], shape[1], 62)
+    x = orc.synth_x(M, shape[1], 14)
+    y_cmp = orc.matmul_ref(x, orc.dequant_d64(qt, bi))
+    y_krn = orc.gemv_d32(x, v44)
+    wt, b, s = t16_dev(qt, v44)
+    y = ops.gemm(dev(x), wt, b, s, shape[0], shape[1], qt["n_cb"])
+    y2 = ops.gemm(dev(x), wt, b, s, shape[0], shape[1], qt["n_cb"])
+    assert torch.equal(y, y2)
+    y = y.cpu().numpy()
+    scale = np.abs(y_cmp).max()
+    assert np.isfinite(y).all()
+    assert np.abs(y - y_cmp).max() <= TOL_VS_COMPARATOR * scale
+    assert np.abs(y - y_krn).max() <= TOL_VS_KERNEL_FORMULA * scale
+    # the rows of a batch do not depend on each other: the first 8 equal the 8-row GEMV's bits
+    y8 = ops.gemv(dev(x[:8]), wt, b, s, shape[0], shape[1], qt["n_cb"]).cpu().numpy()
+    assert np.abs(y[:8] - y8).max() <= 1e-5 * scale
+    from sx8_quantization_b200 import _lib
+    assert _lib.device_error_flag() == 0
 
 
 @pytest.mark.parametrize("shape,M", [((136, 1000), 130), ((48, 80), 64), ((4096, 2560), 256), ((2560, 4096), 1000),
