@@ -713,11 +713,23 @@ struct Choice {
 int g_tune_nt = -1, g_tune_split = -1, g_tune_grid = -1;   // -1: take the environment / automatic choice
 
 
-// Tile-group width NT (x16 columns), cluster split-K and grid size.  Measured on B200 over the
-// Qwen3-4B- and Llama-70B-shaped projections (and their tensor-parallel shards): the best
-// configurations put about 384 CTAs in flight per wave (3 CTAs per SM hold 444; ~2.6 per SM
-// leaves room for the next launch's prefetching CTAs), prefer wide tile groups, and use as
-// little split-K as that allows.  Very large N runs a persistent grid without split-K.
+// The three instantiations of the decode GEMV (NT tiles per group: KB_S block rows per stage,
+// stages): wide groups take fewer, larger stages -- eight units per warp and stage instead of
+// four halve the per-stage bookkeeping, and at batch 8 eight tiles share each activation slice.
+using Cfg8 = GemvCfg<8, 8, 2, 1>;
+using Cfg4 = GemvCfg<4, 8, 3, 1>;
+using Cfg2 = GemvCfg<2, 8, 4, 1>;
+
+// Tile-group width NT (x16 columns), cluster split-K and grid size: a score over the candidates
+// whose constants were fitted to a sweep on B200 of every (NT, split) over the Qwen3-4B- and
+// Llama-70B-shaped projections and their 2/4/8-way tensor-parallel shards (29 shapes, batch 1
+// and 8; mean distance of the chosen shape from the best measured one 2.4 %).  It aims at 80 % of
+// the CTAs that can be resident at once (shared memory decides: three per SM, two when the
+// activation table of a batch-8 launch is large -- fewer than all leave room for the next
+// launch's prefetching CTAs), prefers wide tile groups, few waves, little split-K and at least 16
+// block rows per CTA.  Very large N runs without split-K on eight-tile groups and a persistent
+// grid (151936 x 2560 at batch 1: 88 us against 93 us with four-tile groups on a plain grid),
+// except with a long K at batch <= 4, where the four-tile groups are level or ahead.
 Choice choose(int N, int n_cb, int M) {
     static const int e_nt = exp_env("SX8_GEMV_NT", 0), e_split = exp_env("SX8_GEMV_SPLIT", 0),
                      e_grid = exp_env("SX8_GEMV_GRID", 0);
@@ -725,10 +737,11 @@ Choice choose(int N, int n_cb, int M) {
               f_grid = g_tune_grid >= 0 ? g_tune_grid : e_grid;   // test hook (sx8_b200_test.h), else automatic
     const int n_tiles = (int)t16_tiles(N);
     const int min_split = (n_cb + max_kb_per_cta(M) - 1) / max_kb_per_cta(M);
+    constexpr int kSmemPerSM = 228 * 1024, kSmemReserved = 1024;   // per SM, per resident CTA
     Choice best{8, min_split, 0};
     double best_score = -1e30;
     const int nts[3] = {8, 4, 2};
-    const double nt_pen[3] = {0.0, 0.02, 0.08};
+    const double nt_pen[3] = {0.0, 0.02, 0.1};
     for (int a = 0; a < 3; a++) {
         int nt = nts[a];
         if (f_nt && nt != f_nt) continue;
@@ -736,38 +749,28 @@ Choice choose(int N, int n_cb, int M) {
         for (int split = min_split; split <= 8; split++) {
             if (f_split && split != f_split) continue;
             if (split > min_split && n_cb / split < 4) break;
+            const int kb_per = (n_cb + split - 1) / split;
             long ctas = (long)groups * split;
             double score;
             if (split == 1 && (n_tiles + 7) / 8 >= 6 * kSMs) {
-                // very large N (lm_head): no split-K, many waves; four-tile groups measured best
-                // (117 us against 130 us for eight-tile groups on a persistent grid, 151936 x 2560)
-                // at batch 1-4; at batch 8 the activation table costs more per CTA and eight win
-                score = (nt == (M <= 4 ? 4 : 8)) ? 1.0 : (nt == 2 ? 0.8 : 0.9);
+                const int want = (M <= 4 && n_cb > 128) ? 4 : 8;
+                score = (nt == want) ? 1.0 : 0.9;
             } else {
-                long waves = (ctas + 3 * kSMs - 1) / (3 * kSMs);
+                const int smem = nt == 8 ? Cfg8::smem_bytes(kb_per, M) : nt == 4 ? Cfg4::smem_bytes(kb_per, M) : Cfg2::smem_bytes(kb_per, M);
+                int resident = kSmemPerSM / (smem + kSmemReserved);
+                resident = resident > 3 ? 3 : (resident < 1 ? 1 : resident);   // 72 registers x 288 threads: three at most
+                const double target = 0.8 * resident * kSMs;
+                long waves = (ctas + resident * kSMs - 1) / (resident * kSMs);
                 double per_wave = (double)ctas / (double)waves;
-                double dev = per_wave > 384.0 ? (per_wave - 384.0) / 384.0 : (384.0 - per_wave) / 384.0;
+                double dev = per_wave > target ? (per_wave - target) / target : (target - per_wave) / target;
                 if (ctas < kSMs) dev = 2.0 - (double)ctas / kSMs;   // fewer CTAs than SMs: parallelism first
-                score = -(dev + 0.03 * (double)(waves - 1) + nt_pen[a] + 0.005 * split);
+                score = -(dev + 0.05 * (double)(waves - 1) + nt_pen[a] + 0.01 * split + 0.005 * (kb_per < 16 ? 16 - kb_per : 0));
             }
             if (score > best_score) {
                 best_score = score;
                 best = Choice{nt, split, 0};
             }
         }
-    }
-    // Large matrices (>= 60 MB packed; the 70B-class projections): four-tile groups with a
-    // 2- or 3-way split measured best (28672 x 8192: 78 us against 88; 8192 x 28672: 82 against
-    // 85; 8192 x 8192: 27.9 against 29.9 for the rule above) unless N alone gives thousands of
-    // groups (the lm_head rule above).
-    if (!f_nt && !f_split && (long)n_tiles * n_cb * T16_UNIT >= (60L << 20) && (n_tiles + 7) / 8 < 6 * kSMs) {
-        int g4 = (n_tiles + 3) / 4;
-        int nt = 4, sp = g4 <= 256 ? 3 : 2;
-        if (M > 4) { nt = 8; sp = 3; }   // batch 5..8: the activation table costs more per CTA (94 us against 116)
-        if (sp < min_split) sp = min_split;
-        // only with enough tile groups to fill the GPU this way (the 55 MB shards of a 4-way
-        // tensor-parallel split ran 13 % slower with it than with the rule above)
-        if ((long)((n_tiles + nt - 1) / nt) * sp >= 256) best = Choice{nt, sp, 0};
     }
     int groups = (n_tiles + best.nt - 1) / best.nt;
     best.grid_x = groups;
@@ -893,7 +896,7 @@ int gemv_launch_ex(const void* x, int M, int K, long ldx, const void* wt16, cons
         p.slot_elems = peers->slot_elems; p.rank = peers->rank; p.world = peers->world;
     }
     int rc;
-    if (c.nt == 8) rc = launch_gemv<8, 4, 3>(p, c.grid_x, flags, stream);
+    if (c.nt == 8) rc = launch_gemv<8, 8, 2>(p, c.grid_x, flags, stream);
     else if (c.nt == 4) rc = launch_gemv<4, 8, 3>(p, c.grid_x, flags, stream);
     else rc = launch_gemv<2, 8, 4>(p, c.grid_x, flags, stream);
     if (rc != SX8_OK || p.world <= 1) return rc;
@@ -1003,7 +1006,7 @@ int gemv_launch_multi(const void* x, int M, int K, long ldx, int count, const vo
     }
     p.x = xp; p.ldx = ld; p.n_cb = n_cb; p.M = M; p.split = c.split; p.groups = g0;
     p.rank = 0; p.world = 1; p.slot_elems = 0;
-    if (c.nt == 8) return launch_gemv<8, 4, 3>(p, g0, flags, stream);   // one group per CTA: grid = groups
+    if (c.nt == 8) return launch_gemv<8, 8, 2>(p, g0, flags, stream);   // one group per CTA: grid = groups
     if (c.nt == 4) return launch_gemv<4, 8, 3>(p, g0, flags, stream);
     return launch_gemv<2, 8, 4>(p, g0, flags, stream);
 }
