@@ -756,9 +756,9 @@ def run_tp(args, rank, world, local_rank):
     torch.cuda.empty_cache()
 
     exchange = None
-    if world > 1 and args.allreduce in ("fused", "auto"):
+    if world > 1 and args.allreduce != "nccl":
         try:
-            exchange = tp.PeerExchange(8 * H, dev)
+            exchange = tp.PeerExchange(max(TP_BATCHES) * H, dev)
         except Exception as e:
             if rank == 0:
                 print("peer exchange unavailable, using NCCL:", repr(e)[:300], file=sys.stderr)
@@ -776,6 +776,17 @@ def run_tp(args, rank, world, local_rank):
         xl = xg[:, k0:k1].contiguous()
         y_nccl = tp.linear(xl, t_sh, flags=0).clone()
         y_fused = tp.linear(xl, t_sh, flags=0, exchange=exchange).clone() if exchange is not None else None
+        y_pull = None
+        if exchange is not None:    # the pull protocol: partial into the own slot, one kernel sums + residual + norm
+            part = exchange.partial_out(8, t_sh["N"])
+            tp.linear(xl, t_sh, out=part, flags=0, reduce=False)
+            h0 = torch.zeros(8, t_sh["N"], device=dev)
+            exchange.reduce_norm(h0, torch.ones(t_sh["N"], device=dev), 1e-5, torch.empty(8, t_sh["N"], dtype=torch.float16, device=dev))
+            y_pull = h0          # residual was zero: h holds the sum
+            exchange.partial_out(8, t_sh["N"]).zero_()   # keep the number of pull calls even (two halves)
+            exchange.reduce_norm(torch.zeros_like(h0), torch.ones(t_sh["N"], device=dev), 1e-5,
+                                 torch.empty(8, t_sh["N"], dtype=torch.float16, device=dev))
+            exchange.next()      # and of push calls
         y_full = torch.empty_like(y_nccl)
         if rank == 0:
             if full_layers[0]:
@@ -787,15 +798,18 @@ def run_tp(args, rank, world, local_rank):
         sc = y_full.abs().max()
         rel = lambda a: float(((a - y_full).abs().max() / sc).item())
         chk = torch.tensor([rel(y_nccl), rel(y_fused) if y_fused is not None else 0.0,
-                            float(((y_fused - y_nccl).abs().max() / sc).item()) if y_fused is not None else 0.0],
+                            float(((y_fused - y_nccl).abs().max() / sc).item()) if y_fused is not None else 0.0,
+                            rel(y_pull) if y_pull is not None else 0.0],
                            device=dev, dtype=torch.float64)
         dist.all_reduce(chk, op=dist.ReduceOp.MAX)
-        tp_check = {"nccl_vs_unsharded": chk[0].item(), "fused_vs_unsharded": chk[1].item() if exchange is not None else None,
-                    "fused_vs_nccl": chk[2].item() if exchange is not None else None,
-                    "what": "o projection of layer 0, batch 8: max |diff| / max |y| over all ranks"}
+        tp_check = {"nccl_vs_unsharded": chk[0].item(), "push_vs_unsharded": chk[1].item() if exchange is not None else None,
+                    "push_vs_nccl": chk[2].item() if exchange is not None else None,
+                    "pull_vs_unsharded": chk[3].item() if exchange is not None else None,
+                    "what": "o projection of layer 0, batch 8: max |diff| / max |y| over all ranks; push = GEMV epilogue "
+                            "stores into the peers' slots, pull = all-reduce + residual + RMSNorm kernel reading the peers' partials"}
 
-    def make_stack(M, lay, hd, ex):
-        return tp.TPStack(lay, hd, H, M, dev, exchange=ex, flags=flags)
+    def make_stack(M, lay, hd, ex, how="nccl"):
+        return tp.TPStack(lay, hd, H, M, dev, exchange=ex, flags=flags, reduce=how if ex is not None else "nccl")
 
     def time_stack(stack, M, steps):
         stack.reset(x0[M])
@@ -816,21 +830,24 @@ def run_tp(args, rank, world, local_rank):
     if world > 1:
         dist.barrier()
 
-    # ---- choose the reduction: fused peer-memory exchange or NCCL, whichever replays faster at batch 1
-    choice, trial = "nccl", {}
+    # ---- choose the reduction: NCCL, or one of the two peer-memory exchanges, whichever replays
+    #      faster (trial at every batch size of the step, max over ranks)
+    choice, trial = {M: "nccl" for M in TP_BATCHES}, {}
     if world > 1 and exchange is not None:
-        if args.allreduce == "fused":
-            choice = "fused"
-        else:
-            for name, ex in (("nccl", None), ("fused", exchange)):
-                sT = make_stack(1, layers, head, ex)
-                m_, gr = time_stack(sT, 1, 5)
+        modes = ["nccl", "pull", "push"] if args.allreduce == "auto" else [{"fused": "pull"}.get(args.allreduce, args.allreduce)]
+        for M in TP_BATCHES:
+            trial[str(M)] = {}
+            for how in modes:
+                if how == "push" and M > 8:
+                    continue
+                sT = make_stack(M, layers, head, None if how == "nccl" else exchange, how)
+                m_, gr = time_stack(sT, M, 5)
                 tt = torch.tensor([m_], device=dev, dtype=torch.float64)
                 dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-                trial[name] = round(float(tt.item()), 4)
+                trial[str(M)][how] = round(float(tt.item()), 4)
                 del gr, sT
-            choice = "fused" if trial["fused"] < trial["nccl"] else "nccl"
-    stacks = {M: make_stack(M, layers, head, exchange if (choice == "fused" and M <= 8) else None) for M in TP_BATCHES}
+            choice[M] = min(trial[str(M)], key=trial[str(M)].get)
+    stacks = {M: make_stack(M, layers, head, None if choice[M] == "nccl" else exchange, choice[M]) for M in TP_BATCHES}
     graphs = {}
     for M in TP_BATCHES:
         stacks[M].reset(x0[M])
@@ -941,9 +958,11 @@ def run_tp(args, rank, world, local_rank):
                       "note": "tp1 = the same layers and lm_head unsharded, timed on rank 0 alone in this process "
                               "before the sharded run"}
         cfg = workload_config("tp_decode_llama70b", args, world)
-        launch = {"allreduce": ("fused into the GEMV epilogue over peer memory (fp32, rank-ordered sum) at batch <= 8, NCCL above"
-                                if choice == "fused" else "nccl fp32 sum") + " after o and down; logits all-gather",
-                  "allreduce_trial_ms_batch1": trial or None, "cuda_graph": True, "pdl": not args.no_pdl}
+        names = {"nccl": "NCCL fp32 all-reduce, then residual + RMSNorm",
+                 "pull": "one kernel: every rank reads the peers' partials over NVLink, rank-ordered fp32 sum + residual + RMSNorm",
+                 "push": "GEMV epilogue stores tiles into the peers' slots, small kernel sums them, then residual + RMSNorm"}
+        launch = {"allreduce": {str(M): names[choice[M]] for M in TP_BATCHES}, "allreduce_choice": {str(M): choice[M] for M in TP_BATCHES},
+                  "allreduce_trial_ms": trial or None, "logits": "all-gather (NCCL)", "cuda_graph": True, "pdl": not args.no_pdl}
         line = {
             "metric": "sx8_decode_gemv_weight_GBps", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
@@ -971,7 +990,7 @@ def run_tp(args, rank, world, local_rank):
             "e2e": {"value": round(bytes_step / (e2e_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 3),
                     "steps": e2e_steps, "api": "tp.TPStack.step (eager), input activations from pinned host memory, "
-                                               "gathered logits back to pinned host memory; reduction: " + choice},
+                                               "gathered logits back to pinned host memory; reduction: " + "/".join(choice[M] for M in TP_BATCHES)},
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
@@ -1055,8 +1074,9 @@ def main():
     ap.add_argument("--no-decoder", action="store_true", help="skip the end-to-end decoder leg")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--e2e-steps", type=int, default=10)
-    ap.add_argument("--allreduce", default="auto", choices=["auto", "fused", "nccl"],
-                    help="row-parallel reduction: fused peer-memory exchange, NCCL, or whichever replays faster")
+    ap.add_argument("--allreduce", default="auto", choices=["auto", "pull", "push", "fused", "nccl"],
+                    help="row-parallel reduction: peer-memory exchange (pull = all-reduce + RMSNorm kernel, push = from "
+                         "the GEMV epilogue), NCCL, or whichever replays faster")
     ap.add_argument("--no-tp1", action="store_true", help="N > 1: skip the unsharded run on rank 0")
     ap.add_argument("--case", default=None, choices=["gemv", "gemm", "embed", "dequant", "quantize"],
                     help="time one kernel on one synthetic tensor (for profilers)")

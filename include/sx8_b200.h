@@ -231,6 +231,25 @@ int sx8_glue_attn_decode(const void* q_f16, const void* k_cache_f16, const void*
                          void* out_f16, void* scratch, size_t scratch_bytes, void* stream);
 int sx8_glue_silu_mul(const void* g_f32, const void* u_f32, long n, void* act_out_f16, void* stream);
 
+/* ---- row-parallel partial sums -> residual + RMSNorm, one kernel over peer memory -----------
+ * No counterpart in the reference (it has no multi-GPU code).  The consumer of a row-parallel
+ * linear of a tensor-parallel decode step: every rank has written its partial y_r (M, H) f32 --
+ * with sx8_gemv / sx8_gemm, straight into slot 0 of half (parity & 1) of ITS OWN exchange buffer
+ * (peers->data[rank] + (parity & 1) * world * slot_elems) -- and then calls this on the same
+ * stream.  The kernel publishes "my partial of this call is complete" to every peer, waits --
+ * bounded -- for the same from every peer, reads all partials from the peers' memory (plain loads
+ * over NVLink), sums them in rank order (identical bits on every rank), and does
+ *     h += sum;  x_out = f16(rmsnorm(h) * gamma)                       (as sx8_glue_add_rmsnorm).
+ * peers->parity selects the half of the buffers, advanced by the caller on every call (all ranks
+ * make the same calls in the same order); the calls are counted in device memory, so a CUDA
+ * graph that captured an even number of them can be replayed.  peers->flags[q] must hold at
+ * least 16 u32, zero before the first call (words 4, 5 and 8..15 are this protocol's, words 0..3
+ * sx8_gemv_allreduce's).  A wait that runs out sets bit 3 of the
+ * device error word; the exchange is then out of step and must be rebuilt (zero the flags on all
+ * ranks, barrier) before it is used again -- the same holds for bit 2 and sx8_gemv_allreduce.    */
+int sx8_glue_allreduce_add_rmsnorm(const sx8_peers_t* peers, int M, int H, void* h_f32, const void* gamma_f32,
+                                   float eps, void* x_out_f16, void* stream);
+
 /* Device-side error word of the bounded waits inside the pipelined kernels: 0 when no
  * wait ever ran out.  Reads back synchronously (cudaMemcpy) -- for tests and health
  * checks, not for the hot path.                                                      */

@@ -37,6 +37,7 @@ SIGNATURES = {
     "sx8_blocks_from_planes": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _l, _vp, _vp]),
     "sx8_planes_from_blocks": (_i, [_vp, _l, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "sx8_glue_add_rmsnorm": (_i, [_vp, _vp, _vp, _i, _i, ctypes.c_float, _vp, _vp]),
+    "sx8_glue_allreduce_add_rmsnorm": (_i, [_vp, _i, _i, _vp, _vp, ctypes.c_float, _vp, _vp]),
     "sx8_glue_rope_cache": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "sx8_glue_attn_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "sx8_glue_attn_decode": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, ctypes.c_float, _vp, _vp, _sz, _vp]),

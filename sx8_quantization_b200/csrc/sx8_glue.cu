@@ -100,6 +100,111 @@ add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ y, const flo
     }
 }
 
+// ------------------------------------------------------------------ all-reduce + residual + RMSNorm
+// The consumer of a row-parallel linear in a tensor-parallel decode step, as ONE kernel over peer
+// memory: every rank has written its partial y_r (M, H) f32 into its own exchange buffer (slot
+// `epoch & 1`); this kernel tells every peer "my partial of this epoch is complete", waits --
+// bounded -- for the same word from every peer, then reads all partials straight from the peers'
+// memory (plain loads over NVLink; no multicast, no bulk copies), sums them in rank order (so all
+// ranks compute the same bits), adds the sum to the residual stream and normalises.  One CTA per
+// batch row; a thread keeps its part of the row in registers, so every partial is read once.
+//
+// The epoch is a call counter kept in device memory (so that a CUDA graph that replays these
+// calls keeps counting): every CTA reads it at its start, the last CTA to finish advances it.
+// Buffer re-use: the caller alternates between two slots, so a rank writes a slot again two
+// calls later.  Before that it has passed this kernel's wait of the call in between, i.e. every
+// peer has started that call's kernel, which in stream order comes after the peer finished
+// reading the earlier call's partials.
+struct ArParams {
+    const float* part[8];       // rank q's partial (this call's slot) as mapped in this process
+    unsigned* flag_out[8];      // word [rank] of rank q's epoch array
+    const unsigned* flag_in;    // this rank's epoch array: word [q] is written by rank q
+    unsigned* ctr;              // this rank's call counter and the count of CTAs done with this call
+    int world, rank;
+};
+constexpr uint32_t kArSpinLimit = 1u << 22;
+
+__global__ void __launch_bounds__(kRmsThreads)
+allreduce_add_rmsnorm_kernel(ArParams a, float* __restrict__ h, const float* __restrict__ gamma, int H, float eps,
+                             __half* __restrict__ x) {
+    pdl_prologue();   // this rank's own GEMV has completed: its partial is in memory
+    __shared__ float red[32];
+    __shared__ unsigned s_epoch;
+    if (threadIdx.x == 0) s_epoch = *reinterpret_cast<volatile unsigned*>(a.ctr) + 1u;
+    __syncthreads();
+    const unsigned epoch = s_epoch;
+    if (blockIdx.x == 0 && (int)threadIdx.x < a.world) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.flag_out[threadIdx.x]), "r"(epoch) : "memory");
+    }
+    if ((int)threadIdx.x < a.world) {
+        int ok = 0;
+        for (uint32_t i = 0; i < kArSpinLimit; i++) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.flag_in + threadIdx.x) : "memory");
+            if ((int)(v - epoch) >= 0) { ok = 1; break; }
+        }
+        if (!ok) atomicOr(&g_sx8_error_flag, 8u);   // a peer never arrived: record it, sum what is there
+    }
+    __syncthreads();
+    const long row = blockIdx.x;
+    float4* hr = reinterpret_cast<float4*>(h + row * H);
+    const int n4 = H >> 2;
+    float4 v[kRmsPer];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < kRmsPer; j++) {
+        const int i = threadIdx.x + j * kRmsThreads;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < n4) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int q = 0; q < a.world; q++) {
+                const float4 w = __ldcv(reinterpret_cast<const float4*>(a.part[q] + row * H) + i);
+                acc.x += w.x; acc.y += w.y; acc.z += w.z; acc.w += w.w;
+            }
+            float4 t = hr[i];
+            t.x += acc.x; t.y += acc.y; t.z += acc.z; t.w += acc.w;
+            hr[i] = t;
+            v[j] = t;
+            ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
+        }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 32; w++) tot += red[w];
+    const float r = rsqrtf(tot / (float)H + eps);
+    const float4* gr = reinterpret_cast<const float4*>(gamma);
+    uint2* xr = reinterpret_cast<uint2*>(x + row * H);
+#pragma unroll
+    for (int j = 0; j < kRmsPer; j++) {
+        const int i = threadIdx.x + j * kRmsThreads;
+        if (i < n4) {
+            float4 g = gr[i];
+            __half2 lo = __floats2half2_rn(v[j].x * r * g.x, v[j].y * r * g.y);
+            __half2 hi = __floats2half2_rn(v[j].z * r * g.z, v[j].w * r * g.w);
+            uint2 o;
+            o.x = *reinterpret_cast<uint32_t*>(&lo);
+            o.y = *reinterpret_cast<uint32_t*>(&hi);
+            xr[i] = o;
+        }
+    }
+    // the last CTA to finish advances the call counter (every CTA has read it by then)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned prev = atomicAdd(a.ctr + 1, 1u);
+        if (prev == gridDim.x - 1) {
+            a.ctr[1] = 0u;
+            a.ctr[0] = epoch;
+            __threadfence();
+        }
+    }
+}
+
+
 // Rotary embedding (half-split convention) of q and k at position *pos; q -> f16 (B, hq, D);
 // k, v -> f16 cache rows (B, hkv, S, D) at position *pos.  One CTA per (sequence, head); heads
 // 0..hq-1 are q, hq..hq+hkv-1 are k, the rest v.  cos/sin: (S, D/2) f32.
@@ -325,6 +430,34 @@ silu_mul_kernel(const float* __restrict__ g, const float* __restrict__ u, long n
 }  // namespace sx8
 
 using namespace sx8;
+
+extern "C" int sx8_glue_allreduce_add_rmsnorm(const sx8_peers_t* peers, int M, int H, void* h, const void* gamma,
+                                              float eps, void* x_out, void* stream) {
+    SX8_REQUIRE(peers && h && gamma && x_out, "sx8_glue_allreduce_add_rmsnorm: null pointer");
+    SX8_REQUIRE(peers->world >= 1 && peers->world <= 8 && peers->rank >= 0 && peers->rank < peers->world,
+                "sx8_glue_allreduce_add_rmsnorm: bad rank/world (%d/%d, at most 8 ranks)", peers->rank, peers->world);
+    SX8_REQUIRE(M > 0 && H > 0 && (H % 4) == 0 && H <= 4 * kRmsThreads * kRmsPer,
+                "sx8_glue_allreduce_add_rmsnorm: need M>0 and H a multiple of 4 up to %d (got %d)", 4 * kRmsThreads * kRmsPer, H);
+    SX8_REQUIRE(peers->slot_elems >= (long)M * H, "sx8_glue_allreduce_add_rmsnorm: slot_elems (%ld) < M*H (%ld)",
+                peers->slot_elems, (long)M * H);
+    ArParams a;
+    memset(&a, 0, sizeof(a));
+    const long slot = (long)(peers->parity & 1) * peers->world * peers->slot_elems;
+    for (int q = 0; q < peers->world; q++) {
+        SX8_REQUIRE(peers->data[q] && peers->flags[q] && (reinterpret_cast<uintptr_t>(peers->data[q]) % 16) == 0 &&
+                        (reinterpret_cast<uintptr_t>(peers->flags[q]) % 4) == 0,
+                    "sx8_glue_allreduce_add_rmsnorm: null or misaligned peer pointer for rank %d", q);
+        a.part[q] = (const float*)peers->data[q] + slot;
+        a.flag_out[q] = (unsigned*)peers->flags[q] + 8 + peers->rank;
+    }
+    a.flag_in = (const unsigned*)peers->flags[peers->rank] + 8;
+    a.ctr = (unsigned*)peers->flags[peers->rank] + 4;
+    a.world = peers->world; a.rank = peers->rank;
+    cudaError_t e = launch_pdl(allreduce_add_rmsnorm_kernel, dim3((unsigned)M), dim3(kRmsThreads), 0, (cudaStream_t)stream, a,
+                               (float*)h, (const float*)gamma, H, eps, (__half*)x_out);
+    if (e != cudaSuccess) return cuda_fail(e, "launch(allreduce_add_rmsnorm_kernel)");
+    return SX8_OK;
+}
 
 extern "C" int sx8_glue_add_rmsnorm(void* h, const void* y, const void* gamma, int B, int H, float eps, void* x_out,
                                     void* stream) {

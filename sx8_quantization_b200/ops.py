@@ -365,6 +365,19 @@ def glue_add_rmsnorm(h, y, gamma, eps, x_out):
     return x_out
 
 
+def glue_allreduce_add_rmsnorm(peers, h, gamma, eps, x_out):
+    """Row-parallel consumer over peer memory: h (M,H) f32 += sum over ranks of the partials that
+    every rank wrote into its own exchange slot; x_out (M,H) f16 = rmsnorm(h) * gamma.  `peers`
+    is a _lib.Peers descriptor (tp.PeerExchange)."""
+    import ctypes
+    M, H = h.shape
+    with torch.cuda.device(h.device):
+        rc = _lib.lib().sx8_glue_allreduce_add_rmsnorm(ctypes.addressof(peers), M, H, h.data_ptr(), gamma.data_ptr(),
+                                                       float(eps), x_out.data_ptr(), _stream(h))
+    _lib.check(rc, "sx8_glue_allreduce_add_rmsnorm")
+    return x_out
+
+
 def glue_rope_cache(q, k, v, pos, cos_t, sin_t, hq, hkv, D, q_out, k_cache, v_cache):
     """q (B,hq*D), k, v (B,hkv*D) f32; caches (B,hkv,S,D) f16 written at position pos[0]."""
     B, S = q.shape[0], k_cache.shape[2]

@@ -52,14 +52,22 @@ def shard_tensor(t, style, rank, world):
 
 
 class PeerExchange:
-    """Symmetric receive buffers for the fused GEMV + all-reduce (sx8_gemv_allreduce): every
-    rank maps every other rank's buffer (torch symmetric memory over NVLink peer access) and
-    the GEMV epilogue stores its partial tiles straight into them.  NVLink multicast is not
-    used (plain peer stores only).
+    """Symmetric exchange buffers of a tensor-parallel group: every rank maps every other rank's
+    buffer (torch symmetric memory over NVLink peer access).  NVLink multicast is not used
+    (plain peer loads and stores only).  Two protocols share the buffers:
 
-    Calls alternate between two halves of the buffers ("parity"); all ranks must make the same
-    calls in the same order.  A CUDA graph that captures exchange calls must contain an even
-    number of them, so that a replay starts with the parity it was captured with."""
+      * sx8_gemv_allreduce (next()): the GEMV epilogue pushes its partial tiles into slot `rank`
+        of every peer's buffer and a small kernel sums the slots;
+      * sx8_glue_allreduce_add_rmsnorm (reduce_norm()): a rank writes its partial into slot 0 of
+        its OWN buffer (partial_out()), and the consumer kernel -- residual add + RMSNorm -- pulls
+        all partials from the peers' memory and sums them.
+
+    Calls alternate between two halves of the buffers; all ranks must make the same calls in the
+    same order.  A CUDA graph that captures exchange calls must contain an even number of them
+    per protocol, so that a replay starts with the half it was captured with.
+
+    After a bounded wait inside either kernel ran out (bit 2 or 3 of the device error word, see
+    check()), the ranks are out of step: the exchange must be rebuilt on all ranks."""
 
     def __init__(self, max_elems, device, group=None):
         import os
@@ -82,19 +90,49 @@ class PeerExchange:
         torch.distributed.barrier(self.group)
         self._desc = []
         for par in (0, 1):
-            d = _lib.Peers()
-            for q in range(self.world):
-                d.data[q] = int(self._hd.buffer_ptrs[q])
-                d.flags[q] = int(self._hf.buffer_ptrs[q])
-            d.slot_elems = self.slot_elems
-            d.rank, d.world, d.parity = self.rank, self.world, par
-            self._desc.append(d)
+            self._desc.append(self._make(par))
         self.calls = 0
+        self.pull_calls = 0
+
+    def _make(self, parity):
+        from . import _lib
+        d = _lib.Peers()
+        for q in range(self.world):
+            d.data[q] = int(self._hd.buffer_ptrs[q])
+            d.flags[q] = int(self._hf.buffer_ptrs[q])
+        d.slot_elems = self.slot_elems
+        d.rank, d.world, d.parity = self.rank, self.world, parity
+        return d
 
     def next(self):
         d = self._desc[self.calls & 1]
         self.calls += 1
         return d
+
+    # ---- pull protocol (sx8_glue_allreduce_add_rmsnorm)
+    def partial_out(self, M, N):
+        """The (M, N) f32 view a row-parallel linear writes its partial into for the next
+        reduce_norm() call: slot 0 of the current half of this rank's own buffer."""
+        if M * N > self.slot_elems:
+            raise ops.SX8Error("partial (%d, %d) exceeds the exchange slot (%d elements)" % (M, N, self.slot_elems))
+        off = (self.pull_calls & 1) * self.world * self.slot_elems
+        return self.data[off:off + M * N].view(M, N)
+
+    def reduce_norm(self, h, gamma, eps, x_out):
+        """h += sum over ranks of the partials written through partial_out(); x_out = rmsnorm(h)."""
+        d = self._desc[self.pull_calls & 1]
+        self.pull_calls += 1
+        return ops.glue_allreduce_add_rmsnorm(d, h, gamma, eps, x_out)
+
+    def check(self):
+        """Raise if a bounded wait of either exchange kernel ever ran out on this device (the sums
+        of that call were taken without the late rank's data, and later calls are out of step)."""
+        from . import _lib
+        flag = _lib.device_error_flag()
+        if flag & 0xC:
+            raise ops.SX8Error("tensor-parallel exchange timed out waiting for a peer (device error word 0x%x): "
+                               "results since then are invalid; rebuild the PeerExchange on all ranks" % flag)
+        return flag
 
 
 def linear(x, t, out=None, flags=0, group=None, reduce=True, exchange=None):
@@ -131,11 +169,22 @@ class TPStack:
 
     M <= 8 runs the decode GEMV (q|k|v and gate|up as one launch each), larger M the GEMM.
     layers: list of dicts name -> this rank's shard (shard_tensor); head: column shard or None.
-    exchange: a PeerExchange for the fused GEMV + all-reduce (M <= 8), else NCCL."""
+    How the partial sums of o and down are combined (reduce=):
+      "nccl"  all-reduce by NCCL, then sx8_glue_add_rmsnorm;
+      "pull"  (needs exchange) the linear writes its partial into this rank's exchange slot and
+              ONE kernel, sx8_glue_allreduce_add_rmsnorm, pulls all ranks' partials over NVLink,
+              sums them and applies residual + RMSNorm;
+      "push"  (needs exchange, M <= 8) sx8_gemv_allreduce pushes tiles into the peers' slots from
+              the GEMV epilogue and a small kernel sums them, then sx8_glue_add_rmsnorm."""
 
-    def __init__(self, layers, head, hidden, M, device, group=None, exchange=None, flags=0, eps=1e-5):
+    def __init__(self, layers, head, hidden, M, device, group=None, exchange=None, flags=0, eps=1e-5, reduce=None):
         self.layers, self.head, self.M, self.dev = layers, head, int(M), device
         self.group, self.exchange, self.flags, self.eps = group, exchange, flags, eps
+        self.reduce = reduce if reduce is not None else ("push" if exchange is not None else "nccl")
+        if self.reduce != "nccl" and exchange is None:
+            raise ops.SX8Error("reduce=%r needs a PeerExchange" % (self.reduce,))
+        if self.reduce == "pull" and M * hidden > exchange.slot_elems:
+            self.reduce = "nccl"            # the partial does not fit the exchange slot
         self.world = torch.distributed.get_world_size(group) if torch.distributed.is_initialized() else 1
         o = layers[0]["o"]
         if o.get("global") is None or o["global"][1] == o["K"]:     # unsharded tensors: one rank's whole model
@@ -165,9 +214,16 @@ class TPStack:
         self.packed_bytes = sum(30 * t["N"] * t["n_cb"] for L in layers for t in L.values()) + \
             (30 * head["N"] * head["n_cb"] if head is not None else 0)
 
-    def _row(self, x, t, out):
-        return linear(x, t, out=out, flags=self.flags, group=self.group,
-                      exchange=self.exchange if self.world > 1 else None, reduce=self.world > 1)
+    def _row_norm(self, x, t, out):
+        """Row-parallel linear, sum over ranks, h += sum, self.x = rmsnorm(h)."""
+        if self.world > 1 and self.reduce == "pull":
+            part = self.exchange.partial_out(self.M, t["N"])
+            linear(x, t, out=part, flags=self.flags, group=self.group, reduce=False)
+            self.exchange.reduce_norm(self.h, self.gamma, self.eps, self.x)
+            return
+        linear(x, t, out=out, flags=self.flags, group=self.group,
+               exchange=self.exchange if (self.world > 1 and self.reduce == "push") else None, reduce=self.world > 1)
+        ops.glue_add_rmsnorm(self.h, out, self.gamma, self.eps, self.x)
 
     def step(self):
         """One pass over all layers from the current self.x / self.h; leaves the gathered logits
@@ -183,8 +239,7 @@ class TPStack:
                     ops.gemm(self.x, L[nm]["wt16"], L[nm]["bases"], L[nm]["scales"], L[nm]["N"], L[nm]["K"],
                              L[nm]["n_cb"], out=self.kv)
             self.attn.copy_(q)                                        # stand-in for attention over the cache
-            self._row(self.attn, L["o"], self.y_o)
-            ops.glue_add_rmsnorm(self.h, self.y_o, self.gamma, self.eps, self.x)
+            self._row_norm(self.attn, L["o"], self.y_o)
             if self.multi is not None:
                 g, u = self.multi[i][1](self.x, flags=self.flags)
             else:
@@ -193,8 +248,7 @@ class TPStack:
                 u = ops.gemm(self.x, L["up"]["wt16"], L["up"]["bases"], L["up"]["scales"], L["up"]["N"], L["up"]["K"],
                              L["up"]["n_cb"], out=self.u)
             ops.glue_silu_mul(g, u, self.act)
-            self._row(self.act, L["down"], self.y_d)
-            ops.glue_add_rmsnorm(self.h, self.y_d, self.gamma, self.eps, self.x)
+            self._row_norm(self.act, L["down"], self.y_d)
         if self.head is not None:
             t = self.head
             if M <= 8:

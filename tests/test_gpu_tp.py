@@ -1,5 +1,7 @@
-"""Two-GPU check of the fused row-parallel GEMV + all-reduce (peer-memory exchange) against
-the NCCL path and the CPU oracle.  Skipped on boxes with fewer than two GPUs."""
+"""Two-GPU check of the two peer-memory exchanges of a row-parallel linear -- the GEMV fused
+with its all-reduce (tiles pushed into the peers' slots) and the all-reduce + residual + RMSNorm
+kernel (partials pulled from the peers) -- against the NCCL path and the CPU oracle.  Skipped
+on boxes with fewer than two GPUs."""
 import os
 import sys
 
@@ -31,20 +33,32 @@ def _worker(rank, world, port, out):
     r = tp.shard_tensor(t, "row", rank, world)
     k0, k1 = r["k_range"]
     ex = tp.PeerExchange(8 * N, dev)
-    res = []
+    res, pull_err = [], []
     for it, M in enumerate([1, 8, 3, 8]):          # several calls: both parities, counter re-arming
         x = orc.synth_x(M, K, 90 + it)
         xl = torch.from_numpy(np.ascontiguousarray(x[:, k0:k1])).to(dev)
         y_fused = tp.linear(xl, r, exchange=ex).clone()
         y_nccl = tp.linear(xl, r).clone()
+        # the pull protocol: partial into this rank's own slot, one kernel sums + residual + RMSNorm
+        part = ex.partial_out(M, N)
+        tp.linear(xl, r, out=part, reduce=False)
+        h = torch.full((M, N), 0.5, device=dev)
+        xo = torch.empty(M, N, dtype=torch.float16, device=dev)
+        ex.reduce_norm(h, torch.ones(N, device=dev), 1e-5, xo)
+        torch.cuda.synchronize()
+        pull_sum = (h - 0.5)
+        pull_err.append(float(((pull_sum - y_nccl).abs().max() / y_nccl.abs().max()).item()))
+        x_ref = (h * torch.rsqrt((h * h).mean(dim=1, keepdim=True) + 1e-5)).half()
+        pull_err.append(float((xo.float() - x_ref.float()).abs().max().item() / x_ref.float().abs().max().item()))
         torch.cuda.synchronize()
         ref = orc.matmul_ref(x, orc.dequant_d64(qt, bi))
         res.append((y_fused.cpu().numpy(), y_nccl.cpu().numpy(), ref))
     flag = _lib.device_error_flag()
+    ex.check()
     dist.barrier()
     if rank == 0:
         np.save(out, np.array([flag] + [float(np.abs(a - c).max() / np.abs(c).max()) for a, b, c in res]
-                              + [float(np.abs(a - b).max() / np.abs(c).max()) for a, b, c in res]))
+                              + [float(np.abs(a - b).max() / np.abs(c).max()) for a, b, c in res] + pull_err))
     dist.barrier()
     os._exit(0)
 
@@ -59,3 +73,5 @@ def test_fused_allreduce_two_gpus(tmp_path):
     assert r[0] == 0                        # no bounded wait ran out
     assert (r[1:5] <= 2e-3).all()           # fused result vs the reference comparator
     assert (r[5:9] <= 1e-5).all()           # fused vs NCCL: same partials, different summation order
+    assert len(r) == 17 and (r[9:17:2] <= 1e-5).all()    # pull protocol: the sum against NCCL's
+    assert (r[10:17:2] <= 2e-3).all()       # and its normalised f16 output against rmsnorm of the summed residual
