@@ -941,6 +941,9 @@ def run_tp(args, rank, world, local_rank):
     bytes_step = float(tb.item()) * len(TP_BATCHES)
     value = bytes_step / (ms_per_step * 1e-3) / 1e9
     flag = _lib.device_error_flag()
+    if exchange is not None and flag & 0xC and rank == 0:
+        print("WARNING: a tensor-parallel exchange wait timed out (device error word 0x%x): results invalid" % flag,
+              file=sys.stderr)
     if rank == 0:
         clocks = sampler.summary(t0, t1)
         sampler.stop()

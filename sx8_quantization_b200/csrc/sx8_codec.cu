@@ -205,10 +205,10 @@ quantize_kernel(const void* __restrict__ w_, long out_f, long in_f, long ldw, in
     mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
 
     float d = fmaxf(__fsub_rn(mx, mn), 1e-10f);
-    float q = __fdiv_rn(d, 4.0f);
+    float q = __fmul_rn(d, 0.25f);          // d / 4 exactly
     float best = __int_as_float(0x7F800000);
     int best_r = 0;
-    uint32_t best_hi = 0, best_lo = 0;
+    float best_pa = 0.f, best_pb = 0.f;     // the winner's levels, four per float: c0 + 64 c1 + 4096 c2 + 262144 c3
 #pragma unroll
     for (int r = 0; r < 4; r++) {
         float lo = (r == 2) ? __fsub_rn(mx, q) : ((r == 3) ? __fadd_rn(mn, q) : mn);
@@ -216,18 +216,23 @@ quantize_kernel(const void* __restrict__ w_, long out_f, long in_f, long ldw, in
         const float kInv63 = 1.0f / 63.0f;   // rounded to float32 once, as torch does on the host
         float step = CUDA_ARITH ? fmaxf(__fmul_rn(__fsub_rn(hi, lo), kInv63), 1e-10f)
                                 : fmaxf(__fdiv_rn(__fsub_rn(hi, lo), 63.0f), 1e-10f);
-        float e2[8];
-        uint32_t phi = 0, plo = 0;
+        // round((x - lo) / step) with the IEEE quotient, eight times per range: the quotient is taken
+        // as (x - lo) * (1 / step) -- within 1.5 * 2^-23 relative of the exact one, so for quotients
+        // that matter (the result is clamped to 0..63) within 1.2e-5 absolute of the IEEE-rounded
+        // one -- and rounded; only when it lies within 2e-5 of a rounding boundary k + 0.5 can the
+        // two roundings differ, and then the IEEE division is done (about one weight in 10,000).
+        const float rstep = __frcp_rn(step);
+        float e2[8], c[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            float c = rintf(__fdiv_rn(__fsub_rn(x[i], lo), step));
-            c = fminf(fmaxf(c, 0.0f), 63.0f);
-            int ci = (int)c;
-            float rec = __fadd_rn(lo, __fmul_rn(step, (float)ci));
+            const float a = __fsub_rn(x[i], lo);
+            float ci = rintf(__fmul_rn(a, rstep));
+            if (fabsf(__fsub_rn(__fmul_rn(a, rstep), ci)) > 0.49998f) ci = rintf(__fdiv_rn(a, step));
+            ci = fminf(fmaxf(ci, 0.0f), 63.0f);
+            c[i] = ci;
+            float rec = __fadd_rn(lo, __fmul_rn(step, ci));
             float e = __fsub_rn(x[i], rec);
             e2[i] = __fmul_rn(e, e);
-            phi |= (uint32_t)(ci >> 2) << (4 * i);
-            plo |= (uint32_t)(ci & 3) << ((i >> 2) * 8 + (3 - (i & 3)) * 2);
         }
         float mse;
         if (CUDA_ARITH) {
@@ -238,13 +243,26 @@ quantize_kernel(const void* __restrict__ w_, long out_f, long in_f, long ldw, in
             float sum = 0.0f;
 #pragma unroll
             for (int i = 0; i < 8; i++) sum = __fadd_rn(sum, e2[i]);
-            mse = __fdiv_rn(sum, 8.0f);
+            mse = __fmul_rn(sum, 0.125f);   // sum / 8 exactly
         }
         if (mse < best) {
             best = mse;
             best_r = r;
-            best_hi = phi;
-            best_lo = plo;
+            // integers below 2^24: exact in float32
+            best_pa = fmaf(c[3], 262144.0f, fmaf(c[2], 4096.0f, fmaf(c[1], 64.0f, c[0])));
+            best_pb = fmaf(c[7], 262144.0f, fmaf(c[6], 4096.0f, fmaf(c[5], 64.0f, c[4])));
+        }
+    }
+    // the winner's levels -> the file's bit layout (ref quantize...py:148-167): levels_hi nibble i of
+    // the 32-bit word, levels_lo pair i at bit (i >> 2) * 8 + (3 - (i & 3)) * 2 of the 16-bit word
+    uint32_t best_hi = 0, best_lo = 0;
+    {
+        const uint32_t pa = (uint32_t)best_pa, pb = (uint32_t)best_pb;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint32_t ci = ((i < 4 ? pa : pb) >> (6 * (i & 3))) & 63u;
+            best_hi |= (ci >> 2) << (4 * i);
+            best_lo |= (ci & 3u) << ((i >> 2) * 8 + (3 - (i & 3)) * 2);
         }
     }
     uint32_t cfg = (uint32_t)best_r << (2 * sb);

@@ -522,41 +522,73 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                         wb.z = hfma2_u32(V3 & 0x00FF00FFu, mB, aB);
                         wb.w = hfma2_u32((V3 >> 8) & 0x00FF00FFu, mB, aB);
                         // w = dmin + base * (...)   (fp16 pairs; base = (dmax-dmin)*0.25*0.015873*2^9)
-                        float bAf = (h2f_bits((uint16_t)(H0 >> 16)) - h2f_bits((uint16_t)H0)) * kBase;
-                        float bBf = (h2f_bits((uint16_t)(H1 >> 16)) - h2f_bits((uint16_t)H1)) * kBase;
-                        // A block whose range exceeds ~32000 (possible in the format, absent from real
-                        // weights) would overflow the fp16 step: move a factor 64 from it to the levels.
-                        // (What remains: the step is rounded to fp16 before the multiply, so a weight
-                        // within 0.05 % of the fp16 maximum, 65504, can still round to infinity.)
-                        if (bAf > 60000.0f) {
-                            bAf *= 0.015625f;
-                            wa.x = hfma2_u32(wa.x, 0x54005400u, 0u); wa.y = hfma2_u32(wa.y, 0x54005400u, 0u);
-                            wa.z = hfma2_u32(wa.z, 0x54005400u, 0u); wa.w = hfma2_u32(wa.w, 0x54005400u, 0u);
-                        }
-                        if (bBf > 60000.0f) {
-                            bBf *= 0.015625f;
-                            wb.x = hfma2_u32(wb.x, 0x54005400u, 0u); wb.y = hfma2_u32(wb.y, 0x54005400u, 0u);
-                            wb.z = hfma2_u32(wb.z, 0x54005400u, 0u); wb.w = hfma2_u32(wb.w, 0x54005400u, 0u);
-                        }
-                        __half2 bA2 = __float2half2_rn(bAf), bB2 = __float2half2_rn(bBf);
-                        uint32_t bA = *reinterpret_cast<uint32_t*>(&bA2), bB = *reinterpret_cast<uint32_t*>(&bB2);
-                        uint32_t loA = dup_lo(H0), loB = dup_lo(H1);
-                        wa.x = hfma2_u32(wa.x, bA, loA); wa.y = hfma2_u32(wa.y, bA, loA);
-                        wa.z = hfma2_u32(wa.z, bA, loA); wa.w = hfma2_u32(wa.w, bA, loA);
-                        wb.x = hfma2_u32(wb.x, bB, loB); wb.y = hfma2_u32(wb.y, bB, loB);
-                        wb.z = hfma2_u32(wb.z, bB, loB); wb.w = hfma2_u32(wb.w, bB, loB);
+                        const float loAf = h2f_bits((uint16_t)H0), hiAf = h2f_bits((uint16_t)(H0 >> 16));
+                        const float loBf = h2f_bits((uint16_t)H1), hiBf = h2f_bits((uint16_t)(H1 >> 16));
+                        float bAf = (hiAf - loAf) * kBase;
+                        float bBf = (hiBf - loBf) * kBase;
                         // PCA: + (c0 * 2^-10) * (1024*s0*b0[t]) + (c1 * 2^-10) * (1024*s1*b1[t])
                         uint32_t ccA = hfma2_u32((H2 & 0x000F000Fu) ^ 0x64086408u, 0x14001400u, 0xBC08BC08u);
                         uint32_t ccB = hfma2_u32(((H2 >> 4) & 0x000F000Fu) ^ 0x64086408u, 0x14001400u, 0xBC08BC08u);
-                        uint32_t c0A = dup_lo(ccA), c1A = dup_hi(ccA), c0B = dup_lo(ccB), c1B = dup_hi(ccB);
-                        wa.x = hfma2_u32(c0A, s0.x, wa.x); wa.y = hfma2_u32(c0A, s0.y, wa.y);
-                        wa.z = hfma2_u32(c0A, s0.z, wa.z); wa.w = hfma2_u32(c0A, s0.w, wa.w);
-                        wa.x = hfma2_u32(c1A, s1.x, wa.x); wa.y = hfma2_u32(c1A, s1.y, wa.y);
-                        wa.z = hfma2_u32(c1A, s1.z, wa.z); wa.w = hfma2_u32(c1A, s1.w, wa.w);
-                        wb.x = hfma2_u32(c0B, s0.x, wb.x); wb.y = hfma2_u32(c0B, s0.y, wb.y);
-                        wb.z = hfma2_u32(c0B, s0.z, wb.z); wb.w = hfma2_u32(c0B, s0.w, wb.w);
-                        wb.x = hfma2_u32(c1B, s1.x, wb.x); wb.y = hfma2_u32(c1B, s1.y, wb.y);
-                        wb.z = hfma2_u32(c1B, s1.z, wb.z); wb.w = hfma2_u32(c1B, s1.w, wb.w);
+                        // A block with an endpoint of magnitude >= 32768 (possible in the format, absent from
+                        // real weights) can hold weights next to the fp16 maximum; formed in fp16 arithmetic
+                        // (step rounded to fp16 first) such a weight could round to infinity.  Those blocks
+                        // form their weights in float32, as the reference's decode does
+                        // (ref cuda/sx8_fused_wmma.cu:83-96), and round once.
+                        auto wide = [&](uint4& w, float base, float lo, uint32_t cc) {
+                            const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&cc));   // {c0, c1} * 2^-10
+                            uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
+                            const uint32_t* p0 = reinterpret_cast<const uint32_t*>(&s0);
+                            const uint32_t* p1 = reinterpret_cast<const uint32_t*>(&s1);
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+                                const float2 l = __half22float2(*reinterpret_cast<const __half2*>(&wp[i]));
+                                const float2 a0 = __half22float2(*reinterpret_cast<const __half2*>(&p0[i]));
+                                const float2 a1 = __half22float2(*reinterpret_cast<const __half2*>(&p1[i]));
+                                const float v0 = fmaf(c.y, a1.x, fmaf(c.x, a0.x, fmaf(base, l.x, lo)));
+                                const float v1 = fmaf(c.y, a1.y, fmaf(c.x, a0.y, fmaf(base, l.y, lo)));
+                                __half2 h = __floats2half2_rn(v0, v1);
+                                wp[i] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                        };
+                        const bool wideA = fmaxf(fabsf(loAf), fabsf(hiAf)) >= 32768.0f;
+                        const bool wideB = fmaxf(fabsf(loBf), fabsf(hiBf)) >= 32768.0f;
+                        if (wideA) {
+                            wide(wa, bAf, loAf, ccA);
+                        } else {
+                            // a range above ~29,500 would overflow the fp16 step: move a factor 64 from it to the levels
+                            if (bAf > 60000.0f) {
+                                bAf *= 0.015625f;
+                                wa.x = hfma2_u32(wa.x, 0x54005400u, 0u); wa.y = hfma2_u32(wa.y, 0x54005400u, 0u);
+                                wa.z = hfma2_u32(wa.z, 0x54005400u, 0u); wa.w = hfma2_u32(wa.w, 0x54005400u, 0u);
+                            }
+                            __half2 bA2 = __float2half2_rn(bAf);
+                            const uint32_t bA = *reinterpret_cast<uint32_t*>(&bA2), loA = dup_lo(H0);
+                            wa.x = hfma2_u32(wa.x, bA, loA); wa.y = hfma2_u32(wa.y, bA, loA);
+                            wa.z = hfma2_u32(wa.z, bA, loA); wa.w = hfma2_u32(wa.w, bA, loA);
+                            const uint32_t c0A = dup_lo(ccA), c1A = dup_hi(ccA);
+                            wa.x = hfma2_u32(c0A, s0.x, wa.x); wa.y = hfma2_u32(c0A, s0.y, wa.y);
+                            wa.z = hfma2_u32(c0A, s0.z, wa.z); wa.w = hfma2_u32(c0A, s0.w, wa.w);
+                            wa.x = hfma2_u32(c1A, s1.x, wa.x); wa.y = hfma2_u32(c1A, s1.y, wa.y);
+                            wa.z = hfma2_u32(c1A, s1.z, wa.z); wa.w = hfma2_u32(c1A, s1.w, wa.w);
+                        }
+                        if (wideB) {
+                            wide(wb, bBf, loBf, ccB);
+                        } else {
+                            if (bBf > 60000.0f) {
+                                bBf *= 0.015625f;
+                                wb.x = hfma2_u32(wb.x, 0x54005400u, 0u); wb.y = hfma2_u32(wb.y, 0x54005400u, 0u);
+                                wb.z = hfma2_u32(wb.z, 0x54005400u, 0u); wb.w = hfma2_u32(wb.w, 0x54005400u, 0u);
+                            }
+                            __half2 bB2 = __float2half2_rn(bBf);
+                            const uint32_t bB = *reinterpret_cast<uint32_t*>(&bB2), loB = dup_lo(H1);
+                            wb.x = hfma2_u32(wb.x, bB, loB); wb.y = hfma2_u32(wb.y, bB, loB);
+                            wb.z = hfma2_u32(wb.z, bB, loB); wb.w = hfma2_u32(wb.w, bB, loB);
+                            const uint32_t c0B = dup_lo(ccB), c1B = dup_hi(ccB);
+                            wb.x = hfma2_u32(c0B, s0.x, wb.x); wb.y = hfma2_u32(c0B, s0.y, wb.y);
+                            wb.z = hfma2_u32(c0B, s0.z, wb.z); wb.w = hfma2_u32(c0B, s0.w, wb.w);
+                            wb.x = hfma2_u32(c1B, s1.x, wb.x); wb.y = hfma2_u32(c1B, s1.y, wb.y);
+                            wb.z = hfma2_u32(c1B, s1.z, wb.z); wb.w = hfma2_u32(c1B, s1.w, wb.w);
+                        }
                     }
                     // 16-byte chunk c = 4r + t of the 128-byte row, XOR-swizzled with (row & 7)
                     const uint32_t c = (uint32_t)(r * 4 + t);

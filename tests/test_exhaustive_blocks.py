@@ -114,17 +114,11 @@ def test_gpu_kernels_on_every_block_kind():
     bound = np.abs(x.astype(np.float32)) @ np.abs(w).T + 1e-20
     y = ops.gemv(d(x), wt, bas, sca, N, K, NCB).cpu().numpy()
     assert np.isfinite(y).all() and (np.abs(y - ref) / bound).max() <= 2e-3
-    # The GEMM forms its fp16 operand in fp16 arithmetic: a weight within 0.05 % of the fp16
-    # maximum can round to infinity there (the step is rounded to fp16 first), so its case keeps
-    # the endpoints inside +-60000.
-    qt2 = dict(qt)
-    qt2["dmin"] = np.clip(qt["dmin"].astype(np.float32), -60000, 60000).astype(np.float16)
-    qt2["dmax"] = np.clip(qt["dmax"].astype(np.float32), -60000, 60000).astype(np.float16)
-    wt2 = d(orc.to_t16(qt2))
-    w = orc.dequant_d64(qt2, bi).astype(np.float32)
+    # The GEMM rounds weights to fp16 (as the reference's tensor-core path does); blocks with an
+    # endpoint of magnitude >= 32768 form them in float32 first, so the +-65504 blocks stay finite.
     xg = orc.synth_x(160, K, 78, scale=0.05)
     refg = xg.astype(np.float32) @ w.T
     boundg = np.abs(xg.astype(np.float32)) @ np.abs(w).T + 1e-20
-    yg = ops.gemm(d(xg), wt2, bas, sca, N, K, NCB).cpu().numpy()
+    yg = ops.gemm(d(xg), wt, bas, sca, N, K, NCB).cpu().numpy()
     assert np.isfinite(yg).all() and (np.abs(yg - refg) / boundg).max() <= 4e-3
     assert _lib.device_error_flag() == 0
