@@ -884,6 +884,16 @@ int launch_auto(const CUtensorMap& map, const tc::Params& p, cudaStream_t stream
     static const int force_mt = exp_env("SX8_GEMM_MT", 0);
     if (pair_mode == 3) return launch_tc_bn<1, 128, 2>(map, p, stream);
     static const int groups = exp_env("SX8_GEMM_GROUPS", 4);
+    if (pair_mode == 1 && p.M > 256) {
+        // Narrow matrices at a few hundred rows give the 512 x 256 pair tiles too few CTAs (1024 x 2560
+        // at M = 2048: 32 of 148 SMs; 2560 x 9728 at M = 512: 20).  The one-CTA 256 x 128 tiles, with
+        // their split-K over a cluster of two when at most 74 tiles exist, then fill the GPU in one
+        // wave and halve the decode work per CTA.
+        const long pair_ctas = 2L * ((p.N + 255) / 256) * ((p.M + 511) / 512);
+        const long one_tiles = (long)((p.N + 127) / 128) * ((p.M + 255) / 256);
+        const long one_ctas = (one_tiles <= 74 && p.n_cb >= 32) ? 2 * one_tiles : one_tiles;
+        if (pair_ctas < 100 && one_ctas <= 148 && one_ctas > pair_ctas) return launch_tc<2>(map, p, stream);
+    }
     if (pair_mode == 2 || (pair_mode == 1 && p.M > 256)) {
         if (groups == 2) return launch_tc_bn<2, 128, 2, 2>(map, p, stream);
         return launch_tc_bn<2, 128, 2, 4>(map, p, stream);

@@ -224,14 +224,43 @@ class SX8Decoder:
         self.pos.copy_(pos0)
         return self.graph
 
+    def prefill_captured(self, ids):
+        """prefill() replayed from a CUDA graph (one graph per prompt shape, captured on first
+        use): the glue between the linears is some forty framework kernels per layer, and at
+        small batch the host cannot issue them as fast as the GPU runs them."""
+        if not hasattr(self, "_pf_graphs"):
+            self._pf_graphs = {}
+        key = tuple(ids.shape)
+        ent = self._pf_graphs.get(key)
+        if ent is None:
+            static_ids = ids.clone()
+            side = torch.cuda.Stream(self.dev)
+            side.wait_stream(torch.cuda.current_stream(self.dev))
+            with torch.cuda.stream(side):
+                self.prefill(static_ids)            # warm-up: workspaces and allocator pools
+            torch.cuda.current_stream(self.dev).wait_stream(side)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                logits = self.prefill(static_ids)
+            ent = self._pf_graphs[key] = (g, static_ids, logits)
+        g, static_ids, logits = ent
+        static_ids.copy_(ids)
+        g.replay()
+        return logits
+
     def generate(self, ids, n_new, use_graph=True):
         """Greedy decode.  Returns (tokens (B, n_new) long on the device, timings dict in ms)."""
         e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
         if ids.shape[1] + n_new > self.S:
             raise ops.SX8Error("prompt + new tokens exceed max_seq")
+        if use_graph and tuple(ids.shape) not in getattr(self, "_pf_graphs", {}):
+            self.prefill_captured(ids)           # capture outside the timed region
         torch.cuda.synchronize(self.dev)
         e[0].record()
-        self.prefill(ids)
+        if use_graph:
+            self.prefill_captured(ids)
+        else:
+            self.prefill(ids)
         e[1].record()
         out = torch.empty(self.B, n_new, dtype=torch.long, device=self.dev)
         if use_graph and self.graph is None:

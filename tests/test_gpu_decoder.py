@@ -146,3 +146,20 @@ def test_glue_kernels_against_pytorch():
     act = torch.empty(B, 1000, dtype=torch.float16, device=dev)
     ops.glue_silu_mul(a, b2, act)
     assert (act.float() - F.silu(a) * b2).abs().max().item() <= 2e-3 * 4
+
+
+def test_captured_prefill_equals_eager_prefill():
+    """The prefill replayed from its CUDA graph gives the eager prefill's bits, for a second
+    prompt of the same shape too, and leaves the same cache and decode state."""
+    import torch
+    from sx8_quantization_b200.decoder import SX8Decoder
+    dec = SX8Decoder(SMALL, seed=5, max_seq=64, batch=2)
+    g = torch.Generator(device="cuda").manual_seed(8)
+    for _ in range(2):
+        ids = torch.randint(0, SMALL["vocab"], (2, 24), generator=g, device="cuda")
+        want = dec.prefill(ids).clone()
+        k_want, tok_want = dec.k_cache.clone(), dec.tok.clone()
+        dec.k_cache.zero_()
+        got = dec.prefill_captured(ids)
+        assert torch.equal(got, want)
+        assert torch.equal(dec.k_cache, k_want) and torch.equal(dec.tok, tok_want) and int(dec.pos.item()) == 24

@@ -191,3 +191,52 @@ def test_quantizer_search_against_the_reference_on_torch_cuda(shape):
     q_cpu = ops.quantize_blocks(w16, want_levels=True, arith="cpu")
     frac = (q_cpu["levels"] != q["levels"]).float().mean().item()
     assert frac < 1e-3
+
+
+@pytest.mark.gpu
+def test_reference_clone_model_fused_v44_on_a_transformers_model():
+    """The reference's own end-to-end check (ref scripts/integrate_fused_v44.py:119-167:
+    logits of the model with fp16 dequantised weights against the model whose Linear /
+    Embedding modules were swapped by clone_model_fused_v44, accepted at max|diff| / max|ref|
+    < 5e-2) restated on a small random-init Qwen3-shaped transformers model: the reference's
+    unmodified clone_model_fused_v44 installs SX8LinearV44 / SX8EmbeddingV44 built on the drop-in
+    modules; a 16-token prompt runs the M > 1 path (gemm_sx8_compact), a cached single-token
+    step the M == 1 path (decode1_v44)."""
+    transformers = pytest.importorskip("transformers")
+    m = import_reference_caller()
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+    torch.manual_seed(7)
+    cfg = Qwen3Config(vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=64, max_position_embeddings=128, tie_word_embeddings=False)
+    ref_model = Qwen3ForCausalLM(cfg).half().eval()
+    wd, bd = {}, {}
+    sd = ref_model.state_dict()
+    for name, p in list(ref_model.named_parameters()):
+        if p.dim() < 2:
+            continue
+        w16 = (p.detach().float() * (0.02 / max(1e-6, p.detach().float().std().item()))).half().numpy()
+        qt, bi = orc.quantize(w16, with_pca=True)
+        wd[name], bd[name] = qt, bi
+        sd[name] = torch.from_numpy(orc.dequant_d64(qt, bi))          # the reference model holds the decoded weights
+    ref_model.load_state_dict(sd)
+    import copy
+    fused = copy.deepcopy(ref_model)
+    ref_model = ref_model.cuda()
+    fused, n_rep = m.clone_model_fused_v44(fused, wd, bd)
+    assert n_rep == len(wd) == 2 * 7 + 2                                   # every Linear, the embedding and lm_head
+    fused = fused.cuda().eval()
+    assert type(fused.model.layers[0].self_attn.q_proj).__name__ == "SX8LinearV44"
+    assert type(fused.model.embed_tokens).__module__ == "sx8_quantization_b200.sx8_embed_v44"
+    ids = torch.randint(0, 1000, (1, 16), device="cuda")
+    with torch.no_grad():
+        a = ref_model(input_ids=ids, use_cache=True)
+        b = fused(input_ids=ids, use_cache=True)
+        rel = ((a.logits.float() - b.logits.float()).abs().max() / a.logits.float().abs().max()).item()
+        assert rel < 2e-2, rel                                             # the reference accepts 5e-2
+        nxt = a.logits[:, -1].argmax(-1, keepdim=True)
+        a1 = ref_model(input_ids=nxt, past_key_values=a.past_key_values, use_cache=True)
+        b1 = fused(input_ids=nxt, past_key_values=b.past_key_values, use_cache=True)
+        rel1 = ((a1.logits.float() - b1.logits.float()).abs().max() / a1.logits.float().abs().max()).item()
+        assert rel1 < 2e-2, rel1
+    from sx8_quantization_b200 import _lib
+    assert _lib.device_error_flag() == 0
