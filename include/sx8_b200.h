@@ -172,6 +172,30 @@ int sx8_quantize_blocks(const void* w, int w_is_f16, long out_f, long in_f, long
                         void* dmin_f16, void* dmax_f16, uint8_t* config, uint8_t* levels_hi,
                         uint8_t* levels_lo, uint8_t* levels_u8, int arith, void* stream);
 
+/* ---- quantizer: PCA correction stage ----------------------------------------------
+ * The three device passes of ref: scripts/quantize_qwen35_4b_sx8_v43_gpu.py:75-142
+ * (pca_correct_gpu), over the same w and the planes sx8_quantize_blocks wrote.  The residual
+ * E = w - (lo_sb + st_sb * level) (ref :84-97) is recomputed from w and the packed planes inside
+ * each kernel and never stored.  Between the passes the caller solves the n_cb symmetric
+ * 32 x 32 eigenproblems (the reference calls a batched SVD of E, whose right singular vectors
+ * are the eigenvectors of E^T E) and takes the per-column medians of |coef|: small library work.
+ *   sx8_pca_gram     gram (n_cb, 32, 32) f64 = sum over rows of E[n][kb]^T E[n][kb]; the sum
+ *                    is formed in float32 per chunk of rows and the chunks added in order in
+ *                    float64, so it does not depend on scheduling.  scratch: at least
+ *                    sx8_pca_gram_scratch_bytes(out_f, in_f) bytes, 16-byte aligned.
+ *   sx8_pca_project  coef (n_cb, 2, out_f) f32: coef[kb][j][n] = E[n][kb] . bases[kb][j]
+ *                    (bases (n_cb, 2, 32) f32, the file's layout)            (ref :127-128)
+ *   sx8_pca_pack     coeff (out_f * n_cb) u8, n-major: signed 4-bit round(coef / scale)
+ *                    clamped to -8..7, c0 in the low nibble                 (ref :131-139) */
+size_t sx8_pca_gram_scratch_bytes(long out_f, long in_f);
+int sx8_pca_gram(const void* w, int w_is_f16, long out_f, long in_f, long ldw, const void* dmin_f16,
+                 const void* dmax_f16, const uint8_t* config, const uint8_t* levels_hi,
+                 const uint8_t* levels_lo, double* gram, void* scratch, size_t scratch_bytes, void* stream);
+int sx8_pca_project(const void* w, int w_is_f16, long out_f, long in_f, long ldw, const void* dmin_f16,
+                    const void* dmax_f16, const uint8_t* config, const uint8_t* levels_hi,
+                    const uint8_t* levels_lo, const float* bases, float* coef, void* stream);
+int sx8_pca_pack(const float* coef, const float* scales, long out_f, int n_cb, uint8_t* coeff, void* stream);
+
 /* ---- file planes -> device layout -------------------------------------------------
  * sx8_repack_t16 replaces ref: scripts/sx8_decode1_v3.py:57-66 (make_tensors_v44) /
  * scripts/prepare_v44.py:35-79 (to_v44) as the load-time transform, done on the device.

@@ -30,6 +30,10 @@ SIGNATURES = {
     "sx8_dequant_planes": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _l, _l, _i, _i, _vp, _vp]),
     "sx8_dequant_t16": (_i, [_vp, _vp, _vp, _l, _l, _i, _i, _vp, _vp]),
     "sx8_quantize_blocks": (_i, [_vp, _i, _l, _l, _l, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "sx8_pca_gram_scratch_bytes": (_sz, [_l, _l]),
+    "sx8_pca_gram": (_i, [_vp, _i, _l, _l, _l, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "sx8_pca_project": (_i, [_vp, _i, _l, _l, _l, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "sx8_pca_pack": (_i, [_vp, _vp, _l, _i, _vp, _vp]),
     "sx8_t16_bytes": (_sz, [_l, _i]),
     "sx8_repack_t16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _l, _i, _vp, _vp]),
     "sx8_repack_v44": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _l, _i, _i, _vp, _vp, _vp]),

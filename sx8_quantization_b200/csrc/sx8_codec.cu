@@ -287,6 +287,251 @@ quantize_kernel(const void* __restrict__ w_, long out_f, long in_f, long ldw, in
     }
 }
 
+// ------------------------------------------------------------------ quantizer PCA stage
+// ref scripts/quantize_qwen35_4b_sx8_v43_gpu.py:75-142 (pca_correct_gpu): per block column kb
+// the residual E = w - (lo_sb + st_sb * level) of every row is formed, its top two right
+// singular vectors become the two bases of that column, the residual's coordinates on them the
+// per-block coefficients, their median magnitude / 3 the two scales.  The reference materialises
+// E (4 bytes per weight) and hands it to a batched SVD.  Here E never reaches HBM: the kernels
+// below recompute it from the weights and the packed planes wherever it is needed (34 bytes read
+// per block for f16 weights), the 32x32 Gram matrix E^T E per column is accumulated in registers,
+// and only the n_cb small symmetric eigenproblems are left to a library.
+//
+// One thread owns one 8-weight sub-block, as in the search kernel.  The residual uses the
+// reference's encode-side endpoints (ref :84-87): Q = d / 4, lo in {dmin, dmin, dmax - Q,
+// dmin + Q}, step in {d, Q, Q, max(d - 2 Q, 1e-10)} / 63, all float32 from the f16 endpoints.
+template <bool F16IN>
+__device__ __forceinline__ void pca_residual8(const void* __restrict__ w_, long n, int kb, int sb, long in_f, long ldw,
+                                              int n_cb, const uint16_t* __restrict__ dmin, const uint16_t* __restrict__ dmax,
+                                              const uint8_t* __restrict__ config, const uint8_t* __restrict__ hi,
+                                              const uint8_t* __restrict__ lo, float (&e)[8]) {
+    const long blk = n * n_cb + kb;
+    const long k0 = (long)kb * 32 + sb * 8;
+    const long nv = in_f - k0;
+    float x[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) x[i] = 0.0f;
+    if (F16IN) {
+        const __half* src = reinterpret_cast<const __half*>(w_) + n * ldw + k0;
+        if (nv >= 8 && ((reinterpret_cast<uintptr_t>(src) & 15) == 0)) {
+            uint4 raw = __ldg(reinterpret_cast<const uint4*>(src));
+            const __half* hh = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+            for (int i = 0; i < 8; i++) x[i] = __half2float(hh[i]);
+        } else {
+            for (int i = 0; i < 8; i++)
+                if (i < nv) x[i] = __half2float(src[i]);
+        }
+    } else {
+        const float* src = reinterpret_cast<const float*>(w_) + n * ldw + k0;
+        if (nv >= 8 && ((reinterpret_cast<uintptr_t>(src) & 15) == 0)) {
+            float4 a = __ldg(reinterpret_cast<const float4*>(src));
+            float4 b = __ldg(reinterpret_cast<const float4*>(src) + 1);
+            x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+            x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+        } else {
+            for (int i = 0; i < 8; i++)
+                if (i < nv) x[i] = src[i];
+        }
+    }
+    const float mn = h2f_bits(dmin[blk]), mx = h2f_bits(dmax[blk]);
+    const int s = (config[blk] >> (sb * 2)) & 3;
+    const uint32_t hi4 = *reinterpret_cast<const uint32_t*>(hi + blk * 16 + sb * 4);
+    const uint32_t lo2 = *reinterpret_cast<const uint16_t*>(lo + blk * 8 + sb * 2);
+    const float kInv63 = 1.0f / 63.0f;
+    const float d = fmaxf(__fsub_rn(mx, mn), 1e-10f);
+    const float q = __fmul_rn(d, 0.25f);
+    const float rlo = (s == 2) ? __fsub_rn(mx, q) : ((s == 3) ? __fadd_rn(mn, q) : mn);
+    const float span = (s == 0) ? d : ((s == 3) ? fmaxf(__fsub_rn(d, __fmul_rn(2.0f, q)), 1e-10f) : q);
+    const float step = __fmul_rn(span, kInv63);
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+        e[i] = __fsub_rn(x[i], __fadd_rn(rlo, __fmul_rn(step, (float)level_of(hi4, lo2, i))));
+}
+
+struct PcaArgs {
+    const void* w;
+    long out_f, in_f, ldw;
+    int n_cb;
+    const uint16_t *dmin, *dmax;
+    const uint8_t *config, *hi, *lo;
+};
+
+constexpr int kPcaKb = 4;        // block columns per CTA: 64 bytes of levels_hi and 256 of f16 weights per row
+constexpr int kPcaRows = 64;     // rows staged in shared memory between two accumulation phases
+constexpr int kPcaLd = 36;       // floats per staged row: 32 + 4, keeps every 4-float group 16-byte aligned
+
+// Partial Gram matrices.  grid (ceil(n_cb / 4), chunks), block 256.  Each CTA walks its chunk
+// of rows 64 at a time: the 256 threads form the residuals of 16 rows x 4 block columns x 4
+// sub-blocks per pass into shared memory, then every thread adds the 64 staged rows into its
+// 4 x 4 patch of one column's 32 x 32 matrix (two 16-byte shared loads per 16 multiply-adds).
+// Output: part[chunk][kb][32][32]; a second kernel adds the chunks in order, so the result does
+// not depend on scheduling.
+template <bool F16IN>
+__global__ void __launch_bounds__(256) pca_gram_kernel(PcaArgs a, long rows_per_cta, float* __restrict__ part) {
+    __shared__ __align__(16) float E[kPcaKb][kPcaRows][kPcaLd];
+    const int tid = threadIdx.x;
+    const int kb0 = blockIdx.x * kPcaKb;
+    const long r_begin = (long)blockIdx.y * rows_per_cta;
+    const long r_end = (r_begin + rows_per_cta < a.out_f) ? r_begin + rows_per_cta : a.out_f;
+    // loader role: (row_l, kb_l, sb) with sb fastest, so a row's 4 columns are one contiguous run
+    const int l_sb = tid & 3, l_kb = (tid >> 2) & 3, l_row = tid >> 4;
+    // accumulator role: column c_kb, patch rows i0..i0+3, patch columns j0..j0+3
+    const int c_kb = tid >> 6, i0 = ((tid & 63) >> 3) * 4, j0 = (tid & 7) * 4;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+    for (long r0 = r_begin; r0 < r_end; r0 += kPcaRows) {
+#pragma unroll
+        for (int p = 0; p < kPcaRows / 16; p++) {
+            const int rl = p * 16 + l_row;
+            const long n = r0 + rl;
+            const int kb = kb0 + l_kb;
+            float e[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) e[i] = 0.0f;
+            if (n < r_end && kb < a.n_cb)
+                pca_residual8<F16IN>(a.w, n, kb, l_sb, a.in_f, a.ldw, a.n_cb, a.dmin, a.dmax, a.config, a.hi, a.lo, e);
+            float4* dst = reinterpret_cast<float4*>(&E[l_kb][rl][l_sb * 8]);
+            dst[0] = make_float4(e[0], e[1], e[2], e[3]);
+            dst[1] = make_float4(e[4], e[5], e[6], e[7]);
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int r = 0; r < kPcaRows; r++) {
+            const float4 u = *reinterpret_cast<const float4*>(&E[c_kb][r][i0]);
+            const float4 v = *reinterpret_cast<const float4*>(&E[c_kb][r][j0]);
+            const float uu[4] = {u.x, u.y, u.z, u.w}, vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(uu[i], vv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    const int kb = kb0 + c_kb;
+    if (kb < a.n_cb) {
+        float* dst = part + ((long)blockIdx.y * a.n_cb + kb) * 1024;
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            *reinterpret_cast<float4*>(dst + (i0 + i) * 32 + j0) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+    }
+}
+
+// gram[kb][i][j] = sum over chunks, in chunk order (float64 accumulation, stored as float64 for
+// the eigen-solver).
+__global__ void __launch_bounds__(256) pca_gram_reduce_kernel(const float* __restrict__ part, int chunks, long n_elem,
+                                                              double* __restrict__ gram) {
+    long i = (long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= n_elem) return;
+    double s = 0.0;
+    for (int c = 0; c < chunks; c++) s += (double)part[(long)c * n_elem + i];
+    gram[i] = s;
+}
+
+// Coordinates of every block's residual on the two bases of its column:
+// coef[kb][j][n] = sum_t E[n][kb][t] * bases[kb][j][t].  Same tiling as the Gram kernel (grid
+// (ceil(n_cb / 4), ceil(out_f / 64)), block 256); the four sub-block partial sums meet through
+// two shuffles, and the results of a tile leave through shared memory so that each (kb, j) run
+// of 64 rows is one contiguous 256-byte store.
+template <bool F16IN>
+__global__ void __launch_bounds__(256) pca_project_kernel(PcaArgs a, const float* __restrict__ bases, float* __restrict__ coef) {
+    __shared__ float B[kPcaKb][64];
+    __shared__ float C[kPcaKb][2][kPcaRows];
+    const int tid = threadIdx.x;
+    const int kb0 = blockIdx.x * kPcaKb;
+    const long r0 = (long)blockIdx.y * kPcaRows;
+    {
+        const int kb = kb0 + (tid >> 6);
+        B[tid >> 6][tid & 63] = (kb < a.n_cb) ? bases[(long)kb * 64 + (tid & 63)] : 0.0f;
+    }
+    __syncthreads();
+    const int l_sb = tid & 3, l_kb = (tid >> 2) & 3, l_row = tid >> 4;
+#pragma unroll
+    for (int p = 0; p < kPcaRows / 16; p++) {
+        const int rl = p * 16 + l_row;
+        const long n = r0 + rl;
+        const int kb = kb0 + l_kb;
+        float e[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) e[i] = 0.0f;
+        if (n < a.out_f && kb < a.n_cb)
+            pca_residual8<F16IN>(a.w, n, kb, l_sb, a.in_f, a.ldw, a.n_cb, a.dmin, a.dmax, a.config, a.hi, a.lo, e);
+        float c0 = 0.0f, c1 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            c0 = fmaf(e[i], B[l_kb][l_sb * 8 + i], c0);
+            c1 = fmaf(e[i], B[l_kb][32 + l_sb * 8 + i], c1);
+        }
+        c0 += __shfl_xor_sync(0xFFFFFFFFu, c0, 1);
+        c1 += __shfl_xor_sync(0xFFFFFFFFu, c1, 1);
+        c0 += __shfl_xor_sync(0xFFFFFFFFu, c0, 2);
+        c1 += __shfl_xor_sync(0xFFFFFFFFu, c1, 2);
+        if (l_sb == 0) {
+            C[l_kb][0][rl] = c0;
+            C[l_kb][1][rl] = c1;
+        }
+    }
+    __syncthreads();
+    for (int o = tid; o < kPcaKb * 2 * kPcaRows; o += 256) {
+        const int rl = o & (kPcaRows - 1), j = (o >> 6) & 1, kl = o >> 7;
+        const int kb = kb0 + kl;
+        const long n = r0 + rl;
+        if (kb < a.n_cb && n < a.out_f) coef[((long)kb * 2 + j) * a.out_f + n] = C[kl][j][rl];
+    }
+}
+
+// coeff byte of block (n, kb) = (round(c0 / s0) clamped to -8..7) & 15 | the same of c1 << 4
+// (ref :131-139), written n-major.  32 x 32 tiles transposed through shared memory: reads run
+// along n, writes along kb.
+__global__ void __launch_bounds__(256) pca_pack_kernel(const float* __restrict__ coef, const float* __restrict__ scales,
+                                                       long out_f, int n_cb, uint8_t* __restrict__ coeff) {
+    __shared__ uint8_t T[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
+    const long n0 = (long)blockIdx.x * 32;
+    const int kb0 = blockIdx.y * 32;
+#pragma unroll
+    for (int p = 0; p < 4; p++) {
+        const int kl = p * 8 + ty;
+        const int kb = kb0 + kl;
+        const long n = n0 + tx;
+        uint8_t b = 0;
+        if (kb < n_cb && n < out_f) {
+            const float q0 = rintf(__fdiv_rn(coef[((long)kb * 2 + 0) * out_f + n], scales[kb * 2 + 0]));
+            const float q1 = rintf(__fdiv_rn(coef[((long)kb * 2 + 1) * out_f + n], scales[kb * 2 + 1]));
+            const int i0 = (int)fminf(fmaxf(q0, -8.0f), 7.0f), i1 = (int)fminf(fmaxf(q1, -8.0f), 7.0f);
+            b = (uint8_t)((i0 & 15) | ((i1 & 15) << 4));
+        }
+        T[kl][tx] = b;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int p = 0; p < 4; p++) {
+        const int nl = p * 8 + ty;
+        const long n = n0 + nl;
+        const int kb = kb0 + tx;
+        if (kb < n_cb && n < out_f) coeff[n * n_cb + kb] = T[tx][nl];
+    }
+}
+
+// Row chunks of the Gram kernel: enough CTAs to fill the machine a few times over, chunks a
+// multiple of the staging depth.
+static long pca_rows_per_cta(long out_f, int n_cb) {
+    const long groups = (n_cb + kPcaKb - 1) / kPcaKb;
+    long chunks = (148L * 8 + groups - 1) / groups;
+    const long max_chunks = (out_f + kPcaRows - 1) / kPcaRows;
+    if (chunks > max_chunks) chunks = max_chunks;
+    if (chunks < 1) chunks = 1;
+    long rows = (out_f + chunks - 1) / chunks;
+    return (rows + kPcaRows - 1) / kPcaRows * kPcaRows;
+}
+static long pca_chunks(long out_f, int n_cb) {
+    const long rows = pca_rows_per_cta(out_f, n_cb);
+    return (out_f + rows - 1) / rows;
+}
+
 // ------------------------------------------------------------------ repack to v4.4
 // ref scripts/prepare_v44.py:35-79.  One thread per destination block (kb, n), n
 // fastest, so the kb-major writes are contiguous across the warp.
@@ -575,6 +820,72 @@ extern "C" int sx8_quantize_blocks(const void* w, int w_is_f16, long out_f, long
     else          { if (cu) SX8_QLAUNCH(false, true); else SX8_QLAUNCH(false, false); }
 #undef SX8_QLAUNCH
     SX8_LAUNCH_CHECK("quantize_kernel");
+    return SX8_OK;
+}
+
+static bool pca_args(PcaArgs& a, const char* who, const void* w, int w_is_f16, long out_f, long in_f, long ldw,
+                     const void* dmin, const void* dmax, const uint8_t* config, const uint8_t* hi, const uint8_t* lo) {
+    if (!(w && dmin && dmax && config && hi && lo)) { set_error("%s: null pointer", who); return false; }
+    if (!(out_f > 0 && in_f > 0 && ldw >= in_f)) { set_error("%s: need out_f>0, in_f>0, ldw>=in_f (got %ld, %ld, %ld)", who, out_f, in_f, ldw); return false; }
+    if (!(aligned(w, w_is_f16 ? 2 : 4) && aligned(hi, 4) && aligned(lo, 2) && aligned(dmin, 2) && aligned(dmax, 2))) {
+        set_error("%s: misaligned pointer", who);
+        return false;
+    }
+    a.w = w; a.out_f = out_f; a.in_f = in_f; a.ldw = ldw;
+    a.n_cb = (int)((in_f + 31) / 32);
+    a.dmin = (const uint16_t*)dmin; a.dmax = (const uint16_t*)dmax;
+    a.config = config; a.hi = hi; a.lo = lo;
+    return true;
+}
+
+extern "C" size_t sx8_pca_gram_scratch_bytes(long out_f, long in_f) {
+    if (out_f <= 0 || in_f <= 0) return 0;
+    const int n_cb = (int)((in_f + 31) / 32);
+    return (size_t)pca_chunks(out_f, n_cb) * n_cb * 1024 * sizeof(float);
+}
+
+extern "C" int sx8_pca_gram(const void* w, int w_is_f16, long out_f, long in_f, long ldw, const void* dmin,
+                            const void* dmax, const uint8_t* config, const uint8_t* hi, const uint8_t* lo,
+                            double* gram, void* scratch, size_t scratch_bytes, void* stream) {
+    PcaArgs a;
+    if (!pca_args(a, "sx8_pca_gram", w, w_is_f16, out_f, in_f, ldw, dmin, dmax, config, hi, lo)) return SX8_E_INVALID;
+    SX8_REQUIRE(gram && scratch && aligned(gram, 8) && aligned(scratch, 16), "sx8_pca_gram: gram / scratch null or misaligned");
+    SX8_REQUIRE(scratch_bytes >= sx8_pca_gram_scratch_bytes(out_f, in_f), "sx8_pca_gram: scratch has %zu bytes, need %zu",
+                scratch_bytes, sx8_pca_gram_scratch_bytes(out_f, in_f));
+    const long rows = pca_rows_per_cta(out_f, a.n_cb), chunks = pca_chunks(out_f, a.n_cb);
+    SX8_REQUIRE(chunks <= 65535, "sx8_pca_gram: tensor too large for one launch");
+    dim3 grid((unsigned)((a.n_cb + kPcaKb - 1) / kPcaKb), (unsigned)chunks);
+    if (w_is_f16) pca_gram_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(a, rows, (float*)scratch);
+    else          pca_gram_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(a, rows, (float*)scratch);
+    SX8_LAUNCH_CHECK("pca_gram_kernel");
+    const long n_elem = (long)a.n_cb * 1024;
+    pca_gram_reduce_kernel<<<(unsigned)((n_elem + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const float*)scratch, (int)chunks, n_elem, gram);
+    SX8_LAUNCH_CHECK("pca_gram_reduce_kernel");
+    return SX8_OK;
+}
+
+extern "C" int sx8_pca_project(const void* w, int w_is_f16, long out_f, long in_f, long ldw, const void* dmin,
+                               const void* dmax, const uint8_t* config, const uint8_t* hi, const uint8_t* lo,
+                               const float* bases, float* coef, void* stream) {
+    PcaArgs a;
+    if (!pca_args(a, "sx8_pca_project", w, w_is_f16, out_f, in_f, ldw, dmin, dmax, config, hi, lo)) return SX8_E_INVALID;
+    SX8_REQUIRE(bases && coef && aligned(bases, 4) && aligned(coef, 4), "sx8_pca_project: bases / coef null or misaligned");
+    const long tiles = (out_f + kPcaRows - 1) / kPcaRows;
+    SX8_REQUIRE(tiles <= 65535, "sx8_pca_project: more than 65535 x 64 rows; split the tensor by rows");
+    dim3 grid((unsigned)((a.n_cb + kPcaKb - 1) / kPcaKb), (unsigned)tiles);
+    if (w_is_f16) pca_project_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(a, bases, coef);
+    else          pca_project_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(a, bases, coef);
+    SX8_LAUNCH_CHECK("pca_project_kernel");
+    return SX8_OK;
+}
+
+extern "C" int sx8_pca_pack(const float* coef, const float* scales, long out_f, int n_cb, uint8_t* coeff, void* stream) {
+    SX8_REQUIRE(coef && scales && coeff, "sx8_pca_pack: null pointer");
+    SX8_REQUIRE(out_f > 0 && n_cb > 0, "sx8_pca_pack: need out_f>0, n_cb>0 (got %ld, %d)", out_f, n_cb);
+    const long tn = (out_f + 31) / 32, tk = (n_cb + 31) / 32;
+    SX8_REQUIRE(tn <= 0x7FFFFFFFL && tk <= 65535, "sx8_pca_pack: tensor too large for one launch");
+    pca_pack_kernel<<<dim3((unsigned)tn, (unsigned)tk), 256, 0, (cudaStream_t)stream>>>(coef, scales, out_f, n_cb, coeff);
+    SX8_LAUNCH_CHECK("pca_pack_kernel");
     return SX8_OK;
 }
 

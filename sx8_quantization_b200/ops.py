@@ -282,6 +282,53 @@ def quantize_blocks(w, want_levels=False, arith="cuda"):
     return out
 
 
+def _pca_in(w, q):
+    if w.dtype not in (torch.float16, torch.float32) or not w.is_cuda or w.dim() != 2 or w.stride(1) != 1:
+        raise SX8Error("w must be a 2-D CUDA float16 or float32 tensor with unit inner stride")
+    return (w.data_ptr(), int(w.dtype == torch.float16), w.shape[0], w.shape[1], w.stride(0), q["dmin"].data_ptr(),
+            q["dmax"].data_ptr(), q["config"].data_ptr(), q["levels_hi"].data_ptr(), q["levels_lo"].data_ptr())
+
+
+def pca_gram(w, q):
+    """(n_cb, 32, 32) f64 Gram matrices of the quantisation residual of w against the planes q
+    (the result of quantize_blocks on the same w), one per block column."""
+    out_f, in_f = w.shape
+    n_cb = (in_f + 31) // 32
+    L = _lib.lib()
+    gram = torch.empty((n_cb, 32, 32), dtype=torch.float64, device=w.device)
+    nbytes = L.sx8_pca_gram_scratch_bytes(out_f, in_f)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=w.device)
+    with torch.cuda.device(w.device):
+        rc = L.sx8_pca_gram(*_pca_in(w, q), gram.data_ptr(), scratch.data_ptr(), nbytes, _stream(w))
+    _lib.check(rc, "sx8_pca_gram")
+    return gram
+
+
+def pca_project(w, q, bases):
+    """coef (n_cb, 2, out_f) f32: every block's residual on the two bases (n_cb, 2, 32) f32 of its column."""
+    out_f, in_f = w.shape
+    n_cb = (in_f + 31) // 32
+    if bases.dtype != torch.float32 or not bases.is_contiguous() or bases.numel() != n_cb * 64:
+        raise SX8Error("bases must be contiguous float32 with n_cb * 64 elements")
+    coef = torch.empty((n_cb, 2, out_f), dtype=torch.float32, device=w.device)
+    with torch.cuda.device(w.device):
+        rc = _lib.lib().sx8_pca_project(*_pca_in(w, q), bases.data_ptr(), coef.data_ptr(), _stream(w))
+    _lib.check(rc, "sx8_pca_project")
+    return coef
+
+
+def pca_pack(coef, scales):
+    """coef (n_cb, 2, out_f) f32, scales (n_cb, 2) f32 -> coeff bytes (out_f * n_cb,) u8, n-major."""
+    n_cb, _, out_f = coef.shape
+    if coef.dtype != torch.float32 or scales.dtype != torch.float32 or not coef.is_contiguous() or not scales.is_contiguous():
+        raise SX8Error("coef and scales must be contiguous float32")
+    coeff = torch.empty(out_f * n_cb, dtype=torch.uint8, device=coef.device)
+    with torch.cuda.device(coef.device):
+        rc = _lib.lib().sx8_pca_pack(coef.data_ptr(), scales.data_ptr(), out_f, n_cb, coeff.data_ptr(), _stream(coef))
+    _lib.check(rc, "sx8_pca_pack")
+    return coeff
+
+
 def repack_t16(dmin, dmax, config, coeff, hi, lo, out_f, n_cb):
     """n-major file planes -> T16 device blob, (ceil(out_f/16)*n_cb, 480) u8."""
     dev = hi.device

@@ -5,9 +5,12 @@ device.  Mirrors the per-tensor loop body of the reference's quantizer script
   1. per-block strategy search + bit packing  -- one CUDA kernel (sx8_quantize_blocks),
      bit-exact with the reference's torch functions (ref :22-69, :148-167);
   2. PCA correction (ref :75-142) -- batched over all column blocks: the reference
-     loops over kb in Python and calls a full SVD of the (N x 32) error slice each
-     time; here the 32 x 32 Gram matrices of all kb are formed with one batched matmul
-     and decomposed with one batched eigh.  The right-singular vectors of E are the
+     loops over kb in Python, materialises the (N x 32) error slice and calls a full SVD
+     of it each time; here three CUDA kernels recompute the error from the weights and
+     the packed planes where they need it (sx8_pca_gram: the 32 x 32 Gram matrices of all
+     kb; sx8_pca_project: the coordinates on the two bases; sx8_pca_pack: the signed
+     4-bit coefficient bytes), and torch decomposes the n_cb Gram matrices with one
+     batched eigh and takes the medians.  The right-singular vectors of E are the
      eigenvectors of E^T E, so the bases span the same subspace; their signs (and
      hence the coefficient signs) are arbitrary in both.  Functional parity only:
      neither implementation's coeff/bases bytes are reproducible across LAPACK builds;
@@ -21,11 +24,33 @@ import torch
 from . import ops
 
 
-def _pca_correct(w32, q, n_cb):
-    """w32: (out_f, n_cb*32) f32 zero-padded weights; q: planes from quantize_blocks with
-    levels.  Returns coeff (n_blk,) u8 n-major, bases (n_cb,64) f32, scales (n_cb,2) f32."""
+def _pca_correct(w, q, n_cb):
+    """w: (out_f, in_f) f16|f32 weights; q: planes from quantize_blocks on the same w.
+    Returns coeff (n_blk,) u8 n-major, bases (n_cb,64) f32, scales (n_cb,2) f32.
+
+    ref scripts/quantize_qwen35_4b_sx8_v43_gpu.py:75-142.  The residual passes are CUDA kernels
+    that recompute the residual from w and the planes (ops.pca_gram / pca_project / pca_pack);
+    torch solves the n_cb 32 x 32 symmetric eigenproblems in float64 (the reference's batched
+    SVD of the residual has the same right singular vectors) and takes the medians."""
+    out_f = w.shape[0]
+    dev = w.device
+    if out_f < 4:  # ref :100-103: slices with fewer than 4 blocks get zero bases
+        return (torch.zeros(out_f * n_cb, dtype=torch.uint8, device=dev),
+                torch.zeros(n_cb, 64, device=dev), torch.zeros(n_cb, 2, device=dev))
+    G = ops.pca_gram(w, q)                                                             # (n_cb, 32, 32) f64
+    _, vec = torch.linalg.eigh(G)
+    basis = vec[:, :, [-1, -2]].transpose(1, 2).float().contiguous()                   # (n_cb, 2, 32), top two
+    coef = ops.pca_project(w, q, basis)                                                # (n_cb, 2, N)
+    scales = (torch.median(coef.abs(), dim=2).values / 3.0).clamp(min=1e-10).contiguous()
+    coeff = ops.pca_pack(coef, scales)
+    return coeff, basis.reshape(n_cb, 64), scales
+
+
+def _pca_correct_torch(w32, q, n_cb):
+    """The same stage written with torch tensor operations only, materialising the residual as the
+    reference does; kept as the comparison for the kernels' tests.  w32: (out_f, n_cb*32) f32
+    zero-padded weights; q: planes from quantize_blocks(want_levels=True)."""
     out_f = w32.shape[0]
-    dev = w32.device
     dmin = q["dmin"].float().reshape(out_f, n_cb)
     dmax = q["dmax"].float().reshape(out_f, n_cb)
     d = (dmax - dmin).clamp(min=1e-10)
@@ -40,21 +65,16 @@ def _pca_correct(w32, q, n_cb):
         lo_sb = torch.gather(lo_j, 0, st)[0]
         st_sb = torch.gather(st_j, 0, st)[0]
         err[:, :, sb, :] -= lo_sb.unsqueeze(-1) + st_sb.unsqueeze(-1) * lv[:, :, sb, :]
-    del lv
     E = err.reshape(out_f, n_cb, 32).permute(1, 0, 2).contiguous()                     # (n_cb, N, 32)
-    del err
-    if out_f < 4:  # ref :100-103: slices with fewer than 4 blocks get zero bases
-        return (torch.zeros(out_f * n_cb, dtype=torch.uint8, device=dev),
-                torch.zeros(n_cb, 64, device=dev), torch.zeros(n_cb, 2, device=dev))
     G = torch.bmm(E.transpose(1, 2), E)                                                # (n_cb, 32, 32)
     _, vec = torch.linalg.eigh(G.double())
-    basis = vec[:, :, [-1, -2]].transpose(1, 2).float().contiguous()                   # (n_cb, 2, 32), top two
+    basis = vec[:, :, [-1, -2]].transpose(1, 2).float().contiguous()
     coef = torch.bmm(basis, E.transpose(1, 2))                                         # (n_cb, 2, N)
-    scales = (torch.median(coef.abs(), dim=2).values / 3.0).clamp(min=1e-10)           # (n_cb, 2)
+    scales = (torch.median(coef.abs(), dim=2).values / 3.0).clamp(min=1e-10)
     cq = (coef / scales.unsqueeze(-1)).round().clamp(-8, 7).to(torch.int16)
     byte = ((cq[:, 0] & 0xF) | ((cq[:, 1] & 0xF) << 4)).to(torch.uint8)                # (n_cb, N)
-    coeff = byte.t().contiguous().reshape(-1)                                          # n-major
-    return coeff, basis.reshape(n_cb, 64).contiguous(), scales.contiguous()
+    return {"E": E, "gram": G, "basis": basis, "coef": coef, "scales": scales.contiguous(),
+            "coeff": byte.t().contiguous().reshape(-1)}
 
 
 def quantize_tensor(w, with_pca=True, keep_planes=False):
@@ -62,16 +82,11 @@ def quantize_tensor(w, with_pca=True, keep_planes=False):
     {wt16, bases, scales, N, K, n_cb} and, with keep_planes, the n-major file planes
     under "planes"."""
     out_f, in_f = w.shape
-    q = ops.quantize_blocks(w, want_levels=with_pca)
+    q = ops.quantize_blocks(w)
     n_cb = q["n_cb"]
     dev = w.device
     if with_pca:
-        w32 = w.float()
-        if n_cb * 32 != in_f:
-            w32 = torch.nn.functional.pad(w32, (0, n_cb * 32 - in_f))
-        coeff, bases, scales = _pca_correct(w32, q, n_cb)
-        del w32
-        q.pop("levels")
+        coeff, bases, scales = _pca_correct(w, q, n_cb)
     else:
         coeff = torch.zeros(out_f * n_cb, dtype=torch.uint8, device=dev)
         bases = torch.zeros(n_cb, 64, device=dev)

@@ -153,3 +153,35 @@ def test_quantizer_pca_stage_functional_parity(shape):
     gram = np.einsum("kit,kjt->kij", B, B)
     assert np.abs(gram - np.eye(2)[None]).max() < 1e-4
     assert (bi_g["scales"] > 0).all()
+
+
+@pytest.mark.parametrize("shape,dtype", [((1024, 2560), "f16"), ((256, 1000), "f16"), ((130, 96), "f32"), ((4100, 264), "f32")])
+def test_quantizer_pca_kernels_against_torch_ops(shape, dtype):
+    """sx8_pca_gram / sx8_pca_project / sx8_pca_pack against the same stage written with torch
+    tensor operations on the materialised residual (ref scripts/quantize_qwen35_4b_sx8_v43_gpu.py
+    :84-97 residual, :127-139 projection and packing).  The Gram matrix and the projections are
+    float32 sums in another order, so they agree to float32 rounding of the sums, not bit for bit;
+    the packed bytes are compared with the projection's own values as input, where they must be
+    identical."""
+    from sx8_quantization_b200 import ops, quantizer
+    out_f, in_f = shape
+    w = quantizer.synth_weight_gpu(out_f, in_f, 88)
+    if dtype == "f32":
+        w = w.float() * 1.0001
+    q = ops.quantize_blocks(w, want_levels=True)
+    n_cb = q["n_cb"]
+    w32 = torch.nn.functional.pad(w.float(), (0, n_cb * 32 - in_f))
+    ref = quantizer._pca_correct_torch(w32, q, n_cb)
+    G = ops.pca_gram(w, q)
+    Gr = torch.bmm(ref["E"].double().transpose(1, 2), ref["E"].double())
+    assert (G - Gr).abs().max().item() <= 1e-5 * Gr.abs().max().item()
+    assert torch.equal(G, ops.pca_gram(w, q))                  # chunks are added in a fixed order
+    assert (G - G.transpose(1, 2)).abs().max().item() <= 1e-6 * Gr.abs().max().item()
+    coef = ops.pca_project(w, q, ref["basis"])
+    assert (coef - ref["coef"]).abs().max().item() <= 1e-5 * ref["coef"].abs().max().item()
+    byte = ops.pca_pack(coef, ref["scales"])
+    cq = (coef / ref["scales"].unsqueeze(-1)).round().clamp(-8, 7).to(torch.int16)
+    want = ((cq[:, 0] & 0xF) | ((cq[:, 1] & 0xF) << 4)).to(torch.uint8).t().contiguous().reshape(-1)
+    assert torch.equal(byte, want)
+    # end to end: same bytes as the torch stage except where a coefficient sits on a rounding boundary
+    assert (byte != ref["coeff"]).float().mean().item() < 1e-3
