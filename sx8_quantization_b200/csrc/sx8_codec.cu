@@ -35,61 +35,97 @@ struct DequantArgs {
     __half* out;
 };
 
+// Exact integer -> double without the conversion unit: 2^52 + u has u in its low mantissa bits.
+__device__ __forceinline__ double u2d(uint32_t u) {
+    return __dsub_rn(__hiloint2double(0x43300000, (int)u), 4503599627370496.0);
+}
+
+// One CTA decodes 32 rows x 8 block columns (four passes of 8 rows; thread = (row, kb, sub-block), sub-block
+// fastest): per row it reads 128 contiguous bytes of levels_hi and writes 512 contiguous bytes.  The two bases and
+// the scales of the CTA's 8 block columns are converted to double once, into shared memory; levels and the signed
+// coefficients become doubles by exponent arithmetic.  What is left for the (slow) conversion unit per weight is the
+// float64 -> float32 rounding and half of a float32 -> float16 pair.  The arithmetic itself is unchanged: every
+// double operation of the reference decoder, in its order (ref scripts/kernel_sx8_v43.py:22-51).
+constexpr int kDqKb = 8, kDqRows = 32;
+
 template <int LAYOUT>
 __global__ void __launch_bounds__(256) dequant_d64_kernel(DequantArgs a) {
-    long gid = (long)blockIdx.x * 256 + threadIdx.x;
-    long blk = gid >> 2;  // output-order block index: n*n_cb + kb
-    int sb = (int)(gid & 3);
-    long n_blk = a.out_f * a.n_cb;
-    if (blk >= n_blk) return;
-    long n = blk / a.n_cb;
-    int kb = (int)(blk - n * a.n_cb);
-
-    uint32_t hi4, lo2, cfg, co;
-    float lo_f, hi_f;
-    if (LAYOUT == 0) {
-        hi4 = *reinterpret_cast<const uint32_t*>(a.hi + blk * 16 + sb * 4);
-        lo2 = *reinterpret_cast<const uint16_t*>(a.lo + blk * 8 + sb * 2);
-        lo_f = h2f_bits(a.dmin[blk]);
-        hi_f = h2f_bits(a.dmax[blk]);
-        cfg = a.config[blk];
-        co = a.coeff[blk];
-    } else {
-        T16Sub q = t16_read(a.levels, n, kb, sb, a.n_cb);
-        hi4 = 0; lo2 = 0;
-#pragma unroll
-        for (int i = 0; i < 8; i++) {   // back to the file-format words so both layouts share one decode
-            hi4 |= (q.lv[i] >> 2) << (4 * i);
-            lo2 |= (q.lv[i] & 3) << ((i >> 2) * 8 + (3 - (i & 3)) * 2);
-        }
-        lo_f = h2f_bits((uint16_t)q.dmin);
-        hi_f = h2f_bits((uint16_t)q.dmax);
-        cfg = q.cfg;
-        co = q.coeff;
-    }
-    RangeD64 r = range_d64(lo_f, hi_f, (cfg >> (sb * 2)) & 3);
-    double p0 = 0.0, p1 = 0.0;
+    // basis value (kl, j, t) at kl * 84 + j * 36 + (t >> 3) * 9 + (t & 7): the 16 lanes of a half-warp (4 block
+    // columns x 4 sub-blocks) then read 16 different 8-byte banks
+    __shared__ double B[kDqKb * 84];
+    __shared__ double S[kDqKb][2];
+    const int tid = threadIdx.x;
+    const long kgroups = (a.n_cb + kDqKb - 1) / kDqKb;
+    const long rt = (long)blockIdx.x / kgroups;
+    const int kb0 = (int)((long)blockIdx.x - rt * kgroups) * kDqKb;
+    const long r0 = rt * kDqRows;
     if (a.use_pca) {
-        p0 = __dmul_rn((double)s4(co & 0xF), (double)a.scales[kb * 2 + 0]);
-        p1 = __dmul_rn((double)s4((co >> 4) & 0xF), (double)a.scales[kb * 2 + 1]);
-    }
-    __align__(16) __half v[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        int lv = level_of(hi4, lo2, i);
-        double w = __fma_rn(r.step, (double)lv, r.rlo);
-        if (a.use_pca) {
-            int t = sb * 8 + i;
-            w = __fma_rn(p0, (double)a.bases[kb * 64 + t], w);
-            w = __fma_rn(p1, (double)a.bases[kb * 64 + 32 + t], w);
+        for (int i = tid; i < kDqKb * 64; i += 256) {
+            const int kb = kb0 + (i >> 6);
+            const int t = i & 31;
+            B[(i >> 6) * 84 + ((i >> 5) & 1) * 36 + (t >> 3) * 9 + (t & 7)] = (kb < a.n_cb) ? (double)a.bases[(long)kb * 64 + (i & 63)] : 0.0;
         }
-        v[i] = __float2half_rn(__double2float_rn(w));
+        if (tid < kDqKb * 2) {
+            const int kb = kb0 + (tid >> 1);
+            S[tid >> 1][tid & 1] = (kb < a.n_cb) ? (double)a.scales[kb * 2 + (tid & 1)] : 0.0;
+        }
     }
-    long k0 = (long)kb * 32 + sb * 8;
-    long nv = a.in_f - k0;
-    if (nv <= 0) return;
-    bool vec_ok = (a.in_f % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.out) & 15) == 0);
-    store8(a.out + n * a.in_f + k0, v, (int)(nv > 8 ? 8 : nv), vec_ok);
+    __syncthreads();
+    const int sb = tid & 3, kl = (tid >> 2) & 7, kb = kb0 + kl;
+    const bool vec_ok = (a.in_f % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.out) & 15) == 0);
+    const long k0 = (long)kb * 32 + sb * 8;
+    const long nv = a.in_f - k0;
+    if (kb >= a.n_cb || nv <= 0) return;
+#pragma unroll 1
+    for (int p = 0; p < kDqRows / 8; p++) {
+        const long n = r0 + p * 8 + (tid >> 5);
+        if (n >= a.out_f) break;
+        const long blk = n * a.n_cb + kb;
+        uint32_t hi4, lo2, cfg, co;
+        float lo_f, hi_f;
+        if (LAYOUT == 0) {
+            hi4 = *reinterpret_cast<const uint32_t*>(a.hi + blk * 16 + sb * 4);
+            lo2 = *reinterpret_cast<const uint16_t*>(a.lo + blk * 8 + sb * 2);
+            lo_f = h2f_bits(a.dmin[blk]);
+            hi_f = h2f_bits(a.dmax[blk]);
+            cfg = a.config[blk];
+            co = a.coeff[blk];
+        } else {
+            T16Sub q = t16_read(a.levels, n, kb, sb, a.n_cb);
+            hi4 = 0; lo2 = 0;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {   // back to the file-format words so both layouts share one decode
+                hi4 |= (q.lv[i] >> 2) << (4 * i);
+                lo2 |= (q.lv[i] & 3) << ((i >> 2) * 8 + (3 - (i & 3)) * 2);
+            }
+            lo_f = h2f_bits((uint16_t)q.dmin);
+            hi_f = h2f_bits((uint16_t)q.dmax);
+            cfg = q.cfg;
+            co = q.coeff;
+        }
+        RangeD64 r = range_d64(lo_f, hi_f, (cfg >> (sb * 2)) & 3);
+        double p0 = 0.0, p1 = 0.0;
+        if (a.use_pca) {   // signed nibble c: (c ^ 8) - 8
+            p0 = __dmul_rn(__dsub_rn(u2d((co & 0xF) ^ 8u), 8.0), S[kl][0]);
+            p1 = __dmul_rn(__dsub_rn(u2d(((co >> 4) & 0xF) ^ 8u), 8.0), S[kl][1]);
+        }
+        __align__(16) __half v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+            float f[2];
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                double w = __fma_rn(r.step, u2d((uint32_t)level_of(hi4, lo2, i + j)), r.rlo);
+                if (a.use_pca) {
+                    w = __fma_rn(p0, B[kl * 84 + sb * 9 + i + j], w);
+                    w = __fma_rn(p1, B[kl * 84 + 36 + sb * 9 + i + j], w);
+                }
+                f[j] = __double2float_rn(w);
+            }
+            *reinterpret_cast<__half2*>(&v[i]) = __floats2half2_rn(f[0], f[1]);
+        }
+        store8(a.out + n * a.in_f + k0, v, (int)(nv > 8 ? 8 : nv), vec_ok);
+    }
 }
 
 // ------------------------------------------------------------------ embedding (float32)
@@ -707,8 +743,9 @@ extern "C" int sx8_dequant_planes(const void* dmin, const void* dmax, const uint
                 "sx8_dequant_planes: misaligned plane pointer");
     DequantArgs a{(const uint16_t*)dmin, (const uint16_t*)dmax, config, coeff, hi, lo, nullptr, nullptr,
                   bases, scales, out_f, in_f, n_cb, 6, use_pca, (__half*)out};
-    long threads = out_f * n_cb * 4;
-    dequant_d64_kernel<0><<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(a);
+    const long ctas = ((out_f + kDqRows - 1) / kDqRows) * ((n_cb + kDqKb - 1) / kDqKb);
+    SX8_REQUIRE(ctas <= 0x7FFFFFFFL, "sx8_dequant_planes: tensor too large for one launch");
+    dequant_d64_kernel<0><<<(unsigned)ctas, 256, 0, (cudaStream_t)stream>>>(a);
     SX8_LAUNCH_CHECK("dequant_d64_kernel<planes>");
     return SX8_OK;
 }
@@ -722,8 +759,9 @@ extern "C" int sx8_dequant_t16(const void* wt16, const float* bases, const float
     SX8_REQUIRE(aligned(wt16, 16) && aligned(out, 2), "sx8_dequant_t16: misaligned pointer");
     DequantArgs a{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, (const uint8_t*)wt16,
                   bases, scales, out_f, in_f, n_cb, 6, use_pca, (__half*)out};
-    long threads = out_f * n_cb * 4;
-    dequant_d64_kernel<1><<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(a);
+    const long ctas = ((out_f + kDqRows - 1) / kDqRows) * ((n_cb + kDqKb - 1) / kDqKb);
+    SX8_REQUIRE(ctas <= 0x7FFFFFFFL, "sx8_dequant_t16: tensor too large for one launch");
+    dequant_d64_kernel<1><<<(unsigned)ctas, 256, 0, (cudaStream_t)stream>>>(a);
     SX8_LAUNCH_CHECK("dequant_d64_kernel<t16>");
     return SX8_OK;
 }
