@@ -33,7 +33,11 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 from oracle import sx8_oracle as orc  # noqa: E402  (synthetic generators only)
 
-REF = os.environ.get("SX8_REF", "/root/reference")
+from oracle import build as _ob  # noqa: E402
+
+REF = _ob.ref_root()   # $SX8_REF, else the path BASELINE.json records
+if not REF:
+    sys.exit("set SX8_REF to the reference checkout")
 
 
 def load_ref_quantizer():

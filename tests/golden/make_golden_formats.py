@@ -19,7 +19,12 @@ import tempfile
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("SX8_REF", "/root/reference")
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+from oracle import build as _ob  # noqa: E402
+
+REF = _ob.ref_root()   # $SX8_REF, else the path BASELINE.json records
+if not REF:
+    sys.exit("set SX8_REF to the reference checkout")
 
 
 def tensors_from_small_case():

@@ -101,8 +101,9 @@ def test_launcher_registers_reference_module_names():
 def test_reference_signatures_match_checkout_if_present():
     """When a reference checkout is available, compare against its source directly."""
     import ast
-    ref = os.environ.get("SX8_REF", "/root/reference")
-    if not os.path.isdir(os.path.join(ref, "scripts")):
+    from oracle import build as ob
+    ref = ob.ref_root()   # $SX8_REF, else the path BASELINE.json records
+    if not ref or not os.path.isdir(os.path.join(ref, "scripts")):
         pytest.skip("no reference checkout")
     for (mod, fn), want in REFERENCE_API.items():
         tree = ast.parse(open(os.path.join(ref, "scripts", mod + ".py")).read())
