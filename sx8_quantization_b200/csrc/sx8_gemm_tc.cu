@@ -258,12 +258,21 @@ __device__ __forceinline__ void add_xfer(uint32_t cluster_base, int lane, uint32
 // PCA table: pb[kb][j][t] = fp16(scales[kb][j] * bases[kb][32j + t] * 1024), 128 bytes per kb.
 // (The coefficient operand carries the matching 2^-10; the pre-scale keeps the products of
 // small scales and basis entries out of the fp16 subnormal range.)
+// Launched with programmatic stream serialization: the GEMM that follows may start (and prefetch its
+// weights) while this kernel runs, and this kernel may start while the GEMM before it -- which
+// reads the same table when calls share a workspace -- is still running: bases and scales are
+// weights and are read at once, the table is written only after that GEMM has completed.
 __global__ void __launch_bounds__(256)
 pca_table_kernel(const float* __restrict__ bases, const float* __restrict__ scales, int n_cb, __half* __restrict__ pb) {
+    asm volatile("griddepcontrol.launch_dependents;");
     int i = blockIdx.x * 256 + threadIdx.x;
-    if (i >= n_cb * 64) return;
-    int kb = i >> 6, j = (i >> 5) & 1;
-    pb[i] = __float2half_rn(scales[kb * 2 + j] * bases[i] * 1024.0f);
+    __half v = __float2half_rn(0.0f);
+    if (i < n_cb * 64) {
+        int kb = i >> 6, j = (i >> 5) & 1;
+        v = __float2half_rn(scales[kb * 2 + j] * bases[i] * 1024.0f);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (i < n_cb * 64) pb[i] = v;
 }
 
 struct Params {
@@ -346,38 +355,53 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = lds32(tmem_slot);
 
+    // Programmatic dependent launch: the kernel after this one may begin its own set-up now; this
+    // kernel was itself allowed to start before the one ahead of it finished.  The packed weights
+    // do not depend on that kernel and are requested at once; X, the PCA table and Y are touched
+    // only after griddepcontrol.wait (which every role that reaches global memory executes).
+    asm volatile("griddepcontrol.launch_dependents;");
+
     if (warp == kWarps - 1) {
         // ------------------------------------------------------------ producer of packed slabs
         bool ok = true;
         Ring rp(SP);
-        for (int ks = 0; ks < n_ks; ks++) {
+        // One tensor copy brings the slabs of all TILES tiles: the blob is a 2-D array of
+        // 32-bit words, one row of n_cb * 120 words per 16-column tile; the box is
+        // TILES rows x 240 words (two block rows).  Tiles or block rows past the end
+        // arrive as zeros (and count as bytes).  The PCA table rows of the stage follow as a
+        // second copy onto the same barrier.
+        auto issue = [&](int ks, int s, bool weights, bool table) {
             const int kb0 = (ks0 + ks) * KB_STAGE;
             const int rows = min(KB_STAGE, p.n_cb - kb0);
-            {   // packed slabs + PCA table: lane i < TILES copies tile i, lane 16 the table
-                const int s = rp.s;
-                if (rp.r > 0 && ok) ok = mbar_wait(p_empty + 8 * s, (rp.r - 1) & 1, 0x10u);
-                rp = rp.next();
-                if (SX8_DBG(p) & 4) {
-                    if (lane == 0) mbar_arrive(p_full + 8 * s);
-                    continue;
-                }
-                // One tensor copy brings the slabs of all TILES tiles: the blob is a 2-D array of
-                // 32-bit words, one row of n_cb * 120 words per 16-column tile; the box is
-                // TILES rows x 240 words (two block rows).  Tiles or block rows past the end
-                // arrive as zeros (and count as bytes).
-                const uint32_t dst = sP + s * P_STAGE;
-                if (lane == 0) {
+            const uint32_t dst = sP + s * P_STAGE;
+            if (lane == 0) {
+                if (weights) {
                     mbar_expect_tx(p_full + 8 * s, (uint32_t)P_SLAB + (uint32_t)rows * 128u);
                     tma_load_2d(dst, &wmap, kb0 * (T16_UNIT / 4), tile0, p_full + 8 * s);
-                    bulk_g2s(dst + P_SLAB, p.pb + (long)kb0 * 64, (uint32_t)rows * 128u, p_full + 8 * s);
                 }
-                __syncwarp();
+                if (table) bulk_g2s(dst + P_SLAB, p.pb + (long)kb0 * 64, (uint32_t)rows * 128u, p_full + 8 * s);
             }
+            __syncwarp();
+        };
+        const int pre = (SX8_DBG(p) & 4) ? 0 : min(n_ks, SP);   // stages filled before the wait: weights only
+        for (int ks = 0; ks < pre; ks++) issue(ks, ks, true, false);
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        for (int ks = 0; ks < pre; ks++) { issue(ks, ks, false, true); rp = rp.next(); }
+        for (int ks = pre; ks < n_ks; ks++) {
+            const int s = rp.s;
+            if (rp.r > 0 && ok) ok = mbar_wait(p_empty + 8 * s, (rp.r - 1) & 1, 0x10u);
+            rp = rp.next();
+            if (SX8_DBG(p) & 4) {
+                if (lane == 0) mbar_arrive(p_full + 8 * s);
+                continue;
+            }
+            issue(ks, s, true, true);
         }
     } else if (warp == 0) {
         // ------------------------------------------------------------ producer of X tiles
         bool ok = true;
         Ring ra(SA);
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         for (int ks = 0; ks < n_ks; ks++) {
             {   // MT boxes of 64 (K) x 128 (rows); columns/rows out of range read as zero
                 const int s = ra.s;
@@ -608,6 +632,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         // ------------------------------------------------------------ epilogue
         if constexpr (PAIR == 2) { if (ok) ok = mbar_wait_cl(acc_full, 0u, 0x400u); }
         else { if (ok) ok = mbar_wait(acc_full, 0u, 0x400u); }
+        asm volatile("griddepcontrol.wait;" ::: "memory");   // Y may be read by the kernel before this one
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int quarter = warp & 3;            // TMEM lanes 32*quarter .. +31 are this warp's
         const int part = dw >> 2;                // the four warps of a quarter share the BN columns
@@ -755,6 +780,21 @@ EncodeTiledFn encode_fn() {
 
 size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
 
+int launch_pca_table(const float* bases, const float* scales, int n_cb, __half* pb, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((n_cb * 64 + 255) / 256), 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, tc::pca_table_kernel, bases, scales, n_cb, pb);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(pca_table_kernel)");
+    return SX8_OK;
+}
+
 __global__ void __launch_bounds__(256)
 xstage_kernel(const __half* __restrict__ x, int M, int K, long ldx, int Kp, __half* __restrict__ out) {
     long i = (long)blockIdx.x * 256 + threadIdx.x;
@@ -841,13 +881,20 @@ int launch_tc_bn(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
     cfg.blockDim = dim3(tc::kThreads, 1, 1);
     cfg.dynamicSmemBytes = (size_t)smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = PAIR * KS;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see the kernel: weights are prefetched under the kernel ahead
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    na++;
+    if (PAIR * KS == 2) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = PAIR * KS;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        na++;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = (PAIR * KS == 2) ? 1 : 0;
+    cfg.numAttrs = na;
     e = cudaLaunchKernelEx(&cfg, tc::gemm_tc_kernel<MT, BN, PAIR, G, KS>, map, ymap, wmap, p);
     if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(gemm_tc_kernel)");
     return SX8_OK;
@@ -920,8 +967,8 @@ int gemm_tc_launch(const void* x, int M, int K, long ldx, const void* wt16, cons
                    const float* scales, int N, int n_cb, void* y, int out_f16, void* workspace,
                    cudaStream_t stream) {
     __half* pb = (__half*)workspace;
-    tc::pca_table_kernel<<<(unsigned)((n_cb * 64 + 255) / 256), 256, 0, stream>>>(bases, scales, n_cb, pb);
-    SX8_LAUNCH_CHECK("pca_table_kernel");
+    int rc_t = launch_pca_table(bases, scales, n_cb, pb, stream);
+    if (rc_t != SX8_OK) return rc_t;
     const __half* xp = (const __half*)x;
     long ld = ldx;
     int Kx = K;
@@ -1023,8 +1070,8 @@ extern "C" int sx8_gemm_static(const void* x, int M, int K, long ldx, const void
     __half* pb = nullptr;
     int rc = static_pca_ptr(&pb);
     if (rc != SX8_OK) return rc;
-    tc::pca_table_kernel<<<(unsigned)((n_cb * 64 + 255) / 256), 256, 0, stream>>>(bases, scales, n_cb, pb);
-    SX8_LAUNCH_CHECK("pca_table_kernel");
+    rc = launch_pca_table(bases, scales, n_cb, pb, stream);
+    if (rc != SX8_OK) return rc;
     CUtensorMap map;
     cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)M};
     cuuint64_t gstr[1] = {(cuuint64_t)ldx * 2};
