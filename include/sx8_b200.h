@@ -118,6 +118,19 @@ int sx8_gemm(const void* x_f16, int M, int K, long ldx, const void* wt16, const 
              const float* scales, int N, int n_cb, void* y, int out_f16, void* workspace,
              size_t workspace_bytes, void* stream);
 
+/* ---- several prefill GEMMs on the same activations ---------------------------------
+ * No counterpart in the reference (see sx8_gemv_multi).  y[i] (M, N[i]) = X * W_i^T for count <= 3
+ * matrices with the same K (q|k|v, gate|up).  When M > 16 and every N[i] but the last is a
+ * multiple of 256, all of them run in ONE launch of the tensor-core kernel (their columns side by
+ * side in one grid: the small k and v projections no longer leave most SMs idle, and one launch
+ * replaces three); otherwise the call is count calls of sx8_gemm.  Same results either way.
+ * Arrays are host arrays of device pointers / sizes.                                   */
+size_t sx8_gemm_multi_workspace_bytes(int M, int count, const int* N, int n_cb);
+int sx8_gemm_multi(const void* x_f16, int M, int K, long ldx, int count, const void* const* wt16,
+                   const float* const* bases, const float* const* scales, const int* N,
+                   void* const* y, int out_f16, int n_cb, void* workspace, size_t workspace_bytes,
+                   void* stream);
+
 /* ---- prefill GEMM without any workspace -------------------------------------------
  * No counterpart in the reference.  For callers that are not allowed to allocate device
  * memory while running (a server that gave all of its memory to its own arena at

@@ -24,6 +24,8 @@ SIGNATURES = {
     "sx8_gemv_allreduce": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _i, _i, _vp, _vp, _sz, _u, _vp, _vp]),
     "sx8_gemm_workspace_bytes": (_sz, [_i, _i, _i]),
     "sx8_gemm": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _sz, _vp]),
+    "sx8_gemm_multi_workspace_bytes": (_sz, [_i, _i, _vp, _i]),
+    "sx8_gemm_multi": (_i, [_vp, _i, _i, _l, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _sz, _vp]),
     "sx8_gemm_static_max_ncb": (_sz, []),
     "sx8_gemm_static": (_i, [_vp, _i, _i, _l, _vp, _vp, _vp, _i, _i, _vp, _i, _vp]),
     "sx8_embed": (_i, [_vp, _l, _vp, _vp, _vp, _i, _i, _i, _vp, _vp]),

@@ -19,6 +19,10 @@ bool gemm_tc_supported(int M, int N, int K, int n_cb);
 int gemm_tc_launch(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
                    const float* scales, int N, int n_cb, void* y, int out_f16, void* workspace,
                    cudaStream_t stream);
+size_t gemm_tc_multi_workspace_bytes(int M, int n_cb, int nmat);
+int gemm_tc_launch_multi(const void* x, int M, int K, long ldx, int nmat, const void* const* wt16,
+                         const float* const* bases, const float* const* scales, const int* N, int n_cb,
+                         void* const* y, int out_f16, void* workspace, cudaStream_t stream);
 
 __global__ void __launch_bounds__(256) f32_to_f16_kernel(const float* __restrict__ in, __half* __restrict__ out, long n) {
     long i = ((long)blockIdx.x * 256 + threadIdx.x) * 4;
@@ -83,6 +87,57 @@ extern "C" int sx8_gemm(const void* x, int M, int K, long ldx, const void* wt16,
         long n = (long)M * N;
         f32_to_f16_kernel<<<(unsigned)((n / 4 + 255) / 256 + 1), 256, 0, stream>>>(y32, (__half*)y, n);
         SX8_LAUNCH_CHECK("f32_to_f16_kernel");
+    }
+    return SX8_OK;
+}
+
+// ---- several prefill GEMMs on the same activations -------------------------------------------
+static const int kGemmMultiMax = 3;
+
+// One launch when the tensor-core path takes the call (M > 16) and every matrix but the last is a
+// multiple of 256 columns wide; otherwise one sx8_gemm per matrix, with the same results.
+static bool gemm_multi_fusable(int M, int count, const int* N, int K, int n_cb) {
+    if (M <= kGemvRowsMax || count < 2 || !gemm_tc_supported(M, N[0], K, n_cb)) return false;
+    for (int i = 0; i + 1 < count; i++)
+        if (N[i] % 256 != 0) return false;
+    return true;
+}
+
+extern "C" size_t sx8_gemm_multi_workspace_bytes(int M, int count, const int* N, int n_cb) {
+    if (M <= 0 || count <= 0 || count > kGemmMultiMax || !N || n_cb <= 0) return 0;
+    size_t need = gemm_tc_multi_workspace_bytes(M, n_cb, count);
+    for (int i = 0; i < count; i++) {
+        size_t one = sx8_gemm_workspace_bytes(M, N[i], n_cb);
+        if (one > need) need = one;
+    }
+    return need;
+}
+
+extern "C" int sx8_gemm_multi(const void* x, int M, int K, long ldx, int count, const void* const* wt16,
+                              const float* const* bases, const float* const* scales, const int* N,
+                              void* const* y, int out_f16, int n_cb, void* workspace, size_t workspace_bytes,
+                              void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    SX8_REQUIRE(count >= 1 && count <= kGemmMultiMax, "sx8_gemm_multi: count must be 1..%d (got %d)", kGemmMultiMax, count);
+    SX8_REQUIRE(wt16 && bases && scales && N && y, "sx8_gemm_multi: null array");
+    long total = 0;
+    for (int i = 0; i < count; i++) {
+        int rc = gemv_check("sx8_gemm_multi", x, M, 0x7FFFFFFF, K, ldx, wt16[i], bases[i], scales[i], N[i], n_cb, y[i]);
+        if (rc != SX8_OK) return rc;
+        total += N[i];
+    }
+    SX8_REQUIRE((long)M * total < (1L << 40) && total < 0x7FFFFFFFL, "sx8_gemm_multi: output too large");
+    if (!workspace || workspace_bytes < sx8_gemm_multi_workspace_bytes(M, count, N, n_cb) ||
+        (reinterpret_cast<uintptr_t>(workspace) % 256) != 0) {
+        set_error("sx8_gemm_multi: workspace must be 256-byte aligned and hold %zu bytes (got %zu)",
+                  sx8_gemm_multi_workspace_bytes(M, count, N, n_cb), workspace_bytes);
+        return SX8_E_WORKSPACE;
+    }
+    if (gemm_multi_fusable(M, count, N, K, n_cb))
+        return gemm_tc_launch_multi(x, M, K, ldx, count, wt16, bases, scales, N, n_cb, y, out_f16, workspace, stream);
+    for (int i = 0; i < count; i++) {
+        int rc = sx8_gemm(x, M, K, ldx, wt16[i], bases[i], scales[i], N[i], n_cb, y[i], out_f16, workspace, workspace_bytes, stream_);
+        if (rc != SX8_OK) return rc;
     }
     return SX8_OK;
 }

@@ -262,24 +262,40 @@ __device__ __forceinline__ void add_xfer(uint32_t cluster_base, int lane, uint32
 // weights) while this kernel runs, and this kernel may start while the GEMM before it -- which
 // reads the same table when calls share a workspace -- is still running: bases and scales are
 // weights and are read at once, the table is written only after that GEMM has completed.
-__global__ void __launch_bounds__(256)
-pca_table_kernel(const float* __restrict__ bases, const float* __restrict__ scales, int n_cb, __half* __restrict__ pb) {
+struct TableArgs {
+    const float* bases[3];
+    const float* scales[3];
+};
+// grid (ceil(n_cb * 64 / 256), matrices); the table of matrix i starts at pb + i * n_cb * 64.
+__global__ void __launch_bounds__(256) pca_table_kernel(TableArgs a, int n_cb, __half* __restrict__ pb) {
     asm volatile("griddepcontrol.launch_dependents;");
-    int i = blockIdx.x * 256 + threadIdx.x;
+    const int i = blockIdx.x * 256 + threadIdx.x, mi = blockIdx.y;
+    const float* __restrict__ bases = a.bases[mi];
+    const float* __restrict__ scales = a.scales[mi];
     __half v = __float2half_rn(0.0f);
     if (i < n_cb * 64) {
         int kb = i >> 6, j = (i >> 5) & 1;
         v = __float2half_rn(scales[kb * 2 + j] * bases[i] * 1024.0f);
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (i < n_cb * 64) pb[i] = v;
+    if (i < n_cb * 64) pb[(long)mi * n_cb * 64 + i] = v;
 }
 
+// One launch can serve up to kMaxMats matrices that share X (q|k|v, gate|up): their columns are
+// laid side by side in one virtual N (every matrix but the last a multiple of 256 columns wide,
+// so no tile straddles two matrices); a CTA finds its matrix from its first column and uses that
+// matrix's blob, PCA table and output.
+constexpr int kMaxMats = 3;
+struct Mat {
+    const uint8_t* blob;   // host side only: the tensor map is built from it
+    void* y;               // (M, N) row-major
+    int col0, N, n_tiles;  // first virtual column, columns, 16-column tiles
+};
 struct Params {
-    const uint8_t* blob;
-    const __half* pb;
-    void* y;
-    int M, N, n_cb, n_tiles, out_f16;
+    const __half* pb;      // PCA tables, one of n_cb * 64 halves per matrix
+    int nmat;
+    Mat mat[kMaxMats];
+    int M, N, n_cb, out_f16;   // N: virtual columns of all matrices
     int tma_store;   // Y rows are 16-byte multiples: the epilogue stores through the Y tensor map
     int sa, sb, sp;  // pipeline depths: X-tile, decoded-operand and packed-slab stages
     int debug;       // timing experiments only (results are wrong): 1 = skip the decode math, 2 = skip the
@@ -299,8 +315,10 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
 // small M, where there are fewer tiles than SMs and decoding the weights bounds the time.
 template <int MT, int BN, int PAIR, int G, int KS>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap,
-               const __grid_constant__ CUtensorMap wmap, Params p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap0,
+               const __grid_constant__ CUtensorMap ymap1, const __grid_constant__ CUtensorMap ymap2,
+               const __grid_constant__ CUtensorMap wmap0, const __grid_constant__ CUtensorMap wmap1,
+               const __grid_constant__ CUtensorMap wmap2, Params p) {
     using C = Cfg<MT, BN, PAIR>;
     constexpr int kGroupWarps = kDecodeWarps / G;
     constexpr int B_TILE = C::B_TILE, P_SLAB = C::P_SLAB, P_STAGE = C::P_STAGE, TILES = C::TILES, BNU = C::BNU;
@@ -323,8 +341,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     // PAIR == 2: the cluster is two consecutive CTAs along x; rank 0 leads (issues the MMAs).
     const int rank = (PAIR == 2) ? (int)(blockIdx.x & 1) : 0;
     const int krank = (KS == 2) ? (int)(blockIdx.x & 1) : 0;
-    const int n0 = (int)(blockIdx.x / (PAIR * KS)) * BNU;    // first accumulator column
+    const int nv0 = (int)(blockIdx.x / (PAIR * KS)) * BNU;   // first accumulator column among all matrices' columns
     const int m0 = blockIdx.y * (128 * MT * PAIR);
+    // the matrix of this CTA
+    int mi = 0;
+    if (p.nmat > 1 && nv0 >= p.mat[1].col0) mi = 1;
+    if (p.nmat > 2 && nv0 >= p.mat[2].col0) mi = 2;
+    const CUtensorMap* const wmap = (mi == 0) ? &wmap0 : ((mi == 1) ? &wmap1 : &wmap2);
+    const CUtensorMap* const ymap = (mi == 0) ? &ymap0 : ((mi == 1) ? &ymap1 : &ymap2);
+    const int n0 = nv0 - ((mi == 0) ? p.mat[0].col0 : ((mi == 1) ? p.mat[1].col0 : p.mat[2].col0));   // column within the matrix
+    const int mat_N = (mi == 0) ? p.mat[0].N : ((mi == 1) ? p.mat[1].N : p.mat[2].N);
+    const int mat_tiles = (mi == 0) ? p.mat[0].n_tiles : ((mi == 1) ? p.mat[1].n_tiles : p.mat[2].n_tiles);
+    void* const mat_y = (mi == 0) ? p.mat[0].y : ((mi == 1) ? p.mat[1].y : p.mat[2].y);
+    const __half* const mat_pb = p.pb + (long)mi * p.n_cb * 64;
     const int tile0 = (n0 + rank * BN) >> 4;                 // first 16-column tile this CTA decodes
     const int n_ks_all = (p.n_cb + KB_STAGE - 1) / KB_STAGE;
     const int ks_half = (n_ks_all + KS - 1) / KS;
@@ -377,9 +406,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             if (lane == 0) {
                 if (weights) {
                     mbar_expect_tx(p_full + 8 * s, (uint32_t)P_SLAB + (uint32_t)rows * 128u);
-                    tma_load_2d(dst, &wmap, kb0 * (T16_UNIT / 4), tile0, p_full + 8 * s);
+                    tma_load_2d(dst, wmap, kb0 * (T16_UNIT / 4), tile0, p_full + 8 * s);
                 }
-                if (table) bulk_g2s(dst + P_SLAB, p.pb + (long)kb0 * 64, (uint32_t)rows * 128u, p_full + 8 * s);
+                if (table) bulk_g2s(dst + P_SLAB, mat_pb + (long)kb0 * 64, (uint32_t)rows * 128u, p_full + 8 * s);
             }
             __syncwarp();
         };
@@ -512,7 +541,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
 #pragma unroll
             for (int item = gw; item < TILES * KB_STAGE && !(SX8_DBG(p) & 1); item += kGroupWarps) {
                 const int tl = item % TILES, r = item / TILES;
-                const bool tile_ok = tile0 + tl < p.n_tiles;
+                const bool tile_ok = tile0 + tl < mat_tiles;
                 // Column 16*tl + g sits in operand row 16*tl + rho(g), rho(g) = 4*(g&1) + (g>>1): the
                 // eight lanes of a quarter-warp then store to eight different 16-byte bank groups.
                 // The epilogue undoes the permutation when it reads the accumulator columns.
@@ -697,7 +726,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                            make_uint4(h[4 * q], h[4 * q + 1], h[4 * q + 2], h[4 * q + 3]));
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) tma_store_2d(&ymap, stg, n0 + col, mrow0);
+                if (lane == 0) tma_store_2d(ymap, stg, n0 + col, mrow0);
               }
             } else {
 #pragma unroll 1
@@ -722,17 +751,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                         }
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                         __syncwarp();
-                        if (lane == 0) tma_store_2d(&ymap, stg, n0 + col, mrow0);
+                        if (lane == 0) tma_store_2d(ymap, stg, n0 + col, mrow0);
                     } else if (m < p.M) {
                         // rows of Y are not 16-byte multiples: plain guarded stores
                         const int n = n0 + col;
                         for (int c = 0; c < 32; c++) {
                             const int a = (c & ~7) | ((((c & 7) & 1) << 2) | ((c & 7) >> 1));
-                            if (n + c < p.N) {
+                            if (n + c < mat_N) {
                                 if (p.out_f16)
-                                    reinterpret_cast<__half*>(p.y)[m * p.N + n + c] = __float2half_rn(__uint_as_float(v[a]));
+                                    reinterpret_cast<__half*>(mat_y)[m * mat_N + n + c] = __float2half_rn(__uint_as_float(v[a]));
                                 else
-                                    reinterpret_cast<float*>(p.y)[m * p.N + n + c] = __uint_as_float(v[a]);
+                                    reinterpret_cast<float*>(mat_y)[m * mat_N + n + c] = __uint_as_float(v[a]);
                             }
                         }
                     }
@@ -780,9 +809,12 @@ EncodeTiledFn encode_fn() {
 
 size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
 
-int launch_pca_table(const float* bases, const float* scales, int n_cb, __half* pb, cudaStream_t stream) {
+int launch_pca_table(int nmat, const float* const* bases, const float* const* scales, int n_cb, __half* pb,
+                     cudaStream_t stream) {
+    tc::TableArgs ta = {};
+    for (int i = 0; i < nmat; i++) { ta.bases[i] = bases[i]; ta.scales[i] = scales[i]; }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)((n_cb * 64 + 255) / 256), 1, 1);
+    cfg.gridDim = dim3((unsigned)((n_cb * 64 + 255) / 256), (unsigned)nmat, 1);
     cfg.blockDim = dim3(256, 1, 1);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -790,7 +822,7 @@ int launch_pca_table(const float* bases, const float* scales, int n_cb, __half* 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, tc::pca_table_kernel, bases, scales, n_cb, pb);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, tc::pca_table_kernel, ta, n_cb, pb);
     if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(pca_table_kernel)");
     return SX8_OK;
 }
@@ -820,10 +852,18 @@ bool make_ymap(CUtensorMap* map, void* y, int M, int N, int out_f16) {
 
 template <int MT, int BN, int PAIR, int G = 2, int KS = 1>
 int launch_tc_bn(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
-    CUtensorMap ymap;
-    memset(&ymap, 0, sizeof(ymap));
-    p.tma_store = make_ymap(&ymap, p.y, p.M, p.N, p.out_f16) ? 1 : 0;
     using C = tc::Cfg<MT, BN, PAIR>;
+    CUtensorMap ymap[tc::kMaxMats], wmap[tc::kMaxMats];
+    memset(ymap, 0, sizeof(ymap));
+    memset(wmap, 0, sizeof(wmap));
+    p.tma_store = 1;   // only if every matrix's Y can be addressed by a tensor map
+    for (int i = 0; i < p.nmat; i++)
+        if (!make_ymap(&ymap[i], p.mat[i].y, p.M, p.mat[i].N, p.out_f16)) p.tma_store = 0;
+    for (int i = 1; i < p.nmat; i++)
+        if (p.mat[i].col0 % C::BNU != 0) {
+            set_error("sx8_gemm: matrix %d starts at column %d, not a multiple of the %d-column tile", i, p.mat[i].col0, C::BNU);
+            return SX8_E_INVALID;
+        }
     // Pipeline depths.  The packed slabs come from HBM with the longest latency and get every
     // stage that is left (at most 8); X tiles come from L2.
     static const int env_sa = exp_env("SX8_GEMM_SA", 0);
@@ -855,13 +895,12 @@ int launch_tc_bn(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemm_tc smem)");
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    CUtensorMap wmap;
-    {
-        cuuint64_t gdim[2] = {(cuuint64_t)p.n_cb * (T16_UNIT / 4), (cuuint64_t)p.n_tiles};
+    for (int i = 0; i < p.nmat; i++) {
+        cuuint64_t gdim[2] = {(cuuint64_t)p.n_cb * (T16_UNIT / 4), (cuuint64_t)p.mat[i].n_tiles};
         cuuint64_t gstr[1] = {(cuuint64_t)p.n_cb * T16_UNIT};
         cuuint32_t box[2] = {(cuuint32_t)(tc::KB_STAGE * T16_UNIT / 4), (cuuint32_t)C::TILES};
         cuuint32_t estr[2] = {1u, 1u};
-        CUresult r = encode_fn()(&wmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, (void*)p.blob, gdim, gstr, box, estr,
+        CUresult r = encode_fn()(&wmap[i], CU_TENSOR_MAP_DATA_TYPE_INT32, 2, (void*)p.mat[i].blob, gdim, gstr, box, estr,
                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) {
@@ -895,7 +934,8 @@ int launch_tc_bn(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    e = cudaLaunchKernelEx(&cfg, tc::gemm_tc_kernel<MT, BN, PAIR, G, KS>, map, ymap, wmap, p);
+    e = cudaLaunchKernelEx(&cfg, tc::gemm_tc_kernel<MT, BN, PAIR, G, KS>, map, ymap[0], ymap[1], ymap[2], wmap[0], wmap[1],
+                           wmap[2], p);
     if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(gemm_tc_kernel)");
     return SX8_OK;
 }
@@ -952,10 +992,10 @@ int launch_auto(const CUtensorMap& map, const tc::Params& p, cudaStream_t stream
 
 }  // namespace
 
-// workspace: [PCA table n_cb*128 B][staged x (M, 32*n_cb) f16, only when x is not TMA-addressable]
+size_t gemm_tc_multi_workspace_bytes(int M, int n_cb, int nmat);
 size_t gemm_tc_workspace_bytes(int M, int N, int n_cb) {
     (void)N;
-    return round256((size_t)n_cb * 128) + round256((size_t)M * (size_t)n_cb * 64);
+    return gemm_tc_multi_workspace_bytes(M, n_cb, 1);
 }
 
 bool gemm_tc_supported(int M, int N, int K, int n_cb) {
@@ -963,36 +1003,66 @@ bool gemm_tc_supported(int M, int N, int K, int n_cb) {
     return M >= 1 && encode_fn() != nullptr;
 }
 
-int gemm_tc_launch(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
-                   const float* scales, int N, int n_cb, void* y, int out_f16, void* workspace,
-                   cudaStream_t stream) {
-    __half* pb = (__half*)workspace;
-    int rc_t = launch_pca_table(bases, scales, n_cb, pb, stream);
-    if (rc_t != SX8_OK) return rc_t;
+// X tensor map; stages x through the workspace when a tensor map cannot address it as it is.
+static int make_xmap(CUtensorMap* map, const void* x, int M, int K, long ldx, int n_cb, void* xstage, cudaStream_t stream) {
     const __half* xp = (const __half*)x;
     long ld = ldx;
     int Kx = K;
     if ((ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x) % 16) != 0) {
+        if (!xstage) {
+            set_error("sx8_gemm: x must be 16-byte aligned with a row stride that is a multiple of 8 elements");
+            return SX8_E_INVALID;
+        }
         int Kp = n_cb * 32;
-        __half* xs = (__half*)((uint8_t*)workspace + round256((size_t)n_cb * 128));
-        xstage_kernel<<<(unsigned)(((long)M * Kp + 255) / 256), 256, 0, stream>>>((const __half*)x, M, K, ldx, Kp, xs);
+        xstage_kernel<<<(unsigned)(((long)M * Kp + 255) / 256), 256, 0, stream>>>((const __half*)x, M, K, ldx, Kp, (__half*)xstage);
         SX8_LAUNCH_CHECK("xstage_kernel");
-        xp = xs; ld = Kp; Kx = Kp;
+        xp = (const __half*)xstage; ld = Kp; Kx = Kp;
     }
-    CUtensorMap map;
     cuuint64_t gdim[2] = {(cuuint64_t)Kx, (cuuint64_t)M};
     cuuint64_t gstr[1] = {(cuuint64_t)ld * 2};
     cuuint32_t box[2] = {(cuuint32_t)tc::BK, 128u};
     cuuint32_t estr[2] = {1u, 1u};
-    CUresult r = encode_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)xp, gdim, gstr, box, estr,
+    CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)xp, gdim, gstr, box, estr,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_error("sx8_gemm: cuTensorMapEncodeTiled failed (%d)", (int)r);
         return SX8_E_CUDA;
     }
-    tc::Params p{(const uint8_t*)wt16, pb, y, M, N, n_cb, (int)t16_tiles(N), out_f16, 0, 0, 0, 0, 0};
+    return SX8_OK;
+}
+
+// workspace: [PCA tables, n_cb*128 B per matrix][staged x (M, 32*n_cb) f16, only when x is not TMA-addressable]
+size_t gemm_tc_multi_workspace_bytes(int M, int n_cb, int nmat) {
+    return round256((size_t)nmat * n_cb * 128) + round256((size_t)M * (size_t)n_cb * 64);
+}
+
+// nmat <= 3 matrices with the same K on the same x; N[i] columns each, all but the last a multiple of 256.
+int gemm_tc_launch_multi(const void* x, int M, int K, long ldx, int nmat, const void* const* wt16,
+                         const float* const* bases, const float* const* scales, const int* N, int n_cb,
+                         void* const* y, int out_f16, void* workspace, cudaStream_t stream) {
+    __half* pb = (__half*)workspace;
+    int rc = launch_pca_table(nmat, bases, scales, n_cb, pb, stream);
+    if (rc != SX8_OK) return rc;
+    CUtensorMap map;
+    rc = make_xmap(&map, x, M, K, ldx, n_cb, (uint8_t*)workspace + round256((size_t)nmat * n_cb * 128), stream);
+    if (rc != SX8_OK) return rc;
+    tc::Params p = {};
+    p.pb = pb;
+    p.nmat = nmat;
+    int col = 0;
+    for (int i = 0; i < nmat; i++) {
+        p.mat[i] = tc::Mat{(const uint8_t*)wt16[i], y[i], col, N[i], (int)t16_tiles(N[i])};
+        col += N[i];
+    }
+    p.M = M; p.N = col; p.n_cb = n_cb; p.out_f16 = out_f16;
     return launch_auto(map, p, stream);
+}
+
+int gemm_tc_launch(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
+                   const float* scales, int N, int n_cb, void* y, int out_f16, void* workspace,
+                   cudaStream_t stream) {
+    return gemm_tc_launch_multi(x, M, K, ldx, 1, &wt16, &bases, &scales, &N, n_cb, &y, out_f16, workspace, stream);
 }
 
 }  // namespace sx8
@@ -1070,20 +1140,15 @@ extern "C" int sx8_gemm_static(const void* x, int M, int K, long ldx, const void
     __half* pb = nullptr;
     int rc = static_pca_ptr(&pb);
     if (rc != SX8_OK) return rc;
-    rc = launch_pca_table(bases, scales, n_cb, pb, stream);
+    rc = launch_pca_table(1, &bases, &scales, n_cb, pb, stream);
     if (rc != SX8_OK) return rc;
     CUtensorMap map;
-    cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)M};
-    cuuint64_t gstr[1] = {(cuuint64_t)ldx * 2};
-    cuuint32_t box[2] = {(cuuint32_t)tc::BK, 128u};
-    cuuint32_t estr[2] = {1u, 1u};
-    CUresult r = encode_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), gdim, gstr, box, estr,
-                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        set_error("sx8_gemm_static: cuTensorMapEncodeTiled failed (%d)", (int)r);
-        return SX8_E_CUDA;
-    }
-    tc::Params p{(const uint8_t*)wt16, pb, y, M, N, n_cb, (int)t16_tiles(N), out_f16, 0, 0, 0, 0, 0};
+    rc = make_xmap(&map, x, M, K, ldx, n_cb, nullptr, stream);   // (alignment was checked above: nothing to stage)
+    if (rc != SX8_OK) return rc;
+    tc::Params p = {};
+    p.pb = pb;
+    p.nmat = 1;
+    p.mat[0] = tc::Mat{(const uint8_t*)wt16, y, 0, N, (int)t16_tiles(N)};
+    p.M = M; p.N = N; p.n_cb = n_cb; p.out_f16 = out_f16;
     return launch_auto(map, p, stream);
 }

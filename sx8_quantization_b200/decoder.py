@@ -72,6 +72,8 @@ class SX8Decoder:
         if self.B <= 8:
             self.multi = [(ops.MultiGemv([L["q"], L["k"], L["v"]], self.B, self.dev),
                            ops.MultiGemv([L["gate"], L["up"]], self.B, self.dev)) for L in self.layers]
+        # projections that share their input as one tensor-core launch (prefill; decode above 8 rows)
+        self.multi_gemm = [(ops.MultiGemm([L["q"], L["k"], L["v"]]), ops.MultiGemm([L["gate"], L["up"]])) for L in self.layers]
         self.graph = None
         self.fused_glue = bool(fused_glue)
         f16, f32 = dict(dtype=torch.float16, device=self.dev), dict(dtype=torch.float32, device=self.dev)
@@ -113,9 +115,8 @@ class SX8Decoder:
         cos, sin = self.cos[:T], self.sin[:T]                                       # (T, D/2)
         for l, L in enumerate(self.layers):
             x = self._norm(h)
-            q = self._linear(x, L["q"], torch.float16).view(B, T, hq, D)
-            k = self._linear(x, L["k"], torch.float16).view(B, T, hkv, D)
-            v = self._linear(x, L["v"], torch.float16).view(B, T, hkv, D)
+            q, k, v = self.multi_gemm[l][0](x, out_dtype=torch.float16)
+            q, k, v = q.view(B, T, hq, D), k.view(B, T, hkv, D), v.view(B, T, hkv, D)
             q = _rope(q.float(), cos[None, :, None, :], sin[None, :, None, :]).half().transpose(1, 2)
             k = _rope(k.float(), cos[None, :, None, :], sin[None, :, None, :]).half().transpose(1, 2)
             v = v.transpose(1, 2)
@@ -125,8 +126,7 @@ class SX8Decoder:
             a = a.transpose(1, 2).reshape(B * T, hq * D)
             h = h + self._linear(a, L["o"])
             x = self._norm(h)
-            g = self._linear(x, L["gate"], torch.float16)
-            u = self._linear(x, L["up"], torch.float16)
+            g, u = self.multi_gemm[l][1](x, out_dtype=torch.float16)
             h = h + self._linear(F.silu(g) * u, L["down"])
         last = self._norm(h.view(B, T, -1)[:, -1])
         logits = self._linear(last, self.lm_head)
@@ -152,7 +152,7 @@ class SX8Decoder:
             if self.multi is not None:
                 q, k, v = self.multi[l][0](b["x"], flags=SX8_F_PDL)
             else:
-                q, k, v = (self._lin_into(b["x"], L[n], b[n]) for n in ("q", "k", "v"))
+                q, k, v = self.multi_gemm[l][0](b["x"], outs=[b["q"], b["k"], b["v"]])
             ops.glue_rope_cache(q, k, v, self.pos, self.cos, self.sin, hq, hkv, D, b["q16"], self.k_cache[l], self.v_cache[l])
             ops.glue_attn_decode(b["q16"], self.k_cache[l], self.v_cache[l], self.pos, hq, hkv, D, self.scale, b["a"],
                                  self.attn_scratch)
@@ -161,7 +161,7 @@ class SX8Decoder:
             if self.multi is not None:
                 g, u = self.multi[l][1](b["x"], flags=SX8_F_PDL)
             else:
-                g, u = self._lin_into(b["x"], L["gate"], b["g"]), self._lin_into(b["x"], L["up"], b["u"])
+                g, u = self.multi_gemm[l][1](b["x"], outs=[b["g"], b["u"]])
             ops.glue_silu_mul(g, u, b["act"])
             y = self._lin_into(b["act"], L["down"], b["d"])
         ops.glue_add_rmsnorm(b["h"], y, self.gamma, c["eps"], b["x"])
@@ -186,7 +186,7 @@ class SX8Decoder:
             if self.multi is not None:
                 q, k, v = self.multi[l][0](x, flags=SX8_F_PDL)
             else:
-                q, k, v = self._linear(x, L["q"]), self._linear(x, L["k"]), self._linear(x, L["v"])
+                q, k, v = self.multi_gemm[l][0](x)
             q = _rope(q.view(B, hq, D), cos[:, None, :], sin[:, None, :]).half()
             k = _rope(k.view(B, hkv, D), cos[:, None, :], sin[:, None, :]).half()
             self.k_cache[l].index_copy_(2, self.pos, k.unsqueeze(2))
@@ -199,7 +199,7 @@ class SX8Decoder:
             if self.multi is not None:
                 g, u = self.multi[l][1](x, flags=SX8_F_PDL)
             else:
-                g, u = self._linear(x, L["gate"]), self._linear(x, L["up"])
+                g, u = self.multi_gemm[l][1](x)
             h = h + self._linear((F.silu(g) * u).half(), L["down"])
         logits = self._linear(self._norm(h), self.lm_head)
         self.tok.copy_(logits.argmax(-1))

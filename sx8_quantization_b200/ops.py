@@ -138,6 +138,50 @@ class MultiGemv:
         return self.outs
 
 
+class MultiGemm:
+    """Prepared argument block for sx8_gemm_multi: up to three matrices that share x (q|k|v,
+    gate|up) in one tensor-core launch.  Build once per group of tensors; every call returns new
+    output tensors (M may differ between calls)."""
+
+    def __init__(self, tensors):
+        import ctypes
+        if not 1 <= len(tensors) <= 3:
+            raise SX8Error("1..3 matrices per launch")
+        self.n_cb = tensors[0]["n_cb"]
+        self.K = tensors[0]["K"]
+        if any(t["n_cb"] != self.n_cb or t["K"] != self.K for t in tensors):
+            raise SX8Error("all matrices of a launch must have the same K")
+        n = len(tensors)
+        self.tensors = tensors
+        VP, I = ctypes.c_void_p * n, ctypes.c_int * n
+        self._VP = VP
+        self._wt = VP(*[t["wt16"].data_ptr() for t in tensors])
+        self._ba = VP(*[t["bases"].data_ptr() for t in tensors])
+        self._sc = VP(*[t["scales"].data_ptr() for t in tensors])
+        self._N = I(*[t["N"] for t in tensors])
+        self.count = n
+
+    def __call__(self, x, out_dtype=torch.float32, outs=None, workspace=None):
+        if x.dtype != torch.float16 or not x.is_cuda or x.dim() != 2 or x.stride(1) != 1:
+            raise SX8Error("x must be CUDA float16 (M, K) with unit inner stride")
+        if out_dtype not in (torch.float32, torch.float16):
+            raise SX8Error("out_dtype must be float32 or float16")
+        M = x.shape[0]
+        if outs is None:
+            outs = [torch.empty((M, t["N"]), dtype=out_dtype, device=x.device) for t in self.tensors]
+        elif any(o.dtype != out_dtype or o.shape != (M, t["N"]) or not o.is_contiguous() for o, t in zip(outs, self.tensors)):
+            raise SX8Error("outs must be contiguous (M, N_i) tensors of out_dtype")
+        L = _lib.lib()
+        need = L.sx8_gemm_multi_workspace_bytes(M, self.count, self._N, self.n_cb)
+        ws = workspace if workspace is not None else Workspace.get(x.device, need, tag="gemm")
+        y = self._VP(*[o.data_ptr() for o in outs])
+        with torch.cuda.device(x.device):
+            rc = L.sx8_gemm_multi(x.data_ptr(), M, self.K, x.stride(0), self.count, self._wt, self._ba, self._sc, self._N,
+                                  y, int(out_dtype == torch.float16), self.n_cb, ws.data_ptr(), ws.numel(), _stream(x))
+        _lib.check(rc, "sx8_gemm_multi")
+        return outs
+
+
 def gemv_allreduce(x, wt16, bases, scales, N, K, n_cb, peers, out=None, flags=0, workspace=None):
     """Row-parallel partial GEMV fused with its all-reduce over peer memory: y (M,N) f32 on
     every rank = sum over ranks of x_r @ W_r^T.  `peers` is a _lib.Peers descriptor."""

@@ -185,3 +185,44 @@ def test_quantizer_pca_kernels_against_torch_ops(shape, dtype):
     assert torch.equal(byte, want)
     # end to end: same bytes as the torch stage except where a coefficient sits on a rounding boundary
     assert (byte != ref["coeff"]).float().mean().item() < 1e-3
+
+
+@pytest.mark.parametrize("Ns,K,M", [((4096, 1024, 1024), 2560, 32), ((4096, 1024, 1024), 2560, 512), ((9728, 9728), 2560, 2048),
+                                     ((512, 256, 272), 1024, 40), ((1024, 1000), 1000, 64),
+                                     ((272, 512), 1024, 100), ((4096, 1024, 1024), 2560, 12)])
+@pytest.mark.parametrize("f16out", [True, False])
+def test_gemm_multi_matches_separate_calls(Ns, K, M, f16out):
+    """sx8_gemm_multi: q|k|v and gate|up in one tensor-core launch (every matrix but the last a
+    multiple of 256 columns wide, M > 16), and its per-matrix route for the rest (first matrix 272
+    columns wide; M = 12).  Each output against a float32 matmul on the library's own decode and
+    against the single-matrix call."""
+    from sx8_quantization_b200 import ops, _lib
+    ts = [_tensor(n, K, 500 + i)[0] for i, n in enumerate(Ns)]
+    x = _x(M, K, 23)
+    od = torch.float16 if f16out else torch.float32
+    mg = ops.MultiGemm(ts)
+    outs = mg(x, out_dtype=od)
+    tol = 3e-3 + (2.0 ** -10 if f16out else 0.0)
+    for t, y in zip(ts, outs):
+        w = ops.dequant_t16(t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"], True)
+        ref = x.float() @ w.float().t()
+        assert y.shape == (M, t["N"]) and y.dtype == od
+        assert (y.float() - ref).abs().max().item() <= tol * ref.abs().max().item()
+        one = ops.gemm(x, t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"], out_dtype=od)
+        assert (y.float() - one.float()).abs().max().item() <= 2e-3 * ref.abs().max().item()
+    again = mg(x, out_dtype=od)
+    assert all(torch.equal(a, b) for a, b in zip(outs, again))
+    assert _lib.device_error_flag() == 0
+
+
+def test_gemm_multi_rejects_bad_arguments():
+    from sx8_quantization_b200 import ops
+    t1, _ = _tensor(256, 512, 1)
+    t2, _ = _tensor(256, 1024, 2)
+    with pytest.raises(ops.SX8Error):
+        ops.MultiGemm([t1, t2])                                  # different K
+    with pytest.raises(ops.SX8Error):
+        ops.MultiGemm([t1, t1, t1, t1])                          # more than three
+    mg = ops.MultiGemm([t1, t1])
+    with pytest.raises(ops.SX8Error):
+        mg(_x(32, 512, 1), outs=[torch.empty(32, 256, device="cuda"), torch.empty(31, 256, device="cuda")])
