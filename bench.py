@@ -430,6 +430,23 @@ def other_kernels(dev, layer0, head, fam):
             del x, y
         gem["%s_%dx%d" % (name, t["N"], t["K"])] = row
     out["prefill_gemm"] = gem
+    # projections that share their input, one launch (sx8_gemm_multi): q|k|v and gate|up
+    fused = {}
+    for name, ts in (("q_k_v", [layer0["q"], layer0["k"], layer0["v"]]), ("gate_up", [layer0["gate"], layer0["up"]])):
+        mg = ops.MultiGemm(ts)
+        row = {}
+        for M in (128, 512, 2048, 8192):
+            x = torch.randn(M, ts[0]["K"], generator=g, device=dev).half()
+            outs = [torch.empty(M, t["N"], dtype=torch.float16, device=dev) for t in ts]
+            us = _time_us(lambda: mg(x, out_dtype=torch.float16, outs=outs))
+            us_sep = _time_us(lambda: [ops.gemm(x, t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"],
+                                                out_dtype=torch.float16, out=o) for t, o in zip(ts, outs)])
+            tf = 2.0 * M * sum(t["N"] for t in ts) * ts[0]["K"] / us / 1e6
+            row[str(M)] = {"us": round(us, 1), "us_separate_launches": round(us_sep, 1), "TFLOPs": round(tf, 1),
+                           "frac_of_bf16_burst": round(tf / pk["bf16_tflops"], 3)}
+            del x, outs
+        fused[name] = row
+    out["prefill_gemm_fused"] = fused
     t = layer0["gate"]
     w = quantizer.synth_weight_gpu(t["N"], t["K"], 4242, dev)
     us = _time_us(lambda: ops.quantize_blocks(w))

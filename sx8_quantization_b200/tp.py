@@ -202,11 +202,10 @@ class TPStack:
         if M <= 8:
             self.multi = [(ops.MultiGemv([L["q"], L["k"], L["v"]], M, device), ops.MultiGemv([L["gate"], L["up"]], M, device))
                           for L in layers]
-        else:
-            self.q = torch.empty(M, L0["q"]["N"], **f32)
-            self.kv = torch.empty(M, L0["k"]["N"], **f32)
-            self.g = torch.empty(M, L0["gate"]["N"], **f32)
-            self.u = torch.empty(M, L0["up"]["N"], **f32)
+        else:   # one tensor-core launch per group where the shard widths allow it (sx8_gemm_multi)
+            self.qkv = [torch.empty(M, L0[n]["N"], **f32) for n in ("q", "k", "v")]
+            self.gu = [torch.empty(M, L0[n]["N"], **f32) for n in ("gate", "up")]
+            self.multi_gemm = [(ops.MultiGemm([L["q"], L["k"], L["v"]]), ops.MultiGemm([L["gate"], L["up"]])) for L in layers]
         self.logits_local = torch.empty(M, head["N"], **f32) if head is not None else None
         self.logits = None
         if head is not None and self.world > 1:
@@ -233,20 +232,13 @@ class TPStack:
             if self.multi is not None:
                 q, _, _ = self.multi[i][0](self.x, flags=self.flags)
             else:
-                q = ops.gemm(self.x, L["q"]["wt16"], L["q"]["bases"], L["q"]["scales"], L["q"]["N"], L["q"]["K"],
-                             L["q"]["n_cb"], out=self.q)
-                for nm in ("k", "v"):
-                    ops.gemm(self.x, L[nm]["wt16"], L[nm]["bases"], L[nm]["scales"], L[nm]["N"], L[nm]["K"],
-                             L[nm]["n_cb"], out=self.kv)
+                q, _, _ = self.multi_gemm[i][0](self.x, outs=self.qkv)
             self.attn.copy_(q)                                        # stand-in for attention over the cache
             self._row_norm(self.attn, L["o"], self.y_o)
             if self.multi is not None:
                 g, u = self.multi[i][1](self.x, flags=self.flags)
             else:
-                g = ops.gemm(self.x, L["gate"]["wt16"], L["gate"]["bases"], L["gate"]["scales"], L["gate"]["N"],
-                             L["gate"]["K"], L["gate"]["n_cb"], out=self.g)
-                u = ops.gemm(self.x, L["up"]["wt16"], L["up"]["bases"], L["up"]["scales"], L["up"]["N"], L["up"]["K"],
-                             L["up"]["n_cb"], out=self.u)
+                g, u = self.multi_gemm[i][1](self.x, outs=self.gu)
             ops.glue_silu_mul(g, u, self.act)
             self._row_norm(self.act, L["down"], self.y_d)
         if self.head is not None:
