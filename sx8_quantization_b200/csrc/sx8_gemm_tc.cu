@@ -310,9 +310,9 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
 
 
 // G = decode groups: the 16 decode warps form G groups of 16/G warps that take every G-th stage.
-// KS = 2 (one-CTA tiles only): a cluster of two CTAs shares one output tile, each taking half of
-// the K range; CTA 1 hands its accumulator to CTA 0 through distributed shared memory.  For
-// small M, where there are fewer tiles than SMs and decoding the weights bounds the time.
+// KS = 2 or 4 (one-CTA tiles only): a cluster of KS CTAs shares one output tile, each taking 1/KS
+// of the K range; CTAs 1 .. KS-1 hand their accumulators to CTA 0 through distributed shared
+// memory.  For small M, where there are fewer tiles than SMs and decoding the weights bounds the time.
 template <int MT, int BN, int PAIR, int G, int KS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap0,
@@ -340,7 +340,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // PAIR == 2: the cluster is two consecutive CTAs along x; rank 0 leads (issues the MMAs).
     const int rank = (PAIR == 2) ? (int)(blockIdx.x & 1) : 0;
-    const int krank = (KS == 2) ? (int)(blockIdx.x & 1) : 0;
+    static_assert(KS == 1 || KS == 2 || KS == 4, "split-K over a cluster of 2 or 4");
+    const int krank = (KS > 1) ? (int)(blockIdx.x & (KS - 1)) : 0;
     const int nv0 = (int)(blockIdx.x / (PAIR * KS)) * BNU;   // first accumulator column among all matrices' columns
     const int m0 = blockIdx.y * (128 * MT * PAIR);
     // the matrix of this CTA
@@ -356,12 +357,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     const __half* const mat_pb = p.pb + (long)mi * p.n_cb * 64;
     const int tile0 = (n0 + rank * BN) >> 4;                 // first 16-column tile this CTA decodes
     const int n_ks_all = (p.n_cb + KB_STAGE - 1) / KB_STAGE;
-    const int ks_half = (n_ks_all + KS - 1) / KS;
+    const int ks_half = (n_ks_all + KS - 1) / KS;            // K stages per CTA of the cluster
     const int ks0 = krank * ks_half;                         // first K stage of this CTA
-    const int n_ks = (KS == 2) ? max(0, min(ks_half, n_ks_all - ks0)) : n_ks_all;
+    const int n_ks = (KS > 1) ? max(0, min(ks_half, n_ks_all - ks0)) : n_ks_all;
 
     if (threadIdx.x == 0) {
-        mbar_init(xfer_full, kDecodeWarps);
+        mbar_init(xfer_full, kDecodeWarps * (KS > 1 ? KS - 1 : 1));
         for (int s = 0; s < SA; s++) { mbar_init(a_full + 8 * s, 1); mbar_init(a_empty + 8 * s, 1); }
         for (int s = 0; s < SA; s++) mbar_init(a_peer + 8 * s, 1);
         for (int s = 0; s < SB; s++) { mbar_init(b_full + 8 * s, kGroupWarps * PAIR); mbar_init(b_empty + 8 * s, 1); }
@@ -380,7 +381,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if constexpr (PAIR == 2 || KS == 2) cluster_sync_all();   // the peer's barriers exist before anyone arrives on them
+    if constexpr (PAIR == 2 || KS > 1) cluster_sync_all();   // the peer's barriers exist before anyone arrives on them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = lds32(tmem_slot);
 
@@ -669,12 +670,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         // bytes, 16-byte chunks XOR-swizzled with the row index (the Y tensor map's swizzle).
         // (the host checks that the X and operand stages together hold the 64 KB of staging)
         const uint32_t stg = sA + (uint32_t)dw * 4096u;
-        // Split-K: CTA 1 parks its accumulators in its (idle) X, operand and slab stages, 4 KB per
-        // (accumulator, 32-column chunk, lane quarter), and tells CTA 0; CTA 0 adds them in below.
-        uint32_t peer_xfer = 0;
+        // Split-K: CTAs 1 .. KS-1 park their accumulators in their (idle) X, operand and slab stages, 4 KB
+        // per (accumulator, 32-column chunk, lane quarter), and tell CTA 0; CTA 0 adds them in below, in
+        // rank order.
+        uint32_t peer_xfer[KS > 1 ? KS - 1 : 1] = {};
         auto xfer_off = [&](int mt, int c32) { return (uint32_t)(((mt * (BNU / 32) + c32) * 4 + quarter) * 4096); };
-        if constexpr (KS == 2) {
-            if (krank == 1) {
+        auto add_peers = [&](int mt, int c32, uint32_t (&v)[32]) {
+#pragma unroll
+            for (int r = 0; r < KS - 1; r++) add_xfer(peer_xfer[r] + xfer_off(mt, c32), lane, v);
+        };
+        if constexpr (KS > 1) {
+            if (krank != 0) {
 #pragma unroll 1
                 for (int mt = 0; mt < MT; mt++)
 #pragma unroll 1
@@ -688,11 +694,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 if (lane == 0) mbar_arrive_cl(mapa_u32(xfer_full, 0u));
             } else {
                 if (ok) ok = mbar_wait_cl(xfer_full, 0u, 0x2000u);
-                peer_xfer = mapa_u32(sA, 1u);
+#pragma unroll
+                for (int r = 0; r < KS - 1; r++) peer_xfer[r] = mapa_u32(sA, (uint32_t)(r + 1));
             }
         }
 #pragma unroll 1
-        for (int mt = 0; mt < ((KS == 2 && krank == 1) ? 0 : MT); mt++) {
+        for (int mt = 0; mt < ((KS > 1 && krank != 0) ? 0 : MT); mt++) {
             const int mrow0 = m0 + (mt * PAIR + rank) * 128 + quarter * 32;
             const long m = (long)mrow0 + lane;
             if (p.tma_store && p.out_f16) {
@@ -703,9 +710,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 const int col = c64 * 64;
                 tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BNU + col), v);
                 tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BNU + col + 32), w);
-                if constexpr (KS == 2) {
-                    add_xfer(peer_xfer + xfer_off(mt, 2 * c64), lane, v);
-                    add_xfer(peer_xfer + xfer_off(mt, 2 * c64 + 1), lane, w);
+                if constexpr (KS > 1) {
+                    add_peers(mt, 2 * c64, v);
+                    add_peers(mt, 2 * c64 + 1, w);
                 }
                 asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                 __syncwarp();
@@ -734,7 +741,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                     const int col = c32 * 32;
                     uint32_t v[32];
                     tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BNU + col), v);
-                    if constexpr (KS == 2) add_xfer(peer_xfer + xfer_off(mt, c32), lane, v);
+                    if constexpr (KS > 1) add_peers(mt, c32, v);
                     if (p.tma_store) {
                         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // staging free again
                         __syncwarp();
@@ -774,7 +781,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     __syncthreads();
     // PAIR == 2: neither CTA may free its tensor memory or leave (its shared memory is read by
     // the pair's MMAs and its barriers are arrived on remotely) before both are done.
-    if constexpr (PAIR == 2 || KS == 2) cluster_sync_all();
+    if constexpr (PAIR == 2 || KS > 1) cluster_sync_all();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if constexpr (PAIR == 2)
@@ -909,7 +916,7 @@ int launch_tc_bn(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
         }
     }
     // (the hand-over may run on from the X and operand stages into the slab stages: all idle by then)
-    if (KS == 2 && p.sa * MT * tc::A_TILE + p.sb * C::B_TILE + p.sp * C::P_STAGE < MT * C::BNU * 512) {
+    if (KS > 1 && p.sa * MT * tc::A_TILE + p.sb * C::B_TILE + p.sp * C::P_STAGE < MT * C::BNU * 512) {
         set_error("sx8_gemm: split-K hand-over does not fit the pipeline stages");
         return SX8_E_UNSUPPORTED;
     }
@@ -925,7 +932,7 @@ int launch_tc_bn(const CUtensorMap& map, tc::Params p, cudaStream_t stream) {
     attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see the kernel: weights are prefetched under the kernel ahead
     attr[na].val.programmaticStreamSerializationAllowed = 1;
     na++;
-    if (PAIR * KS == 2) {
+    if (PAIR * KS > 1) {
         attr[na].id = cudaLaunchAttributeClusterDimension;
         attr[na].val.clusterDim.x = PAIR * KS;
         attr[na].val.clusterDim.y = 1;
@@ -952,10 +959,17 @@ int launch_tc(const CUtensorMap& map, const tc::Params& p, cudaStream_t stream) 
     // idle (74 two-SM clusters fit at once) and K is long enough to halve: 9472 x 2560 at
     // M = 128 runs in 28.8 us against 35.0, 2560 x 9728 in 61.7 against 86.4 with 64-column
     // tiles (SX8_GEMM_KSPLIT=0 switches it off).
+    // Over a cluster of four when even that fills at most half of the SMs and K is long: the
+    // hand-over of three accumulator sets has to be paid for by the stages saved (2560 x 9728 at
+    // M = 32: 58 -> 43 us, 2560 x 4096: 29 -> 27 us; with K = 2560 it loses: 22 -> 24 us; with two
+    // accumulators per CTA it pays from K = 8192 on).
     static const int ksplit = exp_env("SX8_GEMM_KSPLIT", 1);
-    const bool can_split = ksplit && ((p.N + 127) / 128) * mtiles <= 74 && p.n_cb >= 32;
-    if (bn == 128 && !can_split && ((p.N + 63) / 64) * mtiles <= 148 && ((p.N + 127) / 128) * mtiles <= 37) bn = 64;
+    const long tiles128 = (long)((p.N + 127) / 128) * mtiles;
+    const bool can_split = ksplit && tiles128 <= 74 && p.n_cb >= 32;
+    const bool can_split4 = ksplit != 2 && can_split && tiles128 <= 37 && p.n_cb >= (MT == 1 ? 128 : 256);
+    if (bn == 128 && !can_split && ((p.N + 63) / 64) * mtiles <= 148 && tiles128 <= 37) bn = 64;
     if (force_bn == 64 || force_bn == 128 || force_bn == 256) bn = force_bn;
+    if (bn == 128 && can_split4) return launch_tc_bn<MT, 128, 1, 2, 4>(map, p, stream);
     if (bn == 128 && can_split) return launch_tc_bn<MT, 128, 1, 2, 2>(map, p, stream);
     if (bn == 256) return launch_tc_bn<MT, 256, 1>(map, p, stream);
     if (bn == 128) return launch_tc_bn<MT, 128, 1>(map, p, stream);
@@ -978,7 +992,8 @@ int launch_auto(const CUtensorMap& map, const tc::Params& p, cudaStream_t stream
         // wave and halve the decode work per CTA.
         const long pair_ctas = 2L * ((p.N + 255) / 256) * ((p.M + 511) / 512);
         const long one_tiles = (long)((p.N + 127) / 128) * ((p.M + 255) / 256);
-        const long one_ctas = (one_tiles <= 74 && p.n_cb >= 32) ? 2 * one_tiles : one_tiles;
+        const long one_ctas = (one_tiles <= 37 && p.n_cb >= 256) ? 4 * one_tiles
+                              : ((one_tiles <= 74 && p.n_cb >= 32) ? 2 * one_tiles : one_tiles);   // launch_tc's split-K
         if (pair_ctas < 100 && one_ctas <= 148 && one_ctas > pair_ctas) return launch_tc<2>(map, p, stream);
     }
     if (pair_mode == 2 || (pair_mode == 1 && p.M > 256)) {

@@ -12,7 +12,8 @@ float32 restatement of the reference kernel's formula): the oracle would need mi
   * the tensor-core GEMM instantiations of the BASELINE prefill sizes: the gate projection at
     M = 128 (76 one-CTA 128-column tiles, no split-K) and M = 512 (two-CTA tiles), the narrow
     projections at M = 512 / 2048 (one-CTA 256 x 128 tiles over several row tiles, with and
-    without the split-K cluster), and a vocabulary-sized N at M = 32 and 256 (256-column tiles);
+    without the split-K cluster), the four-CTA split-K cluster of narrow matrices at small M (one and
+    two accumulators, ragged K), and a vocabulary-sized N at M = 32 and 256 (256-column tiles);
   * the PCA stage of the quantizer driver (functional parity with the reference algorithm).
 """
 import numpy as np
@@ -83,7 +84,8 @@ def test_gemv_lm_head_sizes(shape, M):
 
 @pytest.mark.parametrize("shape,M", [((9728, 2560), 128), ((9728, 2560), 512), ((4096, 2560), 128), ((2560, 9728), 512),
                                      ((1024, 2560), 2048), ((4096, 2560), 512), ((2560, 4096), 2048),
-                                     ((19456, 512), 32), ((19456, 512), 256), ((151936, 2560), 32)])
+                                     ((19456, 512), 32), ((19456, 512), 256), ((151936, 2560), 32),
+                                     ((2560, 4096), 32), ((2560, 4096), 200), ((2560, 9728), 128), ((1000, 2100), 64)])
 @pytest.mark.parametrize("f16out", [True, False])
 def test_gemm_bench_instantiations(shape, M, f16out):
     from sx8_quantization_b200 import ops, _lib
