@@ -85,7 +85,8 @@ def test_gemv_lm_head_sizes(shape, M):
 @pytest.mark.parametrize("shape,M", [((9728, 2560), 128), ((9728, 2560), 512), ((4096, 2560), 128), ((2560, 9728), 512),
                                      ((1024, 2560), 2048), ((4096, 2560), 512), ((2560, 4096), 2048),
                                      ((19456, 512), 32), ((19456, 512), 256), ((151936, 2560), 32),
-                                     ((2560, 4096), 32), ((2560, 4096), 200), ((2560, 9728), 128), ((1000, 2100), 64)])
+                                     ((2560, 4096), 32), ((2560, 4096), 200), ((2560, 9728), 128), ((1000, 2100), 64),
+                                     ((1024, 8192), 200), ((1000, 4100), 64)])
 @pytest.mark.parametrize("f16out", [True, False])
 def test_gemm_bench_instantiations(shape, M, f16out):
     from sx8_quantization_b200 import ops, _lib
