@@ -412,9 +412,7 @@ def other_kernels(dev, layer0, head, fam):
                                                          "hbm_gbs": FALLBACK_HBM_GBS}
     g = torch.Generator(device=dev).manual_seed(77)
     gem = {}
-    shapes = [("q", layer0["q"]), ("k_v", layer0["k"]), ("o", layer0["o"]), ("gate_up", layer0["gate"]),
-              ("down", layer0["down"]), ("lm_head", head)]
-    for name, t in shapes:
+    def gemm_row(name, t):
         row = {}
         for M in (128, 512, 2048, 8192):
             x = torch.randn(M, t["K"], generator=g, device=dev).half()
@@ -429,7 +427,10 @@ def other_kernels(dev, layer0, head, fam):
                 row[str(M)]["frac_of_hbm"] = round(by / us / 1e3 / pk["hbm_gbs"], 3)
             del x, y
         gem["%s_%dx%d" % (name, t["N"], t["K"])] = row
-    out["prefill_gemm"] = gem
+
+    for name, t in [("q", layer0["q"]), ("k_v", layer0["k"]), ("o", layer0["o"]), ("gate_up", layer0["gate"]),
+                    ("down", layer0["down"])]:
+        gemm_row(name, t)
     # projections that share their input, one launch (sx8_gemm_multi): q|k|v and gate|up
     fused = {}
     for name, ts in (("q_k_v", [layer0["q"], layer0["k"], layer0["v"]]), ("gate_up", [layer0["gate"], layer0["up"]])):
@@ -446,6 +447,8 @@ def other_kernels(dev, layer0, head, fam):
                            "frac_of_bf16_burst": round(tf / pk["bf16_tflops"], 3)}
             del x, outs
         fused[name] = row
+    gemm_row("lm_head", head)   # last: its 6 ms launches at M = 8192 run into the power cap and would colour what follows
+    out["prefill_gemm"] = gem
     out["prefill_gemm_fused"] = fused
     t = layer0["gate"]
     w = quantizer.synth_weight_gpu(t["N"], t["K"], 4242, dev)
@@ -1039,6 +1042,9 @@ def run_case(args):
     if args.case == "quantize":
         fn = lambda: ops.quantize_blocks(w)
         units, unit = N * ((K + 31) // 32), "blocks"
+    elif args.case == "quantize_pca":   # search + PCA stage + device layout
+        fn = lambda: quantizer.quantize_tensor(w, with_pca=True)
+        units, unit = N * ((K + 31) // 32), "blocks"
     else:
         t = quantizer.quantize_tensor(w, with_pca=True)
         del w
@@ -1098,7 +1104,7 @@ def main():
                     help="row-parallel reduction: peer-memory exchange (pull = all-reduce + RMSNorm kernel, push = from "
                          "the GEMV epilogue), NCCL, or whichever replays faster")
     ap.add_argument("--no-tp1", action="store_true", help="N > 1: skip the unsharded run on rank 0")
-    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "embed", "dequant", "quantize"],
+    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "embed", "dequant", "quantize", "quantize_pca"],
                     help="time one kernel on one synthetic tensor (for profilers)")
     ap.add_argument("--N", type=int, default=9728)
     ap.add_argument("--K", type=int, default=2560)
