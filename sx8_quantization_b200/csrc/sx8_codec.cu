@@ -1,7 +1,8 @@
-// sx8_codec.cu -- bit-exact S-X8 v4.3 codec kernels for sm_100a: full-tensor decode,
-// embedding-row decode, quantizer search + packing, file-plane -> device-layout repack.
-// All four are HBM-bound byte/float work: one thread owns one 8-weight sub-block, so a
-// warp touches 8 consecutive blocks with 4-, 8- and 16-byte accesses.
+// sx8_codec.cu -- S-X8 v4.3 codec kernels for sm_100a.  Bit-exact with the reference: full-tensor
+// decode, embedding-row decode, quantizer search + packing, file-plane -> device-layout repack.
+// Functional parity (the reference's result depends on its LAPACK build): the three passes of the
+// quantizer's PCA stage.  All of it is byte/float work on CUDA cores in which one thread owns one
+// 8-weight sub-block, so a warp touches 8 consecutive blocks with 4-, 8- and 16-byte accesses.
 #include "sx8_common.cuh"
 #include "sx8_layout.cuh"
 
