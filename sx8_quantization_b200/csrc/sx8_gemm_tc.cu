@@ -969,9 +969,6 @@ int launch_tc(const CUtensorMap& map, const tc::Params& p, cudaStream_t stream) 
     const bool can_split4 = ksplit != 2 && can_split && tiles128 <= 37 && p.n_cb >= (MT == 1 ? 128 : 256);
     if (bn == 128 && !can_split && ((p.N + 63) / 64) * mtiles <= 148 && tiles128 <= 37) bn = 64;
     if (force_bn == 64 || force_bn == 128 || force_bn == 256) bn = force_bn;
-#ifdef SX8_EXPERIMENT
-    if (ksplit == 3) return launch_tc_bn<MT, 256, 1, 2, 2>(map, p, stream);
-#endif
     if (bn == 128 && can_split4) return launch_tc_bn<MT, 128, 1, 2, 4>(map, p, stream);
     if (bn == 128 && can_split) return launch_tc_bn<MT, 128, 1, 2, 2>(map, p, stream);
     if (bn == 256) return launch_tc_bn<MT, 256, 1>(map, p, stream);
