@@ -123,7 +123,8 @@ int sx8_gemm(const void* x_f16, int M, int K, long ldx, const void* wt16, const 
  * matrices with the same K (q|k|v, gate|up).  When M > 16 and every N[i] but the last is a
  * multiple of 256, all of them run in ONE launch of the tensor-core kernel (their columns side by
  * side in one grid: the small k and v projections no longer leave most SMs idle, and one launch
- * replaces three); otherwise the call is count calls of sx8_gemm.  Same results either way.
+ * replaces three); when M <= 16 and Y is float32, in one launch of the GEMV kernel; otherwise the
+ * call is count calls of sx8_gemm.  Same results either way.
  * Arrays are host arrays of device pointers / sizes.                                   */
 size_t sx8_gemm_multi_workspace_bytes(int M, int count, const int* N, int n_cb);
 int sx8_gemm_multi(const void* x_f16, int M, int K, long ldx, int count, const void* const* wt16,

@@ -12,6 +12,12 @@ int gemv_launch(const void* x, int M, int K, long ldx, const void* wt16, const f
 int gemv_rows_launch(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
                      const float* scales, int N, int n_cb, float* y, void* xstage, void* table, unsigned flags,
                      cudaStream_t stream);
+int gemv_rows_launch_multi(const void* x, int M, int K, long ldx, int count, const void* const* wt16,
+                           const float* const* bases, const float* const* scales, const int* N, float* const* y,
+                           int n_cb, void* xstage, void* table, unsigned flags, cudaStream_t stream);
+int gemv_launch_multi(const void* x, int M, int K, long ldx, int count, const void* const* wt16,
+                      const float* const* bases, const float* const* scales, const int* N, float* const* y,
+                      int n_cb, void* workspace, unsigned flags, cudaStream_t stream);
 int gemv_check(const char* who, const void* x, int M, int Mmax, int K, long ldx, const void* wt16,
                const float* bases, const float* scales, int N, int n_cb, const void* y);
 size_t gemm_tc_workspace_bytes(int M, int N, int n_cb);
@@ -95,7 +101,8 @@ extern "C" int sx8_gemm(const void* x, int M, int K, long ldx, const void* wt16,
 static const int kGemmMultiMax = 3;
 
 // One launch when the tensor-core path takes the call (M > 16) and every matrix but the last is a
-// multiple of 256 columns wide; otherwise one sx8_gemm per matrix, with the same results.
+// multiple of 256 columns wide, or when the GEMV kernel takes it (M <= 16) and Y is float32;
+// otherwise one sx8_gemm per matrix, with the same results.
 static bool gemm_multi_fusable(int M, int count, const int* N, int K, int n_cb) {
     if (M <= kGemvRowsMax || count < 2 || !gemm_tc_supported(M, N[0], K, n_cb)) return false;
     for (int i = 0; i + 1 < count; i++)
@@ -106,6 +113,10 @@ static bool gemm_multi_fusable(int M, int count, const int* N, int K, int n_cb) 
 extern "C" size_t sx8_gemm_multi_workspace_bytes(int M, int count, const int* N, int n_cb) {
     if (M <= 0 || count <= 0 || count > kGemmMultiMax || !N || n_cb <= 0) return 0;
     size_t need = gemm_tc_multi_workspace_bytes(M, n_cb, count);
+    if (M <= kGemvRowsMax) {   // [staged x][count activation tables]
+        size_t g = round256((size_t)M * n_cb * 64) + round256((size_t)count * M * n_cb * 16);
+        if (g > need) need = g;
+    }
     for (int i = 0; i < count; i++) {
         size_t one = sx8_gemm_workspace_bytes(M, N[i], n_cb);
         if (one > need) need = one;
@@ -135,6 +146,13 @@ extern "C" int sx8_gemm_multi(const void* x, int M, int K, long ldx, int count, 
     }
     if (gemm_multi_fusable(M, count, N, K, n_cb))
         return gemm_tc_launch_multi(x, M, K, ldx, count, wt16, bases, scales, N, n_cb, y, out_f16, workspace, stream);
+    if (M <= kGemvRowsMax && !out_f16 && count >= 2) {
+        uint8_t* xstage = (uint8_t*)workspace;
+        if (M <= 8)
+            return gemv_launch_multi(x, M, K, ldx, count, wt16, bases, scales, N, (float* const*)y, n_cb, xstage, 0u, stream);
+        return gemv_rows_launch_multi(x, M, K, ldx, count, wt16, bases, scales, N, (float* const*)y, n_cb, xstage,
+                                      xstage + round256((size_t)M * n_cb * 64), 0u, stream);
+    }
     for (int i = 0; i < count; i++) {
         int rc = sx8_gemm(x, M, K, ldx, wt16[i], bases[i], scales[i], N[i], n_cb, y[i], out_f16, workspace, workspace_bytes, stream_);
         if (rc != SX8_OK) return rc;

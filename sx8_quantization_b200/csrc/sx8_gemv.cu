@@ -213,7 +213,7 @@ struct GemvParams {
     const __half* x;       // (M, >= 32*n_cb), rows 16-byte aligned
     long ldx;
     int nseg, n_cb, M, split, groups;
-    const uint8_t* table;  // batches above 8 rows: the activation table in global scratch (n_cb, M, 16 B)
+    const uint8_t* table;  // batches above 8 rows: the activation tables in global scratch, (n_cb, M, 16 B) per matrix
     // Row-parallel exchange (world > 1): instead of y, every finished tile is stored into slot
     // `rank` of each peer's receive buffer (peer memory, plain stores over NVLink), then a
     // per-peer arrival counter is bumped; reduce_peers_kernel sums the slots.
@@ -279,11 +279,18 @@ __device__ __forceinline__ void act_item(const uint4 raw, const float4 (&bq)[4],
 // The table for batches above 8 rows, built once per launch into global scratch (n_cb, M, 16 B)
 // instead of once per CTA into shared memory: the main kernel's producer then brings each
 // stage's slice in with one bulk copy, and a CTA's K range is not limited by table space.
+struct ActTableArgs {
+    const float* bases[kMaxSeg];
+    const float* scales[kMaxSeg];
+};
+// grid (ceil(n_cb * M / 64), matrices): the table of matrix i starts at table + i * n_cb * M * 2.
 __global__ void __launch_bounds__(256)
-act_table_kernel(const __half* __restrict__ x, long ldx, int M, int n_cb, const float* __restrict__ bases,
-                 const float* __restrict__ scales, uint2* __restrict__ table) {
+act_table_kernel(const __half* __restrict__ x, long ldx, int M, int n_cb, ActTableArgs a, uint2* __restrict__ table) {
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    const float* __restrict__ bases = a.bases[blockIdx.y];
+    const float* __restrict__ scales = a.scales[blockIdx.y];
+    table += (long)blockIdx.y * n_cb * M * 2;
     const int t = threadIdx.x & 3;
     const long n_items = (long)n_cb * M;
     long item = (long)blockIdx.x * 64 + (threadIdx.x >> 2);
@@ -390,7 +397,7 @@ __global__ void __launch_bounds__(kThreads, MINB) gemv_kernel(GemvParams p) {
                     bulk_g2s(stage + C::OFF_X + lane * C::XROW, p.x + (long)lane * p.ldx + (long)kb0 * 32,
                              (uint32_t)rows * 64u, bar);
                 if (MB > 1 && lane == 31)
-                    bulk_g2s(stage + C::OFF_T, p.table + (long)kb0 * dt_kb, (uint32_t)(rows * dt_kb), bar);
+                    bulk_g2s(stage + C::OFF_T, p.table + ((long)si * p.n_cb + kb0) * dt_kb, (uint32_t)(rows * dt_kb), bar);
             }
         };
         bool ok = true;
@@ -926,9 +933,11 @@ int gemv_launch_ex(const void* x, int M, int K, long ldx, const void* wt16, cons
 // (one small launch), then the GEMV kernel with two blocks of 8 rows per decoded fragment.
 // xstage: (M, 32*n_cb) f16 scratch, used only when x cannot be fetched as it is; table:
 // n_cb * M * 16 bytes, 16-byte aligned.  Arguments already validated.
-int gemv_rows_launch(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
-                     const float* scales, int N, int n_cb, float* y, void* xstage, void* table, unsigned flags,
-                     cudaStream_t stream) {
+// 9..16 rows: count <= 4 matrices on the same x in one launch (count == 1: the plain case).  table holds
+// count activation tables of n_cb * M * 16 bytes.
+int gemv_rows_launch_multi(const void* x, int M, int K, long ldx, int count, const void* const* wt16,
+                           const float* const* bases, const float* const* scales, const int* N, float* const* y,
+                           int n_cb, void* xstage, void* table, unsigned flags, cudaStream_t stream) {
     const __half* xp = (const __half*)x;
     long ld = ldx;
     const int Kp = n_cb * 32;
@@ -947,19 +956,23 @@ int gemv_rows_launch(const void* x, int M, int K, long ldx, const void* wt16, co
         xp = (const __half*)xstage;
         ld = Kp;
     }
-    cfg.gridDim = dim3((unsigned)(((long)n_cb * M + 63) / 64), 1, 1);
-    cudaError_t e = cudaLaunchKernelEx(&cfg, act_table_kernel, xp, ld, M, n_cb, bases, scales, (uint2*)table);
+    ActTableArgs ta = {};
+    for (int i = 0; i < count; i++) { ta.bases[i] = bases[i]; ta.scales[i] = scales[i]; }
+    cfg.gridDim = dim3((unsigned)(((long)n_cb * M + 63) / 64), (unsigned)count, 1);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, act_table_kernel, xp, ld, M, n_cb, ta, (uint2*)table);
     if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(act_table_kernel)");
-    const int n_tiles = (int)t16_tiles(N);
-    const int groups = (n_tiles + 3) / 4;          // four-tile groups, two CTAs per SM
+    // four-tile groups, one per CTA (two warps share a tile here, and their partial sums are only
+    // combined once, at the end of the CTA), two CTAs per SM; groups never straddle matrices
+    GemvParams p{};
+    p.nseg = count;
+    int groups = 0;
+    for (int i = 0; i < count; i++) {
+        const int nt_i = (int)t16_tiles(N[i]);
+        p.seg[i] = SegDesc{(const uint8_t*)wt16[i], bases[i], scales[i], y[i], N[i], nt_i, groups};
+        groups += (nt_i + 3) / 4;
+    }
     int split = 1;
     while (split < 8 && (long)groups * split < 2 * kSMs && n_cb / (split + 1) >= 8) split++;
-    // one tile group per CTA: two warps share a tile here, and their partial sums are only
-    // combined once, at the end of the CTA
-    const int grid_x = groups;
-    GemvParams p{};
-    p.nseg = 1;
-    p.seg[0] = SegDesc{(const uint8_t*)wt16, bases, scales, y, N, n_tiles, 0};
     p.x = xp; p.ldx = ld; p.table = (const uint8_t*)table;
     p.n_cb = n_cb; p.M = M; p.split = split; p.groups = groups;
     p.rank = 0; p.world = 1; p.slot_elems = 0;
@@ -967,7 +980,13 @@ int gemv_rows_launch(const void* x, int M, int K, long ldx, const void* wt16, co
     // 512 weights, and on this GPU those run at about 32 and 16 cycles each per scheduler
     // (28672 x 8192: 72 us at 8 rows, 106 us at 16, 234 us at 32 with four blocks against 137 us
     // on the tcgen05 kernel), so from 17 rows on the tensor-core GEMM is the faster path.
-    return launch_gemv<4, 8, 3, 2, 2>(p, grid_x, flags, stream);
+    return launch_gemv<4, 8, 3, 2, 2>(p, groups, flags, stream);
+}
+
+int gemv_rows_launch(const void* x, int M, int K, long ldx, const void* wt16, const float* bases,
+                     const float* scales, int N, int n_cb, float* y, void* xstage, void* table, unsigned flags,
+                     cudaStream_t stream) {
+    return gemv_rows_launch_multi(x, M, K, ldx, 1, &wt16, &bases, &scales, &N, &y, n_cb, xstage, table, flags, stream);
 }
 
 // Several matrices that share the activations, one launch (q|k|v, gate|up).  Each CTA owns one

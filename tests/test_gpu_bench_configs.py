@@ -192,13 +192,16 @@ def test_quantizer_pca_kernels_against_torch_ops(shape, dtype):
 
 @pytest.mark.parametrize("Ns,K,M", [((4096, 1024, 1024), 2560, 32), ((4096, 1024, 1024), 2560, 512), ((9728, 9728), 2560, 2048),
                                      ((512, 256, 272), 1024, 40), ((1024, 1000), 1000, 64),
-                                     ((272, 512), 1024, 100), ((4096, 1024, 1024), 2560, 12)])
+                                     ((272, 512), 1024, 100), ((4096, 1024, 1024), 2560, 12), ((4096, 1024, 1024), 2560, 16),
+                                     ((528, 16, 1000), 1000, 9), ((4096, 1024, 1024), 2560, 5)])
 @pytest.mark.parametrize("f16out", [True, False])
 def test_gemm_multi_matches_separate_calls(Ns, K, M, f16out):
     """sx8_gemm_multi: q|k|v and gate|up in one tensor-core launch (every matrix but the last a
-    multiple of 256 columns wide, M > 16), and its per-matrix route for the rest (first matrix 272
-    columns wide; M = 12).  Each output against a float32 matmul on the library's own decode and
-    against the single-matrix call."""
+    multiple of 256 columns wide, M > 16), in one launch of the GEMV kernel (M <= 16 with float32
+    output: two row blocks at 9..16 rows with one activation table per matrix, ragged K and N), and
+    its per-matrix route for the rest (first matrix 272 columns wide; float16 output at M <= 16).
+    Each output against a float32 matmul on the library's own decode and against the
+    single-matrix call."""
     from sx8_quantization_b200 import ops, _lib
     ts = [_tensor(n, K, 500 + i)[0] for i, n in enumerate(Ns)]
     x = _x(M, K, 23)
