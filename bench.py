@@ -1048,6 +1048,16 @@ def run_case(args):
     from sx8_quantization_b200 import _lib, ops, quantizer
     dev = torch.device("cuda:0")
     N, K, M = args.N, args.K, args.M
+    if args.case == "decoder":   # a short eager run of the 4B-shaped decoder: --N layers, --M batch, --K prompt tokens
+        from sx8_quantization_b200.decoder import SX8Decoder, QWEN3_4B_DECODER
+        cfg = dict(QWEN3_4B_DECODER, layers=N)
+        dec = SX8Decoder(cfg, device=dev, seed=9, max_seq=K + 64, batch=M)
+        ids = torch.randint(0, cfg["vocab"], (M, K), generator=torch.Generator(device=dev).manual_seed(1), device=dev)
+        toks, t = dec.generate(ids, args.iters, use_graph=False)
+        print(json.dumps({"case": "decoder", "layers": N, "batch": M, "prompt": K, "new_tokens": args.iters,
+                          "prefill_ms": round(t["prefill_ms"], 3), "decode_ms_per_token": round(t["decode_ms_per_token"], 4),
+                          "device_error_flag": _lib.device_error_flag()}))
+        return
     w = quantizer.synth_weight_gpu(N, K, 3, device=dev)
     g = torch.Generator(device=dev).manual_seed(4)
     if args.case == "quantize":
@@ -1115,7 +1125,7 @@ def main():
                     help="row-parallel reduction: peer-memory exchange (pull = all-reduce + RMSNorm kernel, push = from "
                          "the GEMV epilogue), NCCL, or whichever replays faster")
     ap.add_argument("--no-tp1", action="store_true", help="N > 1: skip the unsharded run on rank 0")
-    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "embed", "dequant", "quantize", "quantize_pca"],
+    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "embed", "dequant", "quantize", "quantize_pca", "decoder"],
                     help="time one kernel on one synthetic tensor (for profilers)")
     ap.add_argument("--N", type=int, default=9728)
     ap.add_argument("--K", type=int, default=2560)
