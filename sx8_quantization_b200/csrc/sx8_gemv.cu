@@ -639,10 +639,19 @@ __global__ void __launch_bounds__(kThreads, MINB) gemv_kernel(GemvParams p) {
 #pragma unroll
             for (int nb = 0; nb < MB; nb++) {
                 uint32_t a = red + ((nb * kConsumerWarps + warp) * 32 + lane) * 16;
-                for (int rk = 1; rk < p.split; rk++) {
-                    float4 u = ld_cluster_f4(a, (uint32_t)rk);
-                    accF[nb][0] += u.x; accF[nb][1] += u.y; accF[nb][2] += u.z; accF[nb][3] += u.w;
-                }
+                // all remote loads first (a load from a peer's shared memory takes several hundred
+                // nanoseconds: one after the other they were the longest phase of a small GEMV), then the
+                // sum in rank order
+                float4 u[7];
+#pragma unroll
+                for (int rk = 1; rk < 8; rk++)
+                    if (rk < p.split) u[rk - 1] = ld_cluster_f4(a, (uint32_t)rk);
+#pragma unroll
+                for (int rk = 1; rk < 8; rk++)
+                    if (rk < p.split) {
+                        accF[nb][0] += u[rk - 1].x; accF[nb][1] += u[rk - 1].y;
+                        accF[nb][2] += u[rk - 1].z; accF[nb][3] += u[rk - 1].w;
+                    }
             }
         }
         cluster_sync_all();  // peers keep their shared memory alive until rank 0 has read it
