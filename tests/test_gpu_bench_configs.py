@@ -232,3 +232,44 @@ def test_gemm_multi_rejects_bad_arguments():
     mg = ops.MultiGemm([t1, t1])
     with pytest.raises(ops.SX8Error):
         mg(_x(32, 512, 1), outs=[torch.empty(32, 256, device="cuda"), torch.empty(31, 256, device="cuda")])
+
+
+def test_gemm_chain_back_to_back_matches_synchronised_calls():
+    """Tensor-core GEMMs launch as programmatic dependent launches: a GEMM prefetches its weights while the
+    kernel ahead still runs, and the kernel that rewrites the shared PCA table waits for the GEMM
+    that still reads it.  A chain in which every GEMM consumes the previous one's output through
+    the same workspace, issued back to back and replayed from a CUDA graph, must give the bits of the
+    same chain run with a device synchronisation after every call."""
+    from sx8_quantization_b200 import ops, _lib
+    dims = [1024, 2560, 1024, 512, 2560]                       # K of link i = N of link i - 1
+    ts = [_tensor(dims[i + 1], dims[i], 600 + i)[0] for i in range(len(dims) - 1)]
+    x = _x(200, dims[0], 31) * 0.05
+
+    def chain(sync):
+        a = x
+        outs = []
+        for t in ts:
+            a = ops.gemm(a, t["wt16"], t["bases"], t["scales"], t["N"], t["K"], t["n_cb"], out_dtype=torch.float16)
+            if sync:
+                torch.cuda.synchronize()
+            outs.append(a)
+        return outs
+
+    want = chain(True)
+    for _ in range(3):
+        got = chain(False)
+        torch.cuda.synchronize()
+        assert all(torch.equal(g, w) for g, w in zip(got, want))
+    assert torch.isfinite(want[-1].float()).all() and want[-1].float().abs().max().item() > 0
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        chain(False)
+        st.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=st):
+            cap = chain(False)
+        for _ in range(3):
+            gr.replay()
+        st.synchronize()
+    assert all(torch.equal(g, w) for g, w in zip(cap, want))
+    assert _lib.device_error_flag() == 0
