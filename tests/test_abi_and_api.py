@@ -48,6 +48,18 @@ def test_host_validation_rejects_before_any_launch():
     assert rc == -1
     rc = L.sx8_quantize_blocks(None, 1, 8, 32, 32, None, None, None, None, None, None, 0, None)
     assert rc == -1
+    rc = L.sx8_pca_gram(None, 1, 8, 32, 32, None, None, None, None, None, None, None, 0, None)
+    assert rc == -1 and b"sx8_pca_gram" in L.sx8_last_error()
+    rc = L.sx8_pca_project(None, 1, 8, 32, 32, None, None, None, None, None, None, None, None)
+    assert rc == -1 and b"sx8_pca_project" in L.sx8_last_error()
+    rc = L.sx8_pca_pack(None, None, 8, 1, None, None)
+    assert rc == -1 and b"sx8_pca_pack" in L.sx8_last_error()
+    rc = L.sx8_gemm_multi(None, 32, 32, 32, 0, None, None, None, None, None, 0, 1, None, 0, None)
+    assert rc == -1 and b"count" in L.sx8_last_error()
+    rc = L.sx8_gemm_multi(None, 32, 32, 32, 2, None, None, None, None, None, 0, 1, None, 0, None)
+    assert rc == -1 and b"null" in L.sx8_last_error()
+    assert L.sx8_gemm_multi_workspace_bytes(32, 0, None, 1) == 0
+    assert L.sx8_pca_gram_scratch_bytes(0, 32) == 0 and L.sx8_pca_gram_scratch_bytes(1000, 64) > 0
 
 
 # (module, function) -> parameter names of the reference's public wrapper API
